@@ -1,0 +1,130 @@
+/*
+ * pto_b200.h - C ABI of the B200 (sm_100a) implementation of the PTO tile library's GEMM hot path.
+ *
+ * Every entry point enqueues work on the caller's CUDA stream and returns immediately (no implicit
+ * synchronisation), like the reference launchers that take `void* stream`. All matrix pointers are
+ * device pointers passed as uint8_t*, as in the reference (`uint8_t* out, uint8_t* src0, uint8_t* src1`).
+ * The caller owns every buffer; the library allocates no device memory.
+ *
+ * Return value: 0 on success, otherwise a PTO_B200_E* code (see pto_b200_error_string). Argument
+ * errors are reported before anything is launched; nothing aborts or traps.
+ *
+ * Storage conventions (reference: include/pto/common/pto_tile.hpp Layout::ND / Layout::DN):
+ *   A    : M x K, row-major (ND), leading dimension lda >= K                       (elements)
+ *   B    : PTO_B200_B_DN  - column-major K x N, i.e. stored N x K row-major, ldb >= K
+ *          PTO_B200_B_ND  - row-major K x N, ldb >= N (16-bit inputs only)
+ *   C    : M x N, row-major (ND), ldc >= N
+ * Base addresses of A and B must be 16-byte aligned and lda/ldb * element size multiples of 16 bytes
+ * (TMA requirement); C has no alignment requirement (aligned C takes the vector-store path).
+ */
+#ifndef PTO_B200_H
+#define PTO_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    PTO_B200_F16 = 0,  /* IEEE half            (reference `half`)          */
+    PTO_B200_BF16 = 1, /* bfloat16             (reference `bfloat16_t`)    */
+    PTO_B200_F32 = 2,  /* float                                              */
+    PTO_B200_S8 = 3,   /* int8_t                                             */
+    PTO_B200_S32 = 4,  /* int32_t                                            */
+    PTO_B200_E4M3 = 5, /* float8_e4m3_t (fn variant: no inf, 0x7f NaN)      */
+    PTO_B200_E5M2 = 6  /* float8_e5m2_t                                      */
+} pto_b200_dtype;
+
+typedef enum {
+    PTO_B200_B_DN = 0, /* B column-major (stored N x K); gemm_performance, mxfp8, gemm_ar */
+    PTO_B200_B_ND = 1  /* B row-major (stored K x N); demos/cpu/gemm_demo              */
+} pto_b200_b_layout;
+
+enum {
+    PTO_B200_OK = 0,
+    PTO_B200_EINVAL = 1,      /* null pointer, non-positive size, ld smaller than the row length  */
+    PTO_B200_EALIGN = 2,      /* A/B base or leading dimension breaks the 16-byte TMA rule        */
+    PTO_B200_EDTYPE = 3,      /* dtype / layout combination outside CheckMadValid's table          */
+    PTO_B200_EWORKSPACE = 4,  /* workspace missing, misaligned or too small                        */
+    PTO_B200_ECUDA = 5,       /* a CUDA runtime / driver call failed (see pto_b200_last_cuda_error)*/
+    PTO_B200_EDEVICE = 6,     /* current device is not compute capability 10.0                     */
+    PTO_B200_ETIMEOUT = 7     /* a kernel gave up on a bounded wait (see pto_b200_device_status)   */
+};
+
+/*
+ * Dense GEMM, C = A * B, fp32 (or int32) accumulate over the whole K: the tile loop
+ * TLOAD -> TEXTRACT -> TMATMUL (k == 0) / TMATMUL_ACC (k > 0) -> TSTORE.
+ * Replaces: RunGemmE2E / LaunchGEMME2E<T>, kernels/manual/a2a3/gemm_performance/gemm_performance_kernel.cpp:170-273
+ * (which hard-codes m = n = k = 6144; sizes are run-time arguments here).
+ *   in_dtype F16 or BF16 -> out_dtype F32, BF16 or F16 (cast = round to nearest even, TSTORE's static_cast,
+ *                           include/pto/cpu/TStore.hpp:187-198)
+ *   in_dtype S8          -> out_dtype S32 (exact accumulators, include/pto/cpu/TMatmul.hpp:104-106)
+ * K-split use (gemm_ar `k_per_rank`, kernels/manual/a2a3/gemm_ar/gemm_compute_kernel.cpp:150-165): pass the
+ * rank's slice pointers with lda = ldb = full K, k = K / ranks and out_dtype F32 to get the fp32 partial.
+ */
+int pto_b200_gemm(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, int m, int n, int k,
+                  long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype, int b_layout);
+
+/*
+ * int8 x int8 -> int32 GEMM with the dequantising store fused:
+ *   out[i][j] = bf16( (float(acc[i][j]) * s_col[j]) * s_row[i] ),  two separately rounded fp32 multiplies.
+ * Replaces: TMATMUL/TMATMUL_ACC on int8 tiles + TSTORE_FP per-column dequant
+ * (kernels/manual/a2a3/dispatch_mega_combine/op_kernel/utils/pto_gmm_preload_async_fixpipe_quant.hpp:75-124,409-411;
+ * scale arithmetic include/pto/cpu/common.hpp:139-185) followed by the per-token row scale
+ * (op_kernel/swiglu.h:101,113). s_col is used as a full fp32 value; to match the reference's 19-bit
+ * per-column scale encoding bit for bit, pass s_col with the low 13 mantissa bits zero.
+ * B is PTO_B200_B_DN. s_row has m floats, s_col n floats (device memory).
+ */
+int pto_b200_gemm_s8_dequant(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1,
+                             const float* s_row, const float* s_col, int m, int n, int k, long long lda,
+                             long long ldb, long long ldc);
+
+/*
+ * MX block-scaled fp8 GEMM: C[i][j] = sum_k A[i][k] * B[k][j] * 2^(SA[i][k/32]-127) * 2^(SB[j][k/32]-127).
+ * Replaces: RunMxMatmul / LaunchMxMatmul (uint8_t* out, src0, src1, src2, src3, void* stream),
+ * kernels/manual/a5/matmul_mxfp8_performance/mxmatmul_performance_kernel.cpp:284-380; arithmetic
+ * TMATMUL_MX, include/pto/cpu/TMatmul.hpp:169-205.
+ *   src2 : e8m0 scales of A, M x K/32 row-major (Layout::MX_A_ND), leading dimension ld_sfa bytes
+ *   src3 : e8m0 scales of B, N x K/32 row-major (Layout::MX_B_DN), leading dimension ld_sfb bytes
+ *   a_dtype / b_dtype : E4M3 or E5M2 (any mix); out_dtype BF16 or F32; B is PTO_B200_B_DN; k % 32 == 0.
+ *   workspace : device scratch of at least pto_b200_gemm_mx_workspace_bytes(m, n, k) bytes, 16-byte aligned;
+ *               the scales are re-tiled into it by a small kernel on the same stream before the GEMM.
+ * Scale byte 0xFF (NaN in the e8m0 encoding) is outside the supported input domain.
+ */
+int pto_b200_gemm_mx(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, const uint8_t* src2,
+                     const uint8_t* src3, uint8_t* workspace, size_t workspace_bytes, int m, int n, int k,
+                     long long lda, long long ldb, long long ldc, long long ld_sfa, long long ld_sfb, int a_dtype,
+                     int b_dtype, int out_dtype);
+
+size_t pto_b200_gemm_mx_workspace_bytes(int m, int n, int k);
+
+/*
+ * fp32 -> bf16 cast (round to nearest even) of `count` contiguous elements: the TSTORE cast applied to the
+ * reduced K-split partials (gemm_ar: reduced_output -> fp16/bf16 result, kernels/manual/a2a3/gemm_ar/README.md:33-46).
+ */
+int pto_b200_cast_f32_to_bf16(void* stream, uint8_t* out, const uint8_t* in, long long count);
+
+/*
+ * Fixed-shape launchers with the reference's exact signatures.
+ * call_kernel: demos/torch_jit/gemm/gemm_kernel.cpp:263-266 (fp16 6144^3, B column-major, fp32 out; blockDim ignored).
+ */
+void call_kernel(uint32_t blockDim, void* stream, uint8_t* out, uint8_t* src0, uint8_t* src1);
+
+/*
+ * Synchronises the current device and returns the kernel status word in *status (0 = every bounded wait
+ * completed; non-zero = the first wait that gave up) and clears it. Returns PTO_B200_ETIMEOUT if non-zero.
+ */
+int pto_b200_device_status(int* status);
+
+const char* pto_b200_error_string(int code);
+/* Text of the last CUDA error seen by the calling thread inside this library ("" if none). */
+const char* pto_b200_last_cuda_error(void);
+/* Kernels launched by this library since it was loaded (all threads). */
+unsigned long long pto_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PTO_B200_H */

@@ -1,0 +1,504 @@
+// C ABI over the sm_100a GEMM tile loop: argument validation, TMA descriptor construction, variant
+// selection and launch. No device memory is allocated here and no call synchronises unless it says so.
+#include "../../include/pto_b200.h"
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "gemm_tile_loop.cuh"
+
+#if !defined(__CUDA_ARCH_LIST__)
+#error "pto_b200 is built with nvcc for sm_100a only"
+#endif
+
+namespace pto_b200 {
+namespace {
+
+__device__ int g_status_word = 0;
+
+thread_local char t_cuda_error[256] = "";
+std::atomic<unsigned long long> g_launches{0};
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct DeviceInfo {
+    bool ready = false;
+    int err = PTO_B200_OK;
+    int sm_count = 0;
+    int* status_ptr = nullptr;
+};
+
+constexpr int kMaxDevices = 64;
+std::mutex g_mutex;
+DeviceInfo g_devices[kMaxDevices];
+EncodeTiledFn g_encode = nullptr;
+
+int note_cuda(cudaError_t e, const char* what)
+{
+    if (e == cudaSuccess) {
+        return PTO_B200_OK;
+    }
+    std::snprintf(t_cuda_error, sizeof(t_cuda_error), "%s: %s", what, cudaGetErrorString(e));
+    return PTO_B200_ECUDA;
+}
+
+// One-time set-up per device (capability check, SM count, status word address, driver entry point).
+int device_info(DeviceInfo** out)
+{
+    int dev = 0;
+    if (int rc = note_cuda(cudaGetDevice(&dev), "cudaGetDevice")) {
+        return rc;
+    }
+    if (dev < 0 || dev >= kMaxDevices) {
+        return PTO_B200_EDEVICE;
+    }
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceInfo& d = g_devices[dev];
+    if (!d.ready) {
+        int major = 0, minor = 0;
+        cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev);
+        if (major != 10 || minor != 0) {
+            d.err = PTO_B200_EDEVICE;
+        } else {
+            cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+            d.err = note_cuda(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status_ptr), g_status_word),
+                              "cudaGetSymbolAddress(status)");
+            if (d.err == PTO_B200_OK && g_encode == nullptr) {
+                void* fn = nullptr;
+                cudaDriverEntryPointQueryResult qres;
+                cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+                if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || fn == nullptr) {
+                    std::snprintf(t_cuda_error, sizeof(t_cuda_error), "cuTensorMapEncodeTiled entry point not found");
+                    d.err = PTO_B200_ECUDA;
+                } else {
+                    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+                }
+            }
+        }
+        d.ready = true;
+    }
+    *out = &d;
+    return d.err;
+}
+
+int elem_size(int dtype)
+{
+    switch (dtype) {
+        case PTO_B200_F16:
+        case PTO_B200_BF16:
+            return 2;
+        case PTO_B200_F32:
+        case PTO_B200_S32:
+            return 4;
+        case PTO_B200_S8:
+        case PTO_B200_E4M3:
+        case PTO_B200_E5M2:
+            return 1;
+        default:
+            return 0;
+    }
+}
+
+// 2-D row-major view [rows, cols] with leading dimension ld (elements), 128-byte swizzled boxes.
+int make_tensor_map(CUtensorMap* map, int dtype, const void* base, long long rows, long long cols, long long ld,
+                    int box_cols, int box_rows)
+{
+    CUtensorMapDataType dt;
+    switch (dtype) {
+        case PTO_B200_F16:
+            dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+            break;
+        case PTO_B200_BF16:
+            dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+            break;
+        default:
+            dt = CU_TENSOR_MAP_DATA_TYPE_UINT8;
+            break;
+    }
+    const int es = elem_size(dtype);
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * es};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        std::snprintf(t_cuda_error, sizeof(t_cuda_error), "cuTensorMapEncodeTiled failed with CUresult %d",
+                      static_cast<int>(r));
+        return PTO_B200_ECUDA;
+    }
+    return PTO_B200_OK;
+}
+
+// tcgen05 instruction descriptor (dense kinds): D format [4,6), A format [7,10), B format [10,13),
+// A/B major bits 15/16 (0 = K-major), N >> 3 at [17,23), M >> 4 at [24,29).
+uint32_t make_idesc(int c_fmt, int a_fmt, int b_fmt, bool b_mn_major, int n, bool block_scaled_e8m0)
+{
+    uint32_t d = 0;
+    if (!block_scaled_e8m0) {
+        d |= static_cast<uint32_t>(c_fmt) << 4;
+    }
+    d |= static_cast<uint32_t>(a_fmt) << 7;
+    d |= static_cast<uint32_t>(b_fmt) << 10;
+    d |= (b_mn_major ? 1u : 0u) << 16;
+    d |= static_cast<uint32_t>(n >> 3) << 17;
+    if (block_scaled_e8m0) {
+        d |= 1u << 23; // scale format e8m0
+    }
+    d |= static_cast<uint32_t>(kBlockM >> 4) << 24;
+    return d;
+}
+
+template <int KIND, int BLOCK_N, int EPI, bool B_MN>
+int launch_variant(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                   int sm_count)
+{
+    constexpr int STAGES = 4;
+    using L = SmemLayout<KIND, BLOCK_N, STAGES>;
+    auto kernel = gemm_tile_loop<KIND, BLOCK_N, STAGES, EPI, B_MN>;
+    static std::atomic<int> attr_done[kMaxDevices];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_done[dev].load(std::memory_order_acquire) == 0) {
+        if (int rc = note_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal),
+                               "cudaFuncSetAttribute")) {
+            return rc;
+        }
+        attr_done[dev].store(1, std::memory_order_release);
+    }
+    const int tiles = p.m_tiles * p.n_tiles;
+    const int grid = tiles < sm_count ? tiles : sm_count;
+    kernel<<<grid, kNumThreads, L::kTotal, stream>>>(ta, tb, p);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return note_cuda(cudaGetLastError(), "gemm_tile_loop launch");
+}
+
+template <int KIND, int EPI, bool B_MN>
+int launch_block_n(int block_n, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb,
+                   const GemmParams& p, int sm_count)
+{
+    if (block_n == 128) {
+        return launch_variant<KIND, 128, EPI, B_MN>(stream, ta, tb, p, sm_count);
+    }
+    return launch_variant<KIND, 256, EPI, B_MN>(stream, ta, tb, p, sm_count);
+}
+
+// 128-wide tiles when 256-wide ones would leave SMs without work and the narrower split fills more of them.
+int pick_block_n(int m, int n, int sm_count)
+{
+    const int m_tiles = (m + kBlockM - 1) / kBlockM;
+    const int t256 = m_tiles * ((n + 255) / 256);
+    if (n <= 128) {
+        return 128;
+    }
+    return (t256 < sm_count) ? 128 : 256;
+}
+
+struct Problem {
+    int m, n, k;
+    long long lda, ldb, ldc;
+};
+
+int check_common(const void* out, const void* a, const void* b, const Problem& q, int a_es, int b_es, bool b_nd)
+{
+    if (out == nullptr || a == nullptr || b == nullptr || q.m <= 0 || q.n <= 0 || q.k <= 0) {
+        return PTO_B200_EINVAL;
+    }
+    if (q.lda < q.k || q.ldc < q.n || q.ldb < (b_nd ? q.n : q.k)) {
+        return PTO_B200_EINVAL;
+    }
+    if ((reinterpret_cast<uintptr_t>(a) & 15u) || (reinterpret_cast<uintptr_t>(b) & 15u) || ((q.lda * a_es) & 15) ||
+        ((q.ldb * b_es) & 15)) {
+        return PTO_B200_EALIGN;
+    }
+    return PTO_B200_OK;
+}
+
+void fill_params(GemmParams& p, void* out, const Problem& q, int block_n, int k_elems_per_block, int* status)
+{
+    std::memset(&p, 0, sizeof(p));
+    p.c = out;
+    p.ldc = q.ldc;
+    p.m = q.m;
+    p.n = q.n;
+    p.k = q.k;
+    p.m_tiles = (q.m + kBlockM - 1) / kBlockM;
+    p.n_tiles = (q.n + block_n - 1) / block_n;
+    p.k_blocks = (q.k + k_elems_per_block - 1) / k_elems_per_block;
+    p.group_m = 16;
+    p.status = status;
+}
+
+} // namespace
+} // namespace pto_b200
+
+using namespace pto_b200;
+
+extern "C" int pto_b200_gemm(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, int m, int n, int k,
+                             long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype, int b_layout)
+{
+    const bool is16 = (in_dtype == PTO_B200_F16 || in_dtype == PTO_B200_BF16);
+    const bool is8 = (in_dtype == PTO_B200_S8);
+    if (!is16 && !is8) {
+        return PTO_B200_EDTYPE;
+    }
+    if (b_layout != PTO_B200_B_DN && b_layout != PTO_B200_B_ND) {
+        return PTO_B200_EDTYPE;
+    }
+    const bool b_nd = (b_layout == PTO_B200_B_ND);
+    if (is16 && !(out_dtype == PTO_B200_F32 || out_dtype == PTO_B200_BF16 || out_dtype == PTO_B200_F16)) {
+        return PTO_B200_EDTYPE;
+    }
+    if (is8 && (out_dtype != PTO_B200_S32 || b_nd)) {
+        return PTO_B200_EDTYPE;
+    }
+    const Problem q{m, n, k, lda, ldb, ldc};
+    const int es = elem_size(in_dtype);
+    if (int rc = check_common(out, src0, src1, q, es, es, b_nd)) {
+        return rc;
+    }
+    DeviceInfo* dev = nullptr;
+    if (int rc = device_info(&dev)) {
+        return rc;
+    }
+    const int block_n = pick_block_n(m, n, dev->sm_count);
+    const int kelems = kBlockKBytes / es;
+    GemmParams p;
+    fill_params(p, out, q, block_n, kelems, dev->status_ptr);
+    CUtensorMap ta, tb;
+    if (int rc = make_tensor_map(&ta, in_dtype, src0, m, k, lda, kelems, kBlockM)) {
+        return rc;
+    }
+    if (b_nd) {
+        if (int rc = make_tensor_map(&tb, in_dtype, src1, k, n, ldb, 64, 64)) {
+            return rc;
+        }
+    } else {
+        if (int rc = make_tensor_map(&tb, in_dtype, src1, n, k, ldb, kelems, block_n)) {
+            return rc;
+        }
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (is8) {
+        p.idesc = make_idesc(2 /*S32*/, 1 /*S8*/, 1 /*S8*/, false, block_n, false);
+        return launch_block_n<KIND_I8, EPI_S32, false>(block_n, s, ta, tb, p, dev->sm_count);
+    }
+    const int fmt = (in_dtype == PTO_B200_BF16) ? 1 : 0;
+    p.idesc = make_idesc(1 /*F32*/, fmt, fmt, b_nd, block_n, false);
+    if (b_nd) {
+        switch (out_dtype) {
+            case PTO_B200_F32:
+                return launch_block_n<KIND_F16, EPI_F32, true>(block_n, s, ta, tb, p, dev->sm_count);
+            case PTO_B200_BF16:
+                return launch_block_n<KIND_F16, EPI_BF16, true>(block_n, s, ta, tb, p, dev->sm_count);
+            default:
+                return launch_block_n<KIND_F16, EPI_F16, true>(block_n, s, ta, tb, p, dev->sm_count);
+        }
+    }
+    switch (out_dtype) {
+        case PTO_B200_F32:
+            return launch_block_n<KIND_F16, EPI_F32, false>(block_n, s, ta, tb, p, dev->sm_count);
+        case PTO_B200_BF16:
+            return launch_block_n<KIND_F16, EPI_BF16, false>(block_n, s, ta, tb, p, dev->sm_count);
+        default:
+            return launch_block_n<KIND_F16, EPI_F16, false>(block_n, s, ta, tb, p, dev->sm_count);
+    }
+}
+
+extern "C" int pto_b200_gemm_s8_dequant(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1,
+                                        const float* s_row, const float* s_col, int m, int n, int k, long long lda,
+                                        long long ldb, long long ldc)
+{
+    if (s_row == nullptr || s_col == nullptr) {
+        return PTO_B200_EINVAL;
+    }
+    const Problem q{m, n, k, lda, ldb, ldc};
+    if (int rc = check_common(out, src0, src1, q, 1, 1, false)) {
+        return rc;
+    }
+    DeviceInfo* dev = nullptr;
+    if (int rc = device_info(&dev)) {
+        return rc;
+    }
+    const int block_n = pick_block_n(m, n, dev->sm_count);
+    GemmParams p;
+    fill_params(p, out, q, block_n, kBlockKBytes, dev->status_ptr);
+    p.s_row = s_row;
+    p.s_col = s_col;
+    p.idesc = make_idesc(2, 1, 1, false, block_n, false);
+    CUtensorMap ta, tb;
+    if (int rc = make_tensor_map(&ta, PTO_B200_S8, src0, m, k, lda, kBlockKBytes, kBlockM)) {
+        return rc;
+    }
+    if (int rc = make_tensor_map(&tb, PTO_B200_S8, src1, n, k, ldb, kBlockKBytes, block_n)) {
+        return rc;
+    }
+    return launch_block_n<KIND_I8, EPI_DEQ_BF16, false>(block_n, static_cast<cudaStream_t>(stream), ta, tb, p,
+                                                        dev->sm_count);
+}
+
+extern "C" size_t pto_b200_gemm_mx_workspace_bytes(int m, int n, int k)
+{
+    if (m <= 0 || n <= 0 || k <= 0) {
+        return 0;
+    }
+    const size_t m_tiles = (static_cast<size_t>(m) + kBlockM - 1) / kBlockM;
+    const size_t n_blocks = 2 * ((static_cast<size_t>(n) + 255) / 256);
+    const size_t k_blocks = (static_cast<size_t>(k) + kBlockKBytes - 1) / kBlockKBytes;
+    return k_blocks * (m_tiles + n_blocks) * 512;
+}
+
+extern "C" int pto_b200_gemm_mx(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1,
+                                const uint8_t* src2, const uint8_t* src3, uint8_t* workspace, size_t workspace_bytes,
+                                int m, int n, int k, long long lda, long long ldb, long long ldc, long long ld_sfa,
+                                long long ld_sfb, int a_dtype, int b_dtype, int out_dtype)
+{
+    const bool a_ok = (a_dtype == PTO_B200_E4M3 || a_dtype == PTO_B200_E5M2);
+    const bool b_ok = (b_dtype == PTO_B200_E4M3 || b_dtype == PTO_B200_E5M2);
+    if (!a_ok || !b_ok || !(out_dtype == PTO_B200_BF16 || out_dtype == PTO_B200_F32)) {
+        return PTO_B200_EDTYPE;
+    }
+    if (src2 == nullptr || src3 == nullptr) {
+        return PTO_B200_EINVAL;
+    }
+    const Problem q{m, n, k, lda, ldb, ldc};
+    if (int rc = check_common(out, src0, src1, q, 1, 1, false)) {
+        return rc;
+    }
+    if (k % 32 != 0 || ld_sfa < k / 32 || ld_sfb < k / 32) {
+        return PTO_B200_EINVAL;
+    }
+    if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 15u) ||
+        workspace_bytes < pto_b200_gemm_mx_workspace_bytes(m, n, k)) {
+        return PTO_B200_EWORKSPACE;
+    }
+    DeviceInfo* dev = nullptr;
+    if (int rc = device_info(&dev)) {
+        return rc;
+    }
+    const int block_n = pick_block_n(m, n, dev->sm_count);
+    GemmParams p;
+    fill_params(p, out, q, block_n, kBlockKBytes, dev->status_ptr);
+    const int n_blocks = p.n_tiles * (block_n / 128);
+    uint8_t* sfa_ws = workspace;
+    uint8_t* sfb_ws = workspace + static_cast<size_t>(p.k_blocks) * p.m_tiles * 512;
+    p.sfa = sfa_ws;
+    p.sfb = sfb_ws;
+    p.idesc = make_idesc(0, a_dtype == PTO_B200_E5M2 ? 1 : 0, b_dtype == PTO_B200_E5M2 ? 1 : 0, false, block_n, true);
+    CUtensorMap ta, tb;
+    if (int rc = make_tensor_map(&ta, a_dtype, src0, m, k, lda, kBlockKBytes, kBlockM)) {
+        return rc;
+    }
+    if (int rc = make_tensor_map(&tb, b_dtype, src1, n, k, ldb, kBlockKBytes, block_n)) {
+        return rc;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    {
+        const long long ta_items = static_cast<long long>(p.m_tiles) * p.k_blocks * 128;
+        const long long tb_items = static_cast<long long>(n_blocks) * p.k_blocks * 128;
+        const int ga = static_cast<int>((ta_items + 255) / 256 < 4096 ? (ta_items + 255) / 256 : 4096);
+        const int gb = static_cast<int>((tb_items + 255) / 256 < 4096 ? (tb_items + 255) / 256 : 4096);
+        retile_scales_kernel<<<ga, 256, 0, s>>>(src2, sfa_ws, m, k / 32, ld_sfa, p.m_tiles, p.k_blocks);
+        retile_scales_kernel<<<gb, 256, 0, s>>>(src3, sfb_ws, n, k / 32, ld_sfb, n_blocks, p.k_blocks);
+        g_launches.fetch_add(2, std::memory_order_relaxed);
+        if (int rc = note_cuda(cudaGetLastError(), "retile_scales launch")) {
+            return rc;
+        }
+    }
+    if (out_dtype == PTO_B200_F32) {
+        return launch_block_n<KIND_MXF8, EPI_F32, false>(block_n, s, ta, tb, p, dev->sm_count);
+    }
+    return launch_block_n<KIND_MXF8, EPI_BF16, false>(block_n, s, ta, tb, p, dev->sm_count);
+}
+
+extern "C" int pto_b200_cast_f32_to_bf16(void* stream, uint8_t* out, const uint8_t* in, long long count)
+{
+    if (out == nullptr || in == nullptr || count < 0) {
+        return PTO_B200_EINVAL;
+    }
+    if ((reinterpret_cast<uintptr_t>(in) & 15u) || (reinterpret_cast<uintptr_t>(out) & 7u)) {
+        return PTO_B200_EALIGN;
+    }
+    if (count == 0) {
+        return PTO_B200_OK;
+    }
+    DeviceInfo* dev = nullptr;
+    if (int rc = device_info(&dev)) {
+        return rc;
+    }
+    const long long want = (count / 4 + 255) / 256 + 1;
+    const long long cap = static_cast<long long>(dev->sm_count) * 16;
+    const int grid = static_cast<int>(want < cap ? want : cap);
+    cast_f32_bf16_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float*>(in), reinterpret_cast<__nv_bfloat16*>(out), count);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return note_cuda(cudaGetLastError(), "cast_f32_bf16 launch");
+}
+
+extern "C" void call_kernel(uint32_t blockDim, void* stream, uint8_t* out, uint8_t* src0, uint8_t* src1)
+{
+    (void)blockDim;
+    constexpr int kDim = 6144;
+    (void)pto_b200_gemm(stream, out, src0, src1, kDim, kDim, kDim, kDim, kDim, kDim, PTO_B200_F16, PTO_B200_F32,
+                        PTO_B200_B_DN);
+}
+
+extern "C" int pto_b200_device_status(int* status)
+{
+    DeviceInfo* dev = nullptr;
+    if (int rc = device_info(&dev)) {
+        return rc;
+    }
+    if (int rc = note_cuda(cudaDeviceSynchronize(), "cudaDeviceSynchronize")) {
+        return rc;
+    }
+    int host = 0;
+    if (int rc = note_cuda(cudaMemcpy(&host, dev->status_ptr, sizeof(int), cudaMemcpyDeviceToHost), "status read")) {
+        return rc;
+    }
+    if (host != 0) {
+        const int zero = 0;
+        cudaMemcpy(dev->status_ptr, &zero, sizeof(int), cudaMemcpyHostToDevice);
+    }
+    if (status != nullptr) {
+        *status = host;
+    }
+    return host == 0 ? PTO_B200_OK : PTO_B200_ETIMEOUT;
+}
+
+extern "C" const char* pto_b200_error_string(int code)
+{
+    switch (code) {
+        case PTO_B200_OK:
+            return "ok";
+        case PTO_B200_EINVAL:
+            return "invalid argument (null pointer, non-positive size or leading dimension too small)";
+        case PTO_B200_EALIGN:
+            return "A/B base address or leading dimension is not a multiple of 16 bytes";
+        case PTO_B200_EDTYPE:
+            return "unsupported dtype / layout combination";
+        case PTO_B200_EWORKSPACE:
+            return "workspace missing, misaligned or too small";
+        case PTO_B200_ECUDA:
+            return "CUDA call failed";
+        case PTO_B200_EDEVICE:
+            return "current device is not an sm_100 GPU";
+        case PTO_B200_ETIMEOUT:
+            return "a kernel gave up on a bounded wait";
+        default:
+            return "unknown error code";
+    }
+}
+
+extern "C" const char* pto_b200_last_cuda_error(void) { return t_cuda_error; }
+
+extern "C" unsigned long long pto_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -1,0 +1,170 @@
+"""Host-side GEMM entry points over the C ABI, taking torch CUDA tensors as device buffers.
+
+These mirror how the reference's upper layers call its GEMM: a torch op that checks dtype / shape /
+contiguity and launches on the current stream (demos/baseline/gemm_basic/csrc/host/my_gemm_basic.cpp:22-48)
+and ctypes launchers that pass raw device pointers (demos/torch_jit/gemm/jit_util_gemm.py:61-93).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import _capi
+from ._capi import B_DN, B_ND, BF16, E4M3, E5M2, F16, F32, S8, S32
+
+_TORCH_TO_PTO = {
+    torch.float16: F16,
+    torch.bfloat16: BF16,
+    torch.float32: F32,
+    torch.int8: S8,
+    torch.int32: S32,
+}
+_PTO_TO_TORCH = {v: k for k, v in _TORCH_TO_PTO.items()}
+if hasattr(torch, "float8_e4m3fn"):
+    _TORCH_TO_PTO[torch.float8_e4m3fn] = E4M3
+    _TORCH_TO_PTO[torch.float8_e5m2] = E5M2
+
+
+def _stream_ptr(stream: Optional[torch.cuda.Stream]) -> int:
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return s.cuda_stream
+
+
+def _require_cuda_2d(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if t.dim() != 2:
+        raise ValueError(f"{name} must be 2-D")
+    if t.stride(1) != 1:
+        raise ValueError(f"{name} must have unit stride in its last dimension")
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype = torch.float32, b_layout: int = B_DN,
+         out: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """C = A @ B with fp32 (int32 for int8 inputs) accumulation over the whole K.
+
+    a: [M, K] row-major (row stride >= K). b: [N, K] when ``b_layout == B_DN`` (column-major K x N, the
+    layout of gemm_performance) or [K, N] when ``B_ND`` (the CPU demo's layout). Strided views are allowed,
+    which is how a K-split rank passes its slice (A[:, k0:k1], B_dn[:, k0:k1]).
+    """
+    lib = _capi.load()
+    _require_cuda_2d(a, "a")
+    _require_cuda_2d(b, "b")
+    if a.dtype != b.dtype or a.dtype not in (torch.float16, torch.bfloat16, torch.int8):
+        raise ValueError("a and b must both be float16, bfloat16 or int8")
+    m, k = a.shape
+    if b_layout == B_DN:
+        n, kb = b.shape
+    else:
+        kb, n = b.shape
+    if kb != k:
+        raise ValueError(f"inner dimensions differ: a is {tuple(a.shape)}, b is {tuple(b.shape)}")
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    else:
+        _require_cuda_2d(out, "out")
+        if tuple(out.shape) != (m, n):
+            raise ValueError("out has the wrong shape")
+        out_dtype = out.dtype
+    rc = lib.pto_b200_gemm(_stream_ptr(stream), out.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, a.stride(0),
+                           b.stride(0), out.stride(0), _TORCH_TO_PTO[a.dtype], _TORCH_TO_PTO[out_dtype], b_layout)
+    _capi.check(rc, "pto_b200_gemm")
+    return out
+
+
+def gemm_s8_dequant(a: torch.Tensor, b_dn: torch.Tensor, s_row: torch.Tensor, s_col: torch.Tensor,
+                    out: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """bf16((float(int32 acc) * s_col[j]) * s_row[i]) for int8 a [M, K] and b_dn [N, K]."""
+    lib = _capi.load()
+    _require_cuda_2d(a, "a")
+    _require_cuda_2d(b_dn, "b_dn")
+    if a.dtype != torch.int8 or b_dn.dtype != torch.int8:
+        raise ValueError("a and b_dn must be int8")
+    m, k = a.shape
+    n, kb = b_dn.shape
+    if kb != k:
+        raise ValueError("inner dimensions differ")
+    for s, cnt, name in ((s_row, m, "s_row"), (s_col, n, "s_col")):
+        if s.dtype != torch.float32 or not s.is_cuda or s.numel() != cnt or not s.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous CUDA float32 tensor with {cnt} elements")
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+    rc = lib.pto_b200_gemm_s8_dequant(_stream_ptr(stream), out.data_ptr(), a.data_ptr(), b_dn.data_ptr(),
+                                      s_row.data_ptr(), s_col.data_ptr(), m, n, k, a.stride(0), b_dn.stride(0),
+                                      out.stride(0))
+    _capi.check(rc, "pto_b200_gemm_s8_dequant")
+    return out
+
+
+def gemm_mx_workspace_bytes(m: int, n: int, k: int) -> int:
+    return int(_capi.load().pto_b200_gemm_mx_workspace_bytes(m, n, k))
+
+
+def gemm_mx(a: torch.Tensor, b_dn: torch.Tensor, sfa: torch.Tensor, sfb: torch.Tensor,
+            out_dtype: torch.dtype = torch.bfloat16, a_fmt: int = E4M3, b_fmt: int = E4M3,
+            workspace: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+            stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """MX block-scaled fp8 GEMM (TMATMUL_MX): a [M, K] and b_dn [N, K] fp8 bytes (uint8 or torch fp8 dtypes),
+    sfa [M, K/32] and sfb [N, K/32] e8m0 bytes (uint8). ``workspace`` is a uint8 CUDA tensor of at least
+    ``gemm_mx_workspace_bytes(m, n, k)`` bytes; one is allocated through torch when omitted."""
+    lib = _capi.load()
+    for t, name in ((a, "a"), (b_dn, "b_dn"), (sfa, "sfa"), (sfb, "sfb")):
+        _require_cuda_2d(t, name)
+        if t.element_size() != 1:
+            raise ValueError(f"{name} must have one-byte elements")
+    m, k = a.shape
+    n, kb = b_dn.shape
+    if kb != k:
+        raise ValueError("inner dimensions differ")
+    if k % 32 != 0 or tuple(sfa.shape) != (m, k // 32) or tuple(sfb.shape) != (n, k // 32):
+        raise ValueError("scales must be [M, K/32] and [N, K/32] with K a multiple of 32")
+    need = gemm_mx_workspace_bytes(m, n, k)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    rc = lib.pto_b200_gemm_mx(_stream_ptr(stream), out.data_ptr(), a.data_ptr(), b_dn.data_ptr(), sfa.data_ptr(),
+                              sfb.data_ptr(), workspace.data_ptr(), workspace.numel(), m, n, k, a.stride(0),
+                              b_dn.stride(0), out.stride(0), sfa.stride(0), sfb.stride(0), a_fmt, b_fmt,
+                              _TORCH_TO_PTO[out.dtype])
+    _capi.check(rc, "pto_b200_gemm_mx")
+    return out
+
+
+def cast_f32_to_bf16(src: torch.Tensor, out: Optional[torch.Tensor] = None,
+                     stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    lib = _capi.load()
+    if src.dtype != torch.float32 or not src.is_cuda or not src.is_contiguous():
+        raise ValueError("src must be a contiguous CUDA float32 tensor")
+    if out is None:
+        out = torch.empty(src.shape, dtype=torch.bfloat16, device=src.device)
+    rc = lib.pto_b200_cast_f32_to_bf16(_stream_ptr(stream), out.data_ptr(), src.data_ptr(), src.numel())
+    _capi.check(rc, "pto_b200_cast_f32_to_bf16")
+    return out
+
+
+def pto_gemm_basic(a: torch.Tensor, b_dn: torch.Tensor) -> torch.Tensor:
+    """The torch op of demos/baseline/gemm_basic: fp16 a [M, K] x fp16 b_dn [N, K] (= b.t().contiguous())
+    -> fp32 [M, N], same argument checks, any shape instead of the reference's fixed 512 x 2048 x 1536."""
+    if a.dtype != torch.float16 or b_dn.dtype != torch.float16:
+        raise ValueError("a and b_dn must be float16")
+    if a.dim() != 2 or b_dn.dim() != 2:
+        raise ValueError("a and b_dn must be 2D tensors")
+    if not a.is_contiguous() or not b_dn.is_contiguous():
+        raise ValueError("a and b_dn must be contiguous")
+    return gemm(a, b_dn, torch.float32, B_DN)
+
+
+def device_status() -> int:
+    """Synchronise and return the kernels' status word (0 = no bounded wait gave up)."""
+    st = ctypes.c_int(0)
+    rc = _capi.load().pto_b200_device_status(ctypes.byref(st))
+    if rc not in (_capi.OK, _capi.ETIMEOUT):
+        _capi.check(rc, "pto_b200_device_status")
+    return st.value
+
+
+def launch_count() -> int:
+    return int(_capi.load().pto_b200_launch_count())
