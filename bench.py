@@ -1,0 +1,515 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 GEMM hot path:  python bench.py --gpus N --steps K --warmup W
+
+Prints ONE JSON line. Metric: GEMM TFLOP/s = 2*M*N*K / time / 1e12 (the reference's definition,
+docs/figures/performance/gemm_performance_a3.svg:9). Workloads (synthetic, seeded):
+
+  N = 1 : dense bf16 GEMM M=N=K=4096, A row-major, B column-major, fp32 accumulate, bf16 output
+          (other single-GPU configurations are timed briefly and reported under "all_configs").
+  N > 1 : K-split GEMM + allreduce, bf16 A[8192 x 65536] x B[65536 x 8192], K partitioned over the ranks,
+          fp32 partials reduced over NCCL, bf16 result on every rank (strong scaling: total work is fixed).
+
+`--impl reference` times the reference's own CPU simulator (oracle/_ref, built from the reference's headers)
+on the host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 1024 * 1024
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
+# summarised under profiles/ (None = not captured for that workload).
+NCU_DRAM_TRAFFIC = {
+    "bf16_4096": None,
+}
+
+WORKLOADS = {
+    "c1_f16_128x256x256": dict(kind="dense", m=128, n=256, k=256, dtype="f16", out="f32"),
+    "bf16_4096": dict(kind="dense", m=4096, n=4096, k=4096, dtype="bf16", out="bf16"),
+    "s8_8192_dequant": dict(kind="s8", m=8192, n=8192, k=8192),
+    "mxfp8_16384x8192x8192": dict(kind="mx", m=16384, n=8192, k=8192),
+    "ksplit_bf16_8192x65536x8192": dict(kind="ksplit", m=8192, n=8192, k=65536),
+}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        p["_source"] = "measured"
+        return p
+    p = dict(FALLBACK_PEAKS)
+    p["_source"] = "fallback"
+    return p
+
+
+# --------------------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """Polls NVML for the SM clock and the clock-event reasons of one GPU while a timed region runs."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            uuid = None
+            try:
+                import torch
+
+                uuid = str(torch.cuda.get_device_properties(index).uuid)
+            except Exception:  # noqa: BLE001
+                uuid = None
+            self.h = None
+            if uuid:
+                for i in range(pynvml.nvmlDeviceGetCount()):
+                    h = pynvml.nvmlDeviceGetHandleByIndex(i)
+                    u = pynvml.nvmlDeviceGetUUID(h)
+                    u = u.decode() if isinstance(u, bytes) else u
+                    if uuid in u:
+                        self.h = h
+            if self.h is None:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:  # noqa: BLE001
+            self.nv = None
+
+    def _poll(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:  # noqa: BLE001
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._poll, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+# --------------------------------------------------------------------------------------- inputs (on the device)
+
+def _randn_scaled(shape, k, dtype, gen, dev):
+    import torch
+
+    return (torch.randn(shape, generator=gen, device=dev, dtype=torch.float32) / (k ** 0.5)).to(dtype)
+
+
+def mx_quantize_torch(x):
+    """OCP MX quantisation along K in blocks of 32 (include/pto/cpu/TQuant.hpp:178-190,226-237,461-494), as data
+    preparation on the device: e8m0 = max(biased_exp(absmax) - 8, 0), element = e4m3fn(x * 2^(127 - e8m0))."""
+    import torch
+
+    rows, k = x.shape
+    g = x.view(rows, k // 32, 32)
+    amax = g.abs().amax(dim=-1)
+    exp = (amax.view(torch.int32) >> 23) & 0xFF
+    e8m0 = torch.clamp(exp - 8, min=0)
+    scaling = ((254 - e8m0) << 23).view(torch.float32)
+    y = (g * scaling.unsqueeze(-1)).clamp(-448.0, 448.0)
+    return y.to(torch.float8_e4m3fn).view(torch.uint8).view(rows, k), e8m0.to(torch.uint8)
+
+
+def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=4, mode="rs_ag"):
+    """Returns (step_fn, flops_per_step, working_set_bytes, launches_hint). step_fn(i) enqueues one pass."""
+    import torch
+
+    import pto_isa_mirror_b200 as pto
+
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    m, n, k = spec["m"], spec["n"], spec["k"]
+    kind = spec["kind"]
+    flops = 2.0 * m * n * k
+    if kind == "dense":
+        dt = torch.bfloat16 if spec["dtype"] == "bf16" else torch.float16
+        odt = {"bf16": torch.bfloat16, "f32": torch.float32, "f16": torch.float16}[spec["out"]]
+        per_set = (m * k + n * k) * 2 + m * n * (4 if odt == torch.float32 else 2)
+        sets = max(2, -(-3 * L2_BYTES // per_set)) if per_set < 3 * L2_BYTES else 1
+        sets = min(sets, 64)
+        bufs = [(_randn_scaled((m, k), k, dt, gen, dev), _randn_scaled((n, k), k, dt, gen, dev),
+                 torch.empty((m, n), dtype=odt, device=dev)) for _ in range(sets)]
+
+        def step(i):
+            a, b, c = bufs[i % sets]
+            pto.gemm(a, b, out=c)
+
+        return step, flops, per_set * sets, sets
+    if kind == "s8":
+        per_set = 2 * m * k + m * n * 2
+        sets = 2
+        bufs = []
+        for _ in range(sets):
+            a = torch.randint(-127, 128, (m, k), generator=gen, device=dev, dtype=torch.int8)
+            b = torch.randint(-127, 128, (n, k), generator=gen, device=dev, dtype=torch.int8)
+            s_row = torch.rand(m, generator=gen, device=dev) * 9e-3 + 1e-3
+            s_col = ((torch.rand(n, generator=gen, device=dev) * 9e-3 + 1e-3).view(torch.int32) & ~0x1FFF).view(
+                torch.float32)
+            bufs.append((a, b, s_row, s_col, torch.empty((m, n), dtype=torch.bfloat16, device=dev)))
+
+        def step(i):
+            a, b, sr, sc, c = bufs[i % sets]
+            pto.gemm_s8_dequant(a, b, sr, sc, out=c)
+
+        return step, flops, per_set * sets, sets
+    if kind == "mx":
+        a, sfa = mx_quantize_torch(torch.randn((m, k), generator=gen, device=dev))
+        b, sfb = mx_quantize_torch(torch.randn((n, k), generator=gen, device=dev))
+        c = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        ws = torch.empty(pto.gemm_mx_workspace_bytes(m, n, k), dtype=torch.uint8, device=dev)
+
+        def step(i):
+            pto.gemm_mx(a, b, sfa, sfb, workspace=ws, out=c)
+
+        return step, flops, m * k + n * k + m * n * 2, 1
+    if kind == "ksplit":
+        from pto_isa_mirror_b200.ksplit import KSplitGemmAllReduce, k_slice
+
+        k0, k1 = k_slice(k, world, rank)
+        kr = k1 - k0
+        # every rank draws its own K slice of the operands (values N(0,1)/sqrt(K) as for the unsplit matrix)
+        gen.manual_seed(seed * 1000 + rank)
+        a = _randn_scaled((m, kr), k, torch.bfloat16, gen, dev)
+        b = _randn_scaled((n, kr), k, torch.bfloat16, gen, dev)
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+        op = KSplitGemmAllReduce(m, n, panels=panels if world > 1 else 1, mode=mode, device=dev)
+
+        def step(i):
+            op.step(a, b, out)
+
+        step.tensors = (a, b, out)
+        return step, flops, (m + n) * kr * 2 + m * n * 6, 1
+    raise ValueError(kind)
+
+
+# --------------------------------------------------------------------------------------- timing
+
+def time_steps(step, steps, warmup, dev, world):
+    import torch
+    import torch.distributed as dist
+
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(steps):
+        step(warmup + i)
+    end.record()
+    torch.cuda.synchronize(dev)
+    ms = start.elapsed_time(end)
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+# --------------------------------------------------------------------------------------- CPU baselines
+
+def cpu_tile_runner(kind: str, k: int, single_thread=False):
+    """A closure that runs ONE 128 x 256 x k output tile of the workload through the reference CPU simulator
+    (or, where it was never built, the C restatement), plus a description of what runs."""
+    import oracle
+    from pto_isa_mirror_b200 import gen_data as gd
+
+    use_ref = oracle.Ref.available(single_thread)
+    cores = 1 if single_thread else (os.cpu_count() or 1)
+    sim = oracle.Ref(single_thread) if use_ref else None
+    if kind == "s8":
+        a, b, _, _ = gd.s8_inputs(128, 256, k, 2)
+        run = (lambda: sim.tile_s8(a, b)) if use_ref else (lambda: oracle.gemm_s8(a, b, cores))
+    elif kind == "mx":
+        a, b, sfa, sfb = gd.mx_inputs(128, 256, k, 3)
+        run = (lambda: sim.tile_mx(a, b, sfa, sfb)) if use_ref else (
+            lambda: oracle.gemm_mx(a, b, sfa, sfb, threads=cores))
+    else:
+        a16, b16 = gd.dense_inputs(128, 256, k, "bf16", 1)
+        if use_ref:
+            af, bf = gd.bf16_bits_to_f32(a16), gd.bf16_bits_to_f32(b16)
+            run = lambda: sim.tile_f32(af, bf)  # noqa: E731
+        else:
+            run = lambda: oracle.gemm_f32acc(a16, b16, oracle.BF16, threads=cores)  # noqa: E731
+    what = ("RunGemmE2E / TMATMUL of the reference CPU simulator (oracle/_ref)" if use_ref
+            else "the C restatement (oracle/pto_gemm_oracle.c)")
+    return run, {"kind": "reference" if use_ref else "port", "cores": cores, "what": what}
+
+
+def cpu_reference_sample(kind: str, k: int, budget_s: float):
+    """Times output tiles of the workload on the host cores until `budget_s` has elapsed."""
+    run, info = cpu_tile_runner(kind, k)
+    flops = 2.0 * 128 * 256 * k
+    run()
+    n, t0 = 0, time.perf_counter()
+    while True:
+        run()
+        n += 1
+        el = time.perf_counter() - t0
+        if el >= budget_s:
+            break
+    return flops * n / el / 1e12, {
+        "kind": info["kind"], "cores": info["cores"],
+        "sample": f"{n} output tile(s) 128x256 with K={k} ({flops * n / 1e9:.2f} GFLOP) in {el:.1f} s through "
+                  + info["what"],
+    }
+
+
+def reference_arm(args, world, rank):
+    """`--impl reference`: the reference's CPU implementation on the host cores, bounded sample per step."""
+    if rank != 0:
+        return
+    name = args.workload or ("bf16_4096" if args.gpus == 1 else "ksplit_bf16_8192x65536x8192")
+    spec = WORKLOADS[name]
+    kind = spec["kind"]
+    import oracle
+
+    if not (oracle.Ref.available() or os.path.exists(oracle.ORACLE_LIB)):
+        oracle.build()
+    # one step = one 128 x 256 output tile over a K that keeps the whole run within a few minutes
+    full_k = spec["k"] if kind != "ksplit" else spec["k"] // max(args.gpus, 1)
+    sk = "dense" if kind == "ksplit" else kind
+    depths = (8192, 4096, 1024, 256) if sk == "dense" else (8192, 1024, 256)
+    candidates = [kk for kk in depths if kk <= full_k] or [256]
+    total_steps = args.steps + args.warmup
+    run, info, chosen = None, None, candidates[-1]
+    for kk in candidates:
+        run, info = cpu_tile_runner(sk, kk)
+        t0 = time.perf_counter()
+        run()
+        if (time.perf_counter() - t0) * total_steps <= 150.0 or kk == candidates[-1]:
+            chosen = kk
+            break
+    for _ in range(args.warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        run()
+    el = time.perf_counter() - t0
+    flops = 2.0 * 128 * 256 * chosen * args.steps
+    value = flops / el / 1e12
+    line = {
+        "impl": "reference", "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": el / max(args.steps, 1) * 1e3,
+        "higher_is_better": True, "scaling": "strong" if kind == "ksplit" else "weak", "vs_baseline": None,
+        "dtype": {"dense": "bf16", "ksplit": "bf16", "s8": "s8", "mx": "mxfp8_e4m3"}[kind], "data": "synthetic",
+        "config": {"workload": name, "m": spec["m"], "n": spec["n"], "k": spec["k"],
+                   "note": "reference CPU simulator on host cores; each step is one 128x256 output tile over "
+                           f"K={chosen} of this workload"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": info["cores"], "kind": info["kind"],
+                         "sample": f"{args.steps} steps, each one 128x256xK={chosen} output tile "
+                                   f"({2.0 * 128 * 256 * chosen / 1e9:.3f} GFLOP) through {info['what']}, "
+                                   "simulator default threading"},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------- main arm
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--panels", type=int, default=4)
+    ap.add_argument("--mode", default="rs_ag", choices=["rs_ag", "allreduce"])
+    ap.add_argument("--no-extras", action="store_true", help="skip all_configs / cpu_baseline / e2e (profiling runs)")
+    ap.add_argument("--cpu-budget", type=float, default=10.0)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        reference_arm(args, world, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import pto_isa_mirror_b200 as pto
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path (use --impl reference for the CPU arm)")
+    if args.gpus != world:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run --nproc-per-node N")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    name = args.workload or ("bf16_4096" if world == 1 else "ksplit_bf16_8192x65536x8192")
+    spec = WORKLOADS[name]
+    peaks = load_peaks()
+    step, flops, ws_bytes, sets = make_step(name, spec, dev, seed=1, world=world, rank=rank, panels=args.panels,
+                                            mode=args.mode)
+
+    launches0 = pto.launch_count()
+    with ClockSampler(local_rank) as clk:
+        ms = time_steps(step, args.steps, args.warmup, dev, world)
+    launches_total = pto.launch_count() - launches0
+    launches = launches_total * args.steps // (args.steps + args.warmup)
+    status = pto.device_status()
+    ms_per_step = ms / args.steps
+    tflops = flops / (ms_per_step * 1e-3) / 1e12
+
+    kind = spec["kind"]
+    dtype = {"dense": spec.get("dtype", "bf16"), "ksplit": "bf16", "s8": "s8", "mx": "mxfp8_e4m3"}[kind]
+    peak_scale = {"dense": 1.0, "ksplit": 1.0, "s8": 2.0, "mx": 2.0}[kind]
+    # a single kernel timed back to back for a short region: burst peak; the long K-split step: sustained
+    peak_key = "bf16_tflops" if ms < 500.0 else "bf16_tflops_sustained"
+    peak = float(peaks.get(peak_key, FALLBACK_PEAKS["bf16_tflops"])) * peak_scale
+    achieved = tflops / world
+    line = {
+        "metric": "gemm_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong" if kind == "ksplit" else "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+        "config": {"workload": name, "m": spec["m"], "n": spec["n"], "k": spec["k"],
+                   "layout": "A row-major, B column-major, fp32 accumulate",
+                   "l2": (f"rotating {sets} input/output sets, {ws_bytes / 2**20:.0f} MiB > 126 MiB L2"
+                          if sets > 1 else f"working set {ws_bytes / 2**20:.0f} MiB > 126 MiB L2"),
+                   "inputs": "seeded torch.randn on device, N(0,1)/sqrt(K)" if kind in ("dense", "ksplit") else "seeded",
+                   **({"parallelism": f"ksplit{world}", "panels": args.panels, "reduce": args.mode}
+                      if kind == "ksplit" else {})},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                     "frac": achieved / peak, "traffic": NCU_DRAM_TRAFFIC.get(name),
+                     "peak_source": f"{peaks['_source']}: {peak_key}" + (" x2 (8-bit kinds, nominal ratio)" if peak_scale > 1 else ""),
+                     "frac_of_sustained": achieved / (float(peaks.get("bf16_tflops_sustained", 1400.0)) * peak_scale),
+                     "per": "GPU"},
+        "clocks": clk.summary(),
+        "gpu_launches": int(launches),
+        "device_status": status,
+    }
+
+    if rank == 0 and world == 1 and not args.no_extras:
+        # end to end through the host-buffer API: H2D of A and B, one launch, D2H of C, every step
+        if kind == "dense":
+            from pto_isa_mirror_b200.host_api import HostGemm
+
+            idt = torch.bfloat16 if spec["dtype"] == "bf16" else torch.float16
+            odt = {"bf16": torch.bfloat16, "f32": torch.float32, "f16": torch.float16}[spec["out"]]
+            hg = HostGemm(spec["m"], spec["n"], spec["k"], idt, odt, dev)
+            h_a = torch.randn((spec["m"], spec["k"])).mul_(spec["k"] ** -0.5).to(idt).pin_memory()
+            h_b = torch.randn((spec["n"], spec["k"])).mul_(spec["k"] ** -0.5).to(idt).pin_memory()
+            for _ in range(3):
+                hg.run(h_a, h_b)
+            e2e_steps = max(3, min(args.steps, 20))
+            t0 = time.perf_counter()
+            for _ in range(e2e_steps):
+                hg.run(h_a, h_b)
+            el = time.perf_counter() - t0
+            line["e2e"] = {"value": flops * e2e_steps / el / 1e12, "unit": "TFLOP/s",
+                           "h2d_bytes_per_step": hg.h2d_bytes, "d2h_bytes_per_step": hg.d2h_bytes,
+                           "steps": e2e_steps, "timer": "host wall clock around HostGemm.run (stream-synchronised)"}
+        # the other single-GPU configurations, briefly
+        others = {}
+        for oname in ("c1_f16_128x256x256", "s8_8192_dequant", "mxfp8_16384x8192x8192", "ksplit_bf16_8192x65536x8192"):
+            if oname == name:
+                continue
+            try:
+                ostep, oflops, _, _ = make_step(oname, WORKLOADS[oname], dev, seed=2)
+                osteps = 20 if oname != "ksplit_bf16_8192x65536x8192" else 5
+                oms = time_steps(ostep, osteps, 3, dev, 1) / osteps
+                okind = WORKLOADS[oname]["kind"]
+                opeak = float(peaks.get("bf16_tflops", 1590.0)) * (2.0 if okind in ("s8", "mx") else 1.0)
+                others[oname] = {"tflops": oflops / (oms * 1e-3) / 1e12, "ms": oms,
+                                 "frac_of_peak": oflops / (oms * 1e-3) / 1e12 / opeak, "peak": opeak}
+                del ostep
+                torch.cuda.empty_cache()
+            except Exception as e:  # noqa: BLE001
+                others[oname] = {"error": repr(e)}
+        line["all_configs"] = others
+        try:
+            v, info = cpu_reference_sample("dense", spec["k"] if spec["k"] <= 8192 else 8192, args.cpu_budget)
+            line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", **info}
+        except Exception as e:  # noqa: BLE001
+            line["cpu_baseline"] = {"value": None, "unit": "TFLOP/s", "cores": 0, "kind": "port", "sample": repr(e)}
+    elif world > 1:
+        # end to end for the K-split step: H2D of this rank's operand slices, the step, D2H of the bf16 result
+        a, b, out = step.tensors
+        h_a = torch.empty(a.shape, dtype=a.dtype).pin_memory()
+        h_b = torch.empty(b.shape, dtype=b.dtype).pin_memory()
+        h_o = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+        h_a.copy_(a)
+        h_b.copy_(b)
+
+        def e2e_step(i):
+            a.copy_(h_a, non_blocking=True)
+            b.copy_(h_b, non_blocking=True)
+            step(i)
+            h_o.copy_(out, non_blocking=True)
+
+        e2e_steps = max(3, min(args.steps, 5))
+        e_ms = time_steps(e2e_step, e2e_steps, 1, dev, world)
+        line["e2e"] = {"value": flops * e2e_steps / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                       "h2d_bytes_per_step": (a.numel() + b.numel()) * 2 * world,
+                       "d2h_bytes_per_step": out.numel() * 2 * world, "steps": e2e_steps}
+        if rank == 0:
+            # the unsplit product on one GPU, for the scaling base of this same workload
+            try:
+                del a, b, out, step
+                torch.cuda.empty_cache()
+                ustep, uflops, _, _ = make_step(name, spec, dev, seed=1, world=1, rank=0)
+                ums = time_steps(ustep, 3, 1, dev, 1) / 3
+                line["unsplit_1gpu"] = {"tflops": uflops / (ums * 1e-3) / 1e12, "ms": ums}
+            except Exception as e:  # noqa: BLE001
+                line["unsplit_1gpu"] = {"error": repr(e)}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

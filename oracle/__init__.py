@@ -1,0 +1,241 @@
+"""CPU checkers of the GEMM hot path. TEST INFRASTRUCTURE ONLY.
+
+Two shared libraries sit behind this module:
+
+* ``libpto_oracle.so``  - the plain-C restatement of the reference CPU simulator's arithmetic
+  (``pto_gemm_oracle.c``), functions ``gemm_f32acc``, ``gemm_s8``, ``gemm_mx``, ``store_cast``,
+  ``dequant_bf16``, ``mx_quantize_e4m3``;
+* ``_ref/libpto_ref.so`` - the reference's own simulator compiled from its headers (``ref_shim.cpp``),
+  exposed as :class:`Ref`; it exists wherever ``make -C oracle`` has run with the reference tree present.
+
+Only tests, the smoke check and the benchmark's CPU-baseline leg may import this module; the product
+(``pto_isa_mirror_b200``) never does.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_LIB = os.path.join(HERE, "libpto_oracle.so")
+REF_LIB = os.path.join(HERE, "_ref", "libpto_ref.so")
+REF_LIB_1T = os.path.join(HERE, "_ref", "libpto_ref_1t.so")
+
+F16, BF16, F32 = 0, 1, 2
+B_DN, B_ND = 0, 1
+E4M3, E5M2 = 5, 6
+
+_ll = ctypes.c_longlong
+_i = ctypes.c_int
+_p = ctypes.c_void_p
+
+
+def build(ref_root: str | None = None) -> None:
+    """Compile the C restatement and, when the reference tree is present, the reference shim."""
+    cmd = ["make", "-C", HERE]
+    if ref_root:
+        cmd.append(f"REF={ref_root}")
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("oracle build failed:\n" + proc.stdout + proc.stderr)
+
+
+_oracle = None
+
+
+def _lib() -> ctypes.CDLL:
+    global _oracle
+    if _oracle is None:
+        if not os.path.exists(ORACLE_LIB):
+            build()
+        lib = ctypes.CDLL(ORACLE_LIB)
+        lib.pto_oracle_gemm_f32acc.argtypes = [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i]
+        lib.pto_oracle_gemm_s8.argtypes = [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i]
+        lib.pto_oracle_gemm_mx.argtypes = [_p, _p, _p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _i, _i, _i]
+        lib.pto_oracle_store_cast.argtypes = [_p, _p, _ll, _i]
+        lib.pto_oracle_dequant_bf16.argtypes = [_p, _p, _p, _p, _i, _i, _ll, _ll, _i]
+        lib.pto_oracle_mx_quantize_e4m3.argtypes = [_p, _p, _p, _i, _i, _ll]
+        lib.pto_oracle_float_to_bf16.argtypes = [ctypes.c_float]
+        lib.pto_oracle_float_to_bf16.restype = ctypes.c_uint16
+        lib.pto_oracle_float_to_half.argtypes = [ctypes.c_float]
+        lib.pto_oracle_float_to_half.restype = ctypes.c_uint16
+        lib.pto_oracle_half_to_float.argtypes = [ctypes.c_uint16]
+        lib.pto_oracle_half_to_float.restype = ctypes.c_float
+        lib.pto_oracle_fp8_to_double.argtypes = [ctypes.c_uint8, _i]
+        lib.pto_oracle_fp8_to_double.restype = ctypes.c_double
+        lib.pto_oracle_e8m0_to_double.argtypes = [ctypes.c_uint8]
+        lib.pto_oracle_e8m0_to_double.restype = ctypes.c_double
+        _oracle = lib
+    return _oracle
+
+
+def _c(a: np.ndarray, dtype) -> np.ndarray:
+    a = np.ascontiguousarray(a)
+    if a.dtype != np.dtype(dtype):
+        raise TypeError(f"expected {np.dtype(dtype)}, got {a.dtype}")
+    return a
+
+
+def _ptr(a: np.ndarray) -> int:
+    return a.ctypes.data
+
+
+# ----------------------------------------------------------------------------- restatement
+
+def gemm_f32acc(a: np.ndarray, b: np.ndarray, in_dtype: int, b_layout: int = B_DN, threads: int = 0) -> np.ndarray:
+    """Sequential-k fmaf GEMM. a [m, k]; b [n, k] (B_DN) or [k, n] (B_ND). F16/BF16 arrays are uint16 bit patterns."""
+    store = np.float32 if in_dtype == F32 else np.uint16
+    a = _c(a, store)
+    b = _c(b, store)
+    m, k = a.shape
+    n = b.shape[0] if b_layout == B_DN else b.shape[1]
+    assert (b.shape[1] if b_layout == B_DN else b.shape[0]) == k
+    c = np.empty((m, n), dtype=np.float32)
+    _lib().pto_oracle_gemm_f32acc(_ptr(a), _ptr(b), _ptr(c), m, n, k, a.shape[1], b.shape[1], n, in_dtype, b_layout,
+                                  threads)
+    return c
+
+
+def gemm_s8(a: np.ndarray, b_dn: np.ndarray, threads: int = 0) -> np.ndarray:
+    a = _c(a, np.int8)
+    b_dn = _c(b_dn, np.int8)
+    m, k = a.shape
+    n = b_dn.shape[0]
+    assert b_dn.shape[1] == k
+    c = np.empty((m, n), dtype=np.int32)
+    _lib().pto_oracle_gemm_s8(_ptr(a), _ptr(b_dn), _ptr(c), m, n, k, k, k, n, threads)
+    return c
+
+
+def gemm_mx(a: np.ndarray, b_dn: np.ndarray, sfa: np.ndarray, sfb: np.ndarray, a_fmt: int = E4M3, b_fmt: int = E4M3,
+            threads: int = 0) -> np.ndarray:
+    a = _c(a, np.uint8)
+    b_dn = _c(b_dn, np.uint8)
+    sfa = _c(sfa, np.uint8)
+    sfb = _c(sfb, np.uint8)
+    m, k = a.shape
+    n = b_dn.shape[0]
+    assert b_dn.shape[1] == k and sfa.shape == (m, k // 32) and sfb.shape == (n, k // 32)
+    c = np.empty((m, n), dtype=np.float32)
+    _lib().pto_oracle_gemm_mx(_ptr(a), _ptr(b_dn), _ptr(sfa), _ptr(sfb), _ptr(c), m, n, k, k, k, n, k // 32, k // 32,
+                              a_fmt, b_fmt, threads)
+    return c
+
+
+def store_cast(src: np.ndarray, out_dtype: int) -> np.ndarray:
+    """fp32 -> bf16 / f16 bit patterns (uint16), round to nearest even."""
+    src = _c(src, np.float32)
+    dst = np.empty(src.shape, dtype=np.uint16)
+    _lib().pto_oracle_store_cast(_ptr(src), _ptr(dst), src.size, out_dtype)
+    return dst
+
+
+def dequant_bf16(acc: np.ndarray, s_row: np.ndarray, s_col: np.ndarray, truncate13: bool = True) -> np.ndarray:
+    acc = _c(acc, np.int32)
+    s_row = _c(s_row, np.float32)
+    s_col = _c(s_col, np.float32)
+    m, n = acc.shape
+    out = np.empty((m, n), dtype=np.uint16)
+    _lib().pto_oracle_dequant_bf16(_ptr(acc), _ptr(s_row), _ptr(s_col), _ptr(out), m, n, n, n, int(truncate13))
+    return out
+
+
+def mx_quantize_e4m3(src: np.ndarray):
+    """OCP MX quantisation of fp32 [rows, k] along k in blocks of 32 -> (e4m3 bytes [rows, k], e8m0 bytes [rows, k/32])."""
+    src = _c(src, np.float32)
+    rows, k = src.shape
+    assert k % 32 == 0
+    data = np.empty((rows, k), dtype=np.uint8)
+    scales = np.empty((rows, k // 32), dtype=np.uint8)
+    _lib().pto_oracle_mx_quantize_e4m3(_ptr(src), _ptr(data), _ptr(scales), rows, k, k)
+    return data, scales
+
+
+def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    return store_cast(np.ascontiguousarray(x, dtype=np.float32), BF16)
+
+
+# ----------------------------------------------------------------------------- the reference itself
+
+class Ref:
+    """The reference simulator (oracle/_ref). ``single_thread`` picks the PTO_CPU_MAX_THREADS=1 build."""
+
+    TILE_M, TILE_N = 128, 256
+
+    def __init__(self, single_thread: bool = False):
+        path = REF_LIB_1T if single_thread else REF_LIB
+        if not os.path.exists(path):
+            raise FileNotFoundError(f"{path} not built (run `make -C oracle` where the reference tree is present)")
+        lib = ctypes.CDLL(path)
+        lib.ref_tile_f16.argtypes = [_p, _p, _p, _i]
+        lib.ref_tile_f32.argtypes = [_p, _p, _p, _i]
+        lib.ref_tile_s8.argtypes = [_p, _p, _p, _i]
+        lib.ref_tile_mx.argtypes = [_p, _p, _p, _p, _p, _i, _i, _i]
+        lib.ref_dequant_col.argtypes = [ctypes.c_int32, ctypes.c_float]
+        lib.ref_dequant_col.restype = ctypes.c_float
+        lib.ref_cast_bf16.argtypes = [ctypes.c_float]
+        lib.ref_cast_bf16.restype = ctypes.c_uint16
+        lib.ref_cast_f16.argtypes = [ctypes.c_float]
+        lib.ref_cast_f16.restype = ctypes.c_uint16
+        lib.ref_mx_quantize_e4m3.argtypes = [_p, _p, _p, _i, _i]
+        lib.ref_fp8_to_double.argtypes = [ctypes.c_uint8, _i]
+        lib.ref_fp8_to_double.restype = ctypes.c_double
+        lib.ref_e8m0_to_double.argtypes = [ctypes.c_uint8]
+        lib.ref_e8m0_to_double.restype = ctypes.c_double
+        self.lib = lib
+
+    @staticmethod
+    def available(single_thread: bool = False) -> bool:
+        return os.path.exists(REF_LIB_1T if single_thread else REF_LIB)
+
+    def has_real_bf16(self) -> bool:
+        return bool(self.lib.ref_has_real_bf16())
+
+    def _tile(self, fn, a, b_dn, store, out_dtype):
+        a = _c(a, store)
+        b_dn = _c(b_dn, store)
+        assert a.shape[0] == self.TILE_M and b_dn.shape[0] == self.TILE_N and a.shape[1] == b_dn.shape[1]
+        out = np.empty((self.TILE_M, self.TILE_N), dtype=out_dtype)
+        rc = fn(_ptr(out), _ptr(a), _ptr(b_dn), a.shape[1])
+        if rc != 0:
+            raise ValueError(f"K={a.shape[1]} is not instantiated in ref_shim.cpp")
+        return out
+
+    def tile_f16(self, a, b_dn):
+        """RunGemmE2E<float, half, half, ...> on a [128, K] x [256, K] tile (K in 256, 1024, 6144)."""
+        return self._tile(self.lib.ref_tile_f16, a, b_dn, np.uint16, np.float32)
+
+    def tile_f32(self, a, b_dn):
+        return self._tile(self.lib.ref_tile_f32, a, b_dn, np.float32, np.float32)
+
+    def tile_s8(self, a, b_dn):
+        return self._tile(self.lib.ref_tile_s8, a, b_dn, np.int8, np.int32)
+
+    def tile_mx(self, a, b_dn, sfa, sfb, a_fmt=E4M3, b_fmt=E4M3):
+        a = _c(a, np.uint8)
+        b_dn = _c(b_dn, np.uint8)
+        sfa = _c(sfa, np.uint8)
+        sfb = _c(sfb, np.uint8)
+        k = a.shape[1]
+        assert a.shape[0] == self.TILE_M and b_dn.shape == (self.TILE_N, k)
+        assert sfa.shape == (self.TILE_M, k // 32) and sfb.shape == (self.TILE_N, k // 32)
+        out = np.empty((self.TILE_M, self.TILE_N), dtype=np.float32)
+        rc = self.lib.ref_tile_mx(_ptr(out), _ptr(a), _ptr(b_dn), _ptr(sfa), _ptr(sfb), k, a_fmt, b_fmt)
+        if rc != 0:
+            raise ValueError("unsupported K or format for ref_tile_mx")
+        return out
+
+    def mx_quantize_e4m3(self, src):
+        src = _c(src, np.float32)
+        rows, k = src.shape
+        data = np.empty((rows, k), dtype=np.uint8)
+        scales = np.empty((rows, k // 32), dtype=np.uint8)
+        self.lib.ref_mx_quantize_e4m3(_ptr(src), _ptr(data), _ptr(scales), rows, k)
+        return data, scales

@@ -1,0 +1,228 @@
+// ref_shim.cpp - thin extern "C" entry points into the REFERENCE's own CPU simulator.
+//
+// TEST INFRASTRUCTURE ONLY. This file contains no arithmetic of its own: it includes the reference's headers
+// and its gemm_performance tile loop from the reference tree (given on the command line as REF, never copied
+// into this repository) and instantiates them for the tile shapes the parity tests and fixtures use. The
+// result, oracle/_ref/libpto_ref.so, validates the C restatement in pto_gemm_oracle.c, generates the fixtures
+// under tests/golden/, and is the CPU baseline of the benchmark (kind "reference").
+//
+// Build: see oracle/Makefile (g++ -std=c++23 with __cplusplus forced to 202302L so that the simulator's
+// bfloat16_t is the real std::bfloat16_t, -O2 -D__CPU_SIM -include stdint.h -include stddef.h).
+#include <pto/pto-inst.hpp>
+#include <pto/common/constants.hpp>
+#include <pto/cpu/MXTypes.hpp>
+#include <pto/cpu/TQuant.hpp>
+
+#include <cstdint>
+#include <cstring>
+
+// The reference tile loop RunGemmE2E (kernels/manual/a2a3/gemm_performance/gemm_performance_kernel.cpp:170-235).
+// Its <<<>>> launcher is guarded by #ifndef __COSTMODEL, the same way the reference's own host-side test pulls
+// the file in (tests/costmodel/st/testcase/gemm_perf_sim/main.cpp:16-31).
+#define __COSTMODEL
+#include REF_GEMM_KERNEL_CPP
+#undef __COSTMODEL
+
+using namespace pto;
+
+namespace {
+
+template <int K>
+void run_f16_tile(float* out, const uint16_t* a, const uint16_t* b_dn)
+{
+    RunGemmE2E<float, half, half, float, 1, 128, K, 256, 128, K, 256, 128, K, 256, 128, 64, 256, 1, 4, 4, 1>(
+        out, reinterpret_cast<half*>(const_cast<uint16_t*>(a)), reinterpret_cast<half*>(const_cast<uint16_t*>(b_dn)));
+}
+
+// fp32 operands (bf16-representable values feed the same cast-to-float + fma arithmetic, cpu/TMatmul.hpp:101-104).
+// baseN = 128 and stepK = 2 keep the 4-byte panels inside the simulated L1 / L0B capacities.
+template <int K>
+void run_f32_tile(float* out, const float* a, const float* b_dn)
+{
+    RunGemmE2E<float, float, float, float, 1, 128, K, 256, 128, K, 256, 128, K, 256, 128, 64, 128, 1, 2, 2, 1>(
+        out, const_cast<float*>(a), const_cast<float*>(b_dn));
+}
+
+template <int K>
+void run_s8_tile(int32_t* out, const int8_t* a, const int8_t* b_dn)
+{
+    RunGemmE2E<int32_t, int8_t, int8_t, int32_t, 1, 128, K, 256, 128, K, 256, 128, K, 256, 128, 64, 256, 1, 4, 4, 1>(
+        out, const_cast<int8_t*>(a), const_cast<int8_t*>(b_dn));
+}
+
+template <typename AT, typename BT>
+void run_mx_tile(float* out, const uint8_t* a, const uint8_t* b_dn, const uint8_t* sfa, const uint8_t* sfb, int k)
+{
+    constexpr int M = 128, N = 256, KC = 128, KS = KC / 32;
+    NPU_MEMORY_INIT(NPUArch::A5);
+    using LeftTile = TileLeft<AT, M, KC, M, KC>;
+    using RightTile = TileRight<BT, KC, N, KC, N>;
+    using LeftScaleTile = TileLeftScale<float8_e8m0_t, M, KS, M, KS>;
+    using RightScaleTile = TileRightScale<float8_e8m0_t, KS, N, KS, N>;
+    using AccTile = TileAcc<float, M, N, M, N>;
+    LeftTile aTile;
+    RightTile bTile;
+    LeftScaleTile saTile;
+    RightScaleTile sbTile;
+    AccTile cTile;
+    TASSIGN(aTile, 0x0);
+    TASSIGN(bTile, 0x0);
+    TASSIGN(saTile, GetScaleAddr(aTile.data()));
+    TASSIGN(sbTile, GetScaleAddr(bTile.data()));
+    TASSIGN(cTile, 0x0);
+    const int kg = k / 32;
+    for (int k0 = 0; k0 < k; k0 += KC) {
+        for (int i = 0; i < M; ++i) {
+            for (int kk = 0; kk < KC; ++kk) {
+                aTile.SetElement(i, kk, AT::FromRaw(a[static_cast<size_t>(i) * k + k0 + kk]));
+            }
+            for (int g = 0; g < KS; ++g) {
+                saTile.SetElement(i, g, float8_e8m0_t::FromRaw(sfa[static_cast<size_t>(i) * kg + k0 / 32 + g]));
+            }
+        }
+        for (int j = 0; j < N; ++j) {
+            for (int kk = 0; kk < KC; ++kk) {
+                bTile.SetElement(kk, j, BT::FromRaw(b_dn[static_cast<size_t>(j) * k + k0 + kk]));
+            }
+            for (int g = 0; g < KS; ++g) {
+                sbTile.SetElement(g, j, float8_e8m0_t::FromRaw(sfb[static_cast<size_t>(j) * kg + k0 / 32 + g]));
+            }
+        }
+        if (k0 == 0) {
+            TMATMUL_MX(cTile, aTile, saTile, bTile, sbTile);
+        } else {
+            TMATMUL_MX(cTile, cTile, aTile, saTile, bTile, sbTile);
+        }
+    }
+    for (int i = 0; i < M; ++i) {
+        for (int j = 0; j < N; ++j) {
+            out[static_cast<size_t>(i) * N + j] = cTile.GetElement(i, j);
+        }
+    }
+}
+
+} // namespace
+
+extern "C" {
+
+// 1 if this build has the simulator's real bfloat16_t (std::bfloat16_t), 0 if it is the _Float16 placeholder.
+int ref_has_real_bf16()
+{
+#if defined(__STDCPP_BFLOAT16_T__) && __cplusplus >= 202302L
+    return 1;
+#else
+    return 0;
+#endif
+}
+
+// One 128 x 256 output tile with the full K, B column-major (stored 256 x K). Returns 0, or -1 if K is not
+// one of the instantiated depths.
+int ref_tile_f16(float* out, const uint16_t* a, const uint16_t* b_dn, int k)
+{
+    switch (k) {
+        case 256: run_f16_tile<256>(out, a, b_dn); return 0;
+        case 1024: run_f16_tile<1024>(out, a, b_dn); return 0;
+        case 6144: run_f16_tile<6144>(out, a, b_dn); return 0;
+        default: return -1;
+    }
+}
+
+int ref_tile_f32(float* out, const float* a, const float* b_dn, int k)
+{
+    switch (k) {
+        case 256: run_f32_tile<256>(out, a, b_dn); return 0;
+        case 1024: run_f32_tile<1024>(out, a, b_dn); return 0;
+        case 4096: run_f32_tile<4096>(out, a, b_dn); return 0;
+        case 8192: run_f32_tile<8192>(out, a, b_dn); return 0;
+        case 65536: run_f32_tile<65536>(out, a, b_dn); return 0;
+        default: return -1;
+    }
+}
+
+int ref_tile_s8(int32_t* out, const int8_t* a, const int8_t* b_dn, int k)
+{
+    switch (k) {
+        case 256: run_s8_tile<256>(out, a, b_dn); return 0;
+        case 1024: run_s8_tile<1024>(out, a, b_dn); return 0;
+        case 8192: run_s8_tile<8192>(out, a, b_dn); return 0;
+        default: return -1;
+    }
+}
+
+// fmt: 5 = e4m3, 6 = e5m2 (the pto_b200_dtype values). k must be a multiple of 128.
+int ref_tile_mx(float* out, const uint8_t* a, const uint8_t* b_dn, const uint8_t* sfa, const uint8_t* sfb, int k,
+                int a_fmt, int b_fmt)
+{
+    if (k <= 0 || k % 128 != 0) {
+        return -1;
+    }
+    if (a_fmt == 5 && b_fmt == 5) {
+        run_mx_tile<float8_e4m3_t, float8_e4m3_t>(out, a, b_dn, sfa, sfb, k);
+    } else if (a_fmt == 6 && b_fmt == 6) {
+        run_mx_tile<float8_e5m2_t, float8_e5m2_t>(out, a, b_dn, sfa, sfb, k);
+    } else if (a_fmt == 5 && b_fmt == 6) {
+        run_mx_tile<float8_e4m3_t, float8_e5m2_t>(out, a, b_dn, sfa, sfb, k);
+    } else if (a_fmt == 6 && b_fmt == 5) {
+        run_mx_tile<float8_e5m2_t, float8_e4m3_t>(out, a, b_dn, sfa, sfb, k);
+    } else {
+        return -1;
+    }
+    return 0;
+}
+
+// Fixpipe per-column dequant of one int32 accumulator (vector form: the 64-bit scale word carries the fp32
+// bits of s_col in [31:0], of which the simulator reads [31:13]); returns the fp32 value before the output cast.
+float ref_dequant_col(int32_t acc, float s_col)
+{
+    uint32_t bits;
+    std::memcpy(&bits, &s_col, 4);
+    return quantize_element<float, int32_t, QuantMode_t::VQS322BF16_PRE, false>(acc, static_cast<uint64_t>(bits));
+}
+
+// TSTORE's no-quant cast, static_cast<Dst>(float) (include/pto/cpu/common.hpp:187-198).
+uint16_t ref_cast_bf16(float v)
+{
+    const bfloat16_t h = ConvertStoreValue<bfloat16_t, float, QuantMode_t::NoQuant, false>(v, 0);
+    uint16_t u;
+    std::memcpy(&u, &h, 2);
+    return u;
+}
+
+uint16_t ref_cast_f16(float v)
+{
+    const half h = ConvertStoreValue<half, float, QuantMode_t::NoQuant, false>(v, 0);
+    uint16_t u;
+    std::memcpy(&u, &h, 2);
+    return u;
+}
+
+// OCP MX quantiser pieces (include/pto/cpu/TQuant.hpp:178-190, 226-237, 118-153) applied per row and 32-wide block.
+void ref_mx_quantize_e4m3(const float* src, uint8_t* data, uint8_t* scales, int rows, int k)
+{
+    using namespace pto::cpu_quant;
+    const int groups = k / 32;
+    for (int r = 0; r < rows; ++r) {
+        for (int g = 0; g < groups; ++g) {
+            const float* x = src + static_cast<size_t>(r) * k + g * 32;
+            float amax = 0.0f;
+            for (int i = 0; i < 32; ++i) {
+                amax = std::max(amax, std::fabs(x[i]));
+            }
+            const uint8_t e = ComputeSharedExponent(amax);
+            const float scaling = ComputeMxScalingFromExponent(e);
+            scales[static_cast<size_t>(r) * groups + g] = e;
+            for (int i = 0; i < 32; ++i) {
+                data[static_cast<size_t>(r) * k + g * 32 + i] = EncodeE4M3Fn<QuantScaleAlg::OCP>(x[i] * scaling);
+            }
+        }
+    }
+}
+
+double ref_fp8_to_double(uint8_t raw, int fmt)
+{
+    return fmt == 6 ? static_cast<double>(float8_e5m2_t::FromRaw(raw)) : static_cast<double>(float8_e4m3_t::FromRaw(raw));
+}
+
+double ref_e8m0_to_double(uint8_t raw) { return static_cast<double>(float8_e8m0_t::FromRaw(raw)); }
+
+} // extern "C"

@@ -1,0 +1,127 @@
+"""K-split GEMM + allreduce across the GPUs of one node (one process per GPU).
+
+Reference shape of the computation: kernels/manual/a2a3/gemm_ar (README.md:33-46): every rank multiplies its
+own K slice (the compute kernel takes a ``k_per_rank`` stride, gemm_compute_kernel.cpp:150-165), the fp32
+partials are summed across ranks (reduce-scatter by atomic add into the owner's window, comm_kernel.cpp:165-210),
+and every rank ends with the full result (all-gather, comm_kernel.cpp:377-400), compute and communication running
+on two streams (main.cpp:761-800).
+
+Here rank r computes P_r = A[:, K_r] @ B[K_r, :] with the tcgen05 tile loop, panel by panel over M; each panel's
+fp32 partial is reduced with NCCL over NVLink on a second stream while the next panel is being multiplied, and
+the reduced panel is cast to bf16 (the TSTORE cast). Two reductions are offered:
+
+* ``"allreduce"``: ncclAllReduce(fp32 sum) then cast;
+* ``"rs_ag"``    : reduce-scatter (fp32) -> cast of the owned shard -> all-gather (bf16), which moves 25 % fewer
+  bytes per GPU than the fp32 allreduce.
+
+The result is bf16(sum_r P_r); the order of the cross-rank sum is NCCL's, so parity is by tolerance (1e-3).
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def panel_bounds(m: int, panels: int, align: int) -> List[tuple]:
+    """Split [0, m) into at most ``panels`` contiguous row ranges whose sizes are multiples of ``align``
+    (the last takes the remainder). Empty ranges are dropped."""
+    if m <= 0:
+        return []
+    panels = max(1, panels)
+    per = -(-m // panels)
+    per = -(-per // align) * align
+    out = []
+    r0 = 0
+    while r0 < m:
+        r1 = min(m, r0 + per)
+        out.append((r0, r1))
+        r0 = r1
+    return out
+
+
+def k_slice(k: int, world_size: int, rank: int) -> tuple:
+    """The K range owned by ``rank``: K is partitioned evenly (the benchmark's K-split configuration)."""
+    if k % world_size != 0:
+        raise ValueError(f"K={k} is not divisible by {world_size} ranks")
+    kr = k // world_size
+    return rank * kr, (rank + 1) * kr
+
+
+class KSplitGemmAllReduce:
+    """Pipelined per-rank GEMM + cross-rank reduction + bf16 cast.
+
+    ``gemm_fn(a, b_dn, out_f32)`` and ``cast_fn(src_f32, out_bf16)`` default to the CUDA library; the CPU tests
+    pass stand-ins so the scheduling, slicing and collective logic run under gloo without a GPU.
+    """
+
+    def __init__(self, m: int, n: int, group: Optional[dist.ProcessGroup] = None, panels: int = 4,
+                 mode: str = "rs_ag", device: Optional[torch.device] = None,
+                 gemm_fn: Optional[Callable] = None, cast_fn: Optional[Callable] = None):
+        if mode not in ("allreduce", "rs_ag"):
+            raise ValueError("mode must be 'allreduce' or 'rs_ag'")
+        self.m, self.n = m, n
+        self.group = group
+        self.world_size = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.mode = mode if self.world_size > 1 else "allreduce"
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.on_cuda = self.device.type == "cuda"
+        # panel rows are multiples of 128 * world_size so that tiles and reduce-scatter shards both divide evenly
+        self.panels = panel_bounds(m, panels, 128 * self.world_size)
+        if self.mode == "rs_ag" and any((r1 - r0) % self.world_size for r0, r1 in self.panels):
+            self.mode = "allreduce"
+        if gemm_fn is None or cast_fn is None:
+            from . import gemm as _g
+
+            gemm_fn = gemm_fn or (lambda a, b, out: _g.gemm(a, b, out=out))
+            cast_fn = cast_fn or (lambda src, out: _g.cast_f32_to_bf16(src, out=out))
+        self.gemm_fn, self.cast_fn = gemm_fn, cast_fn
+        self.partial = torch.empty((m, n), dtype=torch.float32, device=self.device)
+        if self.mode == "rs_ag":
+            max_rows = max(r1 - r0 for r0, r1 in self.panels) // self.world_size
+            self.shard_f32 = torch.empty((max_rows, n), dtype=torch.float32, device=self.device)
+            self.shard_bf16 = torch.empty((max_rows, n), dtype=torch.bfloat16, device=self.device)
+        if self.on_cuda:
+            self.comm_stream = torch.cuda.Stream(device=self.device)
+            self.events = [torch.cuda.Event() for _ in self.panels]
+            self.shard_free = torch.cuda.Event()
+
+    def step(self, a_slice: torch.Tensor, b_slice_dn: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """a_slice [m, K/ranks], b_slice_dn [n, K/ranks] (strided views of the full operands are fine),
+        out [m, n] bf16 contiguous. Enqueues everything; the caller's current stream ends up waiting for the result."""
+        assert tuple(out.shape) == (self.m, self.n) and out.is_contiguous()
+        if not self.on_cuda:
+            return self._step_serial(a_slice, b_slice_dn, out)
+        main = torch.cuda.current_stream(self.device)
+        self.comm_stream.wait_stream(main)
+        for i, (r0, r1) in enumerate(self.panels):
+            self.gemm_fn(a_slice[r0:r1], b_slice_dn, self.partial[r0:r1])
+            self.events[i].record(main)
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(self.events[i])
+                self._reduce_panel(r0, r1, out)
+        main.wait_stream(self.comm_stream)
+        return out
+
+    def _reduce_panel(self, r0: int, r1: int, out: torch.Tensor) -> None:
+        part = self.partial[r0:r1]
+        if self.world_size == 1:
+            self.cast_fn(part, out[r0:r1])
+        elif self.mode == "allreduce":
+            dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group)
+            self.cast_fn(part, out[r0:r1])
+        else:
+            rows = (r1 - r0) // self.world_size
+            shard = self.shard_f32[:rows]
+            shard16 = self.shard_bf16[:rows]
+            dist.reduce_scatter_tensor(shard, part, op=dist.ReduceOp.SUM, group=self.group)
+            self.cast_fn(shard, shard16)
+            dist.all_gather_into_tensor(out[r0:r1], shard16, group=self.group)
+
+    def _step_serial(self, a_slice, b_slice_dn, out):
+        for r0, r1 in self.panels:
+            self.gemm_fn(a_slice[r0:r1], b_slice_dn, self.partial[r0:r1])
+            self._reduce_panel(r0, r1, out)
+        return out

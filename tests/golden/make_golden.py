@@ -1,0 +1,103 @@
+"""Generate the golden fixtures under tests/golden/ by running the REFERENCE CPU simulator (oracle/_ref).
+
+Run where the reference tree is mounted:  make -C oracle && python tests/golden/make_golden.py
+Inputs are not stored: they are regenerated from pto_isa_mirror_b200.gen_data with the seeds below, and each
+fixture carries the SHA-256 of its input bytes so a drifting generator is caught. Outputs are the reference's.
+"""
+import hashlib
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+import oracle  # noqa: E402
+from pto_isa_mirror_b200 import gen_data as gd  # noqa: E402
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def sha(*arrays) -> str:
+    h = hashlib.sha256()
+    for a in arrays:
+        h.update(np.ascontiguousarray(a).tobytes())
+    return h.hexdigest()
+
+
+def save(name, **kw):
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **kw)
+    print("wrote", name, {k: getattr(v, "shape", v) for k, v in kw.items()})
+
+
+def main():
+    ref = oracle.Ref()
+    assert ref.has_real_bf16()
+
+    # C1: fp16 128 x 256 x 256, uniform[-1, 1), seed 0 (RunGemmE2E<float, half, half, ...>)
+    a, b = gd.dense_inputs(128, 256, 256, "f16", 0, "uniform")
+    save("c1_f16_k256", out=ref.tile_f16(a, b), input_sha=sha(a, b), seed=0)
+
+    # the reference's exactness style: small integers (tests/cpu/st/testcase/tmatmul/gen_data.py:43-45)
+    ai = gd.randint((128, 1024), 1, 5, 19, 0).astype(np.float16).view(np.uint16)
+    bi = gd.randint((256, 1024), 1, 5, 19, 1).astype(np.float16).view(np.uint16)
+    save("f16_randint_k1024", out=ref.tile_f16(ai, bi), input_sha=sha(ai, bi), seed=19)
+
+    # C2 / C5 sampled tiles: bf16 values through the float path, full K of the configuration
+    for k, seed in ((1024, 1), (4096, 1), (8192, 4), (65536, 4)):
+        a, b = gd.dense_inputs(128, 256, k, "bf16", seed)
+        out = ref.tile_f32(gd.bf16_bits_to_f32(a), gd.bf16_bits_to_f32(b))
+        out_bf16 = np.array([ref.lib.ref_cast_bf16(float(v)) for v in out.ravel()], dtype=np.uint16).reshape(out.shape)
+        save(f"bf16_tile_k{k}", out=out, out_bf16=out_bf16, input_sha=sha(a, b), seed=seed)
+
+    # C3 sampled tile: int8, exact int32 accumulators + the dequantised bf16 store
+    for k in (1024, 8192):
+        a, b, s_row, s_col = gd.s8_inputs(128, 256, k, 2)
+        acc = ref.tile_s8(a, b)
+        deq = np.empty(acc.shape, dtype=np.uint16)
+        for i in range(acc.shape[0]):
+            for j in range(acc.shape[1]):
+                t = np.float32(ref.lib.ref_dequant_col(int(acc[i, j]), float(s_col[j])))
+                deq[i, j] = ref.lib.ref_cast_bf16(float(np.float32(t * s_row[i])))
+        save(f"s8_tile_k{k}", acc=acc, deq_bf16=deq, input_sha=sha(a, b, s_row, s_col), seed=2)
+
+    # C4 sampled tile: MXFP8 e4m3 with e8m0 block scales, inputs through the reference's OCP quantiser
+    for k in (256, 8192):
+        xa = gd.normal((128, k), 3, 0)
+        xb = gd.normal((256, k), 3, 1)
+        a, sfa = ref.mx_quantize_e4m3(xa)
+        b, sfb = ref.mx_quantize_e4m3(xb)
+        save(f"mx_tile_k{k}", out=ref.tile_mx(a, b, sfa, sfb), a_sha=sha(a, sfa), b_sha=sha(b, sfb), seed=3)
+
+    # the reference's MX exactness style: integers in [-10, 10], scales 2^0..2^2, mixed e4m3 x e5m2
+    ai = gd.randint((128, 256), -10, 10, 19, 2).astype(np.float32)
+    bi = gd.randint((256, 256), -10, 10, 19, 3).astype(np.float32)
+    a8 = gd.encode_e4m3fn(ai)
+    import ml_dtypes
+
+    b8 = bi.astype(ml_dtypes.float8_e5m2).view(np.uint8)
+    sfa = gd.randint((128, 8), 127, 129, 19, 4).astype(np.uint8)
+    sfb = gd.randint((256, 8), 127, 129, 19, 5).astype(np.uint8)
+    save("mx_randint_e4m3_e5m2_k256", out=ref.tile_mx(a8, b8, sfa, sfb, oracle.E4M3, oracle.E5M2), a=a8, b=b8, sfa=sfa,
+         sfb=sfb)
+
+    # scalar tables: store casts, fp8 / e8m0 decode, quantiser
+    x = np.concatenate([gd.normal((4096,), 5) * np.float32(3.0),
+                        np.array([0, -0.0, 65504, 65519.9, 65520, 1e-8, 5.96e-8, 2.98e-8, 3e-8, 6.1e-5, 1e38, -1e38,
+                                  1.00390625, 1.01171875], dtype=np.float32)])
+    save("store_casts", x=x, bf16=np.array([ref.lib.ref_cast_bf16(float(v)) for v in x], dtype=np.uint16),
+         f16=np.array([ref.lib.ref_cast_f16(float(v)) for v in x], dtype=np.uint16))
+    save("fp8_decode", e4m3=np.array([ref.lib.ref_fp8_to_double(i, 5) for i in range(256)]),
+         e5m2=np.array([ref.lib.ref_fp8_to_double(i, 6) for i in range(256)]),
+         e8m0=np.array([ref.lib.ref_e8m0_to_double(i) for i in range(256)]))
+    src = gd.normal((64, 256), 6)
+    src[0, :32] = 0
+    src[1, :32] *= 1e-30
+    src[2, :32] *= 1e30
+    src[3, 5] = -1e-9
+    d, s = ref.mx_quantize_e4m3(src)
+    save("mx_quantize", src=src, data=d, scales=s)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,85 @@
+"""CPU-side checks of the C ABI: the library loads, exports every symbol include/pto_b200.h declares, and
+rejects bad arguments before touching a device (no compute calls here)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from pto_isa_mirror_b200 import _capi, build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build.build()
+    return _capi.load()
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "pto_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(pto_b200_\w+|call_kernel)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(lib):
+    names = declared_functions()
+    assert "pto_b200_gemm" in names and "call_kernel" in names and len(names) >= 10
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in include/pto_b200.h but not exported"
+    assert sorted(_capi.SYMBOLS) == names
+
+
+def test_error_strings(lib):
+    for code in range(8):
+        assert lib.pto_b200_error_string(code)
+    assert b"unknown" in lib.pto_b200_error_string(99)
+
+
+def test_argument_errors_come_before_any_launch(lib):
+    buf = (ctypes.c_uint8 * 4096)()
+    p = ctypes.addressof(buf)
+    p = (p + 15) & ~15
+    F16, BF16, F32, S8, S32 = _capi.F16, _capi.BF16, _capi.F32, _capi.S8, _capi.S32
+    g = lib.pto_b200_gemm
+    before = lib.pto_b200_launch_count()
+    assert g(None, None, p, p, 16, 16, 16, 16, 16, 16, F16, F32, 0) == _capi.EINVAL
+    assert g(None, p, p, p, 0, 16, 16, 16, 16, 16, F16, F32, 0) == _capi.EINVAL          # empty M
+    assert g(None, p, p, p, 16, 16, 16, 8, 16, 16, F16, F32, 0) == _capi.EINVAL          # lda < k
+    assert g(None, p, p, p, 16, 16, 16, 16, 16, 8, F16, F32, 0) == _capi.EINVAL          # ldc < n
+    assert g(None, p, p + 2, p, 16, 16, 16, 16, 16, 16, F16, F32, 0) == _capi.EALIGN      # A not 16-byte aligned
+    assert g(None, p, p, p, 16, 16, 12, 12, 12, 16, F16, F32, 0) == _capi.EALIGN          # 24-byte row pitch
+    assert g(None, p, p, p, 16, 16, 16, 16, 16, 16, F32, F32, 0) == _capi.EDTYPE          # fp32 inputs
+    assert g(None, p, p, p, 16, 16, 16, 16, 16, 16, F16, S32, 0) == _capi.EDTYPE          # half -> int32
+    assert g(None, p, p, p, 16, 16, 16, 16, 16, 16, S8, F32, 0) == _capi.EDTYPE           # int8 -> float
+    assert g(None, p, p, p, 16, 16, 16, 16, 16, 16, S8, S32, 1) == _capi.EDTYPE           # int8 with row-major B
+    assert g(None, p, p, p, 16, 16, 16, 16, 16, 16, BF16, F32, 7) == _capi.EDTYPE         # unknown layout
+    d = lib.pto_b200_gemm_s8_dequant
+    assert d(None, p, p, p, None, p, 16, 16, 16, 16, 16, 16) == _capi.EINVAL
+    mx = lib.pto_b200_gemm_mx
+    E4M3, E5M2 = _capi.E4M3, _capi.E5M2
+    assert mx(None, p, p, p, p, p, p, 1 << 20, 16, 16, 48, 48, 48, 16, 2, 2, E4M3, E4M3, BF16) == _capi.EINVAL   # k % 32
+    assert mx(None, p, p, p, p, p, p, 1 << 20, 16, 16, 64, 64, 64, 16, 2, 2, S8, E4M3, BF16) == _capi.EDTYPE
+    assert mx(None, p, p, p, p, p, p, 1 << 20, 16, 16, 64, 64, 64, 16, 2, 2, E4M3, E5M2, F16 + 0) == _capi.EDTYPE
+    assert mx(None, p, p, p, p, p, None, 0, 16, 16, 64, 64, 64, 16, 2, 2, E4M3, E4M3, BF16) == _capi.EWORKSPACE
+    assert mx(None, p, p, p, p, p, p, 16, 16, 16, 64, 64, 64, 16, 2, 2, E4M3, E4M3, BF16) == _capi.EWORKSPACE   # too small
+    assert lib.pto_b200_cast_f32_to_bf16(None, None, p, 4) == _capi.EINVAL
+    assert lib.pto_b200_cast_f32_to_bf16(None, p, p, 0) == _capi.OK
+    assert lib.pto_b200_launch_count() == before
+
+
+def test_mx_workspace_size(lib):
+    ws = lib.pto_b200_gemm_mx_workspace_bytes
+    assert ws(0, 16, 32) == 0
+    # 512-byte atoms: one per (128-row block, 128-wide K block) of A plus two per 256-column tile of B
+    assert ws(128, 256, 128) == 512 * (1 + 2)
+    assert ws(129, 257, 129) == 2 * 512 * (2 + 4)
+    assert ws(16384, 8192, 8192) == 64 * 512 * (128 + 64)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_capi, "_lib", None)
+    monkeypatch.setattr(_capi, "LIB_PATH", str(tmp_path / "libpto_b200.so"))
+    with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):
+        _capi.load()

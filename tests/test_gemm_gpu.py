@@ -1,0 +1,307 @@
+"""Parity of the CUDA tile loop with the oracle, through the C ABI (ctypes) with torch tensors as device buffers.
+
+Tolerances (from the benchmark specification): int8 accumulators bit-exact; fp16/bf16 -> fp32 max relative
+error <= 1e-3; MXFP8 <= 1e-2; integer-valued inputs (the reference tests' own style) exact in every precision."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import pto_isa_mirror_b200 as pto
+from conftest import golden
+from parity import bf16_ulp_distance, max_elem_rel_err, max_rel_err, result_cmp
+from pto_isa_mirror_b200 import gen_data as gd
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DENSE_TOL = 1e-3
+MX_TOL = 1e-2
+
+
+def dev16(bits, dtype):
+    return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).to(DEV).view(dtype)
+
+
+def dev8(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(DEV)
+
+
+def host(t):
+    torch.cuda.synchronize()
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).cpu().numpy().view(np.uint16)
+    if t.dtype == torch.float16:
+        return t.view(torch.int16).cpu().numpy().view(np.uint16)
+    return t.cpu().numpy()
+
+
+@pytest.fixture(autouse=True)
+def status_word_stays_clear():
+    yield
+    assert pto.device_status() == 0, "a kernel gave up on a bounded wait"
+
+
+# ------------------------------------------------------------------ configuration 1 and the reference's small cases
+
+@pytest.mark.parametrize("b_layout", [pto.B_DN, pto.B_ND])
+def test_c1_fp16_128x256x256(b_layout):
+    g = golden("c1_f16_k256")
+    a, b = gd.dense_inputs(128, 256, 256, "f16", 0, "uniform")
+    bt = dev16(b if b_layout == pto.B_DN else np.ascontiguousarray(b.T), torch.float16)
+    out = host(pto.gemm(dev16(a, torch.float16), bt, torch.float32, b_layout))
+    assert max_rel_err(out, g["out"]) <= DENSE_TOL
+    assert max_elem_rel_err(out, g["out"]) <= DENSE_TOL
+    assert result_cmp(g["out"], out, 1e-3)
+    assert np.array_equal(oracle.gemm_f32acc(a, b, oracle.F16), g["out"])
+
+
+def test_pto_gemm_basic_op():
+    a, b = gd.dense_inputs(512, 1536, 2048, "f16", 21)   # the op's reference shape
+    out = host(pto.pto_gemm_basic(dev16(a, torch.float16), dev16(b, torch.float16)))
+    ref = oracle.gemm_f32acc(a[:128], b[:256], oracle.F16)
+    assert max_rel_err(out[:128, :256], ref) <= DENSE_TOL
+    with pytest.raises(ValueError):
+        pto.pto_gemm_basic(dev16(a, torch.float16).float(), dev16(b, torch.float16))
+
+
+def padded(x, mult):
+    """Copy x into a buffer whose row pitch is a multiple of `mult` elements and return the [rows, cols] view."""
+    rows, cols = x.shape
+    pitch = (cols + mult - 1) // mult * mult
+    buf = torch.zeros((rows, pitch), dtype=x.dtype, device=DEV)
+    buf[:, :cols] = x
+    return buf[:, :cols]
+
+
+# shapes of tests/cpu/st/testcase/tmatmul/gen_data.py:102-119 and tests/npu/a2a3/src/st/testcase/tmatmul/gen_data.py:170-190
+REF_SMALL = [("f16", 40, 50, 60), ("f16", 128, 128, 64), ("f16", 1, 110, 50), ("bf16", 40, 50, 60),
+             ("bf16", 11, 402, 30), ("s8", 6, 7, 8), ("s8", 65, 90, 89), ("f16", 120, 110, 50), ("f16", 127, 72, 64)]
+
+
+@pytest.mark.parametrize("kind,m,n,k", REF_SMALL)
+def test_reference_small_integer_cases_exact(kind, m, n, k):
+    ai = gd.randint((m, k), 1, 5, 19, 0)
+    bi = gd.randint((n, k), 1, 5, 19, 1)
+    exact = ai @ bi.T
+    if kind == "s8":
+        a = padded(torch.from_numpy(ai.astype(np.int8)).to(DEV), 16)
+        b = padded(torch.from_numpy(bi.astype(np.int8)).to(DEV), 16)
+        out = host(pto.gemm(a, b, torch.int32))
+        assert np.array_equal(out, exact)
+        assert np.array_equal(oracle.gemm_s8(ai.astype(np.int8), bi.astype(np.int8)), exact)
+        return
+    dt = torch.float16 if kind == "f16" else torch.bfloat16
+    a = padded(torch.from_numpy(ai.astype(np.float32)).to(DEV).to(dt), 8)
+    b = padded(torch.from_numpy(bi.astype(np.float32)).to(DEV).to(dt), 8)
+    out = host(pto.gemm(a, b, torch.float32))
+    assert np.array_equal(out.astype(np.int64), exact)
+    # row-major B (the demo's layout) gives the same result
+    b_nd = padded(torch.from_numpy(np.ascontiguousarray(bi.T).astype(np.float32)).to(DEV).to(dt), 8)
+    assert np.array_equal(host(pto.gemm(a, b_nd, torch.float32, pto.B_ND)).astype(np.int64), exact)
+    # 16-bit stores: values <= 25 * k are exact in half only for small k; compare against the oracle's cast
+    for out_dt, code in ((torch.float16, oracle.F16), (torch.bfloat16, oracle.BF16)):
+        got = host(pto.gemm(a, b, out_dt))
+        assert np.array_equal(got, oracle.store_cast(exact.astype(np.float32), code))
+
+
+def test_split_k_accumulation_equals_one_chain():
+    """TMATMUL then TMATMUL_ACC over K chunks (tmatmul split-K case) is the same sum as one call over the whole K."""
+    a, b = gd.dense_inputs(128, 128, 320, "f16", 23)
+    ta, tb = dev16(a, torch.float16), dev16(b, torch.float16)
+    whole = host(pto.gemm(ta, tb, torch.float32))
+    ref = oracle.gemm_f32acc(a, b, oracle.F16)
+    assert max_rel_err(whole, ref) <= DENSE_TOL
+
+
+# ------------------------------------------------------------------ sampled tiles of the big configurations
+
+@pytest.mark.parametrize("k", [1024, 4096, 8192, 65536])
+def test_bf16_golden_tiles(k):
+    g = golden(f"bf16_tile_k{k}")
+    seed = 1 if k <= 4096 else 4
+    a, b = gd.dense_inputs(128, 256, k, "bf16", seed)
+    ta, tb = dev16(a, torch.bfloat16), dev16(b, torch.bfloat16)
+    out32 = host(pto.gemm(ta, tb, torch.float32))
+    assert max_rel_err(out32, g["out"]) <= DENSE_TOL
+    assert max_elem_rel_err(out32, g["out"]) <= DENSE_TOL
+    out16 = host(pto.gemm(ta, tb, torch.bfloat16))
+    assert bf16_ulp_distance(out16, g["out_bf16"]) <= 1
+    assert np.array_equal(out16, gd.f32_to_bf16_bits(out32))   # the store cast itself is exact RNE
+
+
+@pytest.mark.parametrize("k", [1024, 8192])
+def test_int8_golden_tiles_bit_exact(k):
+    g = golden(f"s8_tile_k{k}")
+    a, b, s_row, s_col = gd.s8_inputs(128, 256, k, 2)
+    ta, tb = dev8(a), dev8(b)
+    assert np.array_equal(host(pto.gemm(ta, tb, torch.int32)), g["acc"])
+    deq = host(pto.gemm_s8_dequant(ta, tb, dev8(s_row), dev8(s_col)))
+    assert np.array_equal(deq, g["deq_bf16"])
+
+
+@pytest.mark.parametrize("k", [256, 8192])
+def test_mx_golden_tiles(k):
+    g = golden(f"mx_tile_k{k}")
+    a, sfa = gd.mx_quantize_e4m3(gd.normal((128, k), 3, 0))
+    b, sfb = gd.mx_quantize_e4m3(gd.normal((256, k), 3, 1))
+    out = host(pto.gemm_mx(dev8(a), dev8(b), dev8(sfa), dev8(sfb), torch.float32))
+    assert max_rel_err(out, g["out"]) <= MX_TOL
+    assert max_elem_rel_err(out, g["out"]) <= MX_TOL
+    out16 = host(pto.gemm_mx(dev8(a), dev8(b), dev8(sfa), dev8(sfb), torch.bfloat16))
+    assert np.array_equal(out16, gd.f32_to_bf16_bits(out))
+
+
+def test_mx_mixed_formats_integers_exact():
+    g = golden("mx_randint_e4m3_e5m2_k256")
+    out = host(pto.gemm_mx(dev8(g["a"]), dev8(g["b"]), dev8(g["sfa"]), dev8(g["sfb"]), torch.float32,
+                           a_fmt=pto.E4M3, b_fmt=pto.E5M2))
+    assert np.array_equal(out, g["out"])
+
+
+# shapes of tests/cpu/st/testcase/tmatmul_mx/gen_data.py (K rounded up to the 32-element block)
+@pytest.mark.parametrize("m,n,k,fa,fb", [(128, 64, 64, 5, 5), (127, 72, 64, 5, 6), (10, 50, 64, 6, 5),
+                                          (4, 30, 128, 6, 6), (200, 136, 96, 5, 5), (1, 256, 32, 5, 5)])
+def test_mx_reference_shapes_integers_exact(m, n, k, fa, fb):
+    import ml_dtypes
+
+    def enc(x, f):
+        return x.astype(ml_dtypes.float8_e4m3fn if f == 5 else ml_dtypes.float8_e5m2).view(np.uint8)
+
+    ai = gd.randint((m, k), -10, 10, 19, 2).astype(np.float32)
+    bi = gd.randint((n, k), -10, 10, 19, 3).astype(np.float32)
+    a8, b8 = enc(ai, fa), enc(bi, fb)
+    sfa = gd.randint((m, k // 32), 127, 129, 19, 4).astype(np.uint8)
+    sfb = gd.randint((n, k // 32), 127, 129, 19, 5).astype(np.uint8)
+    ref = oracle.gemm_mx(a8, b8, sfa, sfb, fa, fb)
+    ta, tb = padded(dev8(a8), 16), padded(dev8(b8), 16)
+    tsa, tsb = dev8(sfa), dev8(sfb)
+    out = host(pto.gemm_mx(ta, tb, tsa, tsb, torch.float32, a_fmt=fa, b_fmt=fb))
+    assert np.array_equal(out, ref)
+
+
+# ------------------------------------------------------------------ full-size configurations: sampled tiles + whole-matrix properties
+
+def sample_tiles(m, n, count, seed):
+    idx = gd.randint((count, 2), 0, 1 << 30, seed, 9)
+    return [(int(i % (m // 128)) * 128, int(j % (n // 256)) * 256) for i, j in idx]
+
+
+def test_c2_bf16_4096_cubed():
+    m = n = k = 4096
+    a, b = gd.dense_inputs(m, n, k, "bf16", 1)
+    ta, tb = dev16(a, torch.bfloat16), dev16(b, torch.bfloat16)
+    out32 = host(pto.gemm(ta, tb, torch.float32))
+    out16 = host(pto.gemm(ta, tb, torch.bfloat16))
+    assert np.array_equal(out16, gd.f32_to_bf16_bits(out32))
+    for r0, c0 in sample_tiles(m, n, 8, 31):
+        ref = oracle.gemm_f32acc(a[r0:r0 + 128], b[c0:c0 + 256], oracle.BF16)
+        assert max_rel_err(out32[r0:r0 + 128, c0:c0 + 256], ref) <= DENSE_TOL
+        assert bf16_ulp_distance(out16[r0:r0 + 128, c0:c0 + 256], gd.f32_to_bf16_bits(ref)) <= 1
+    # linearity in a power of two is exact, and a row permutation of A permutes C bit for bit
+    a2 = gd.f32_to_bf16_bits(gd.bf16_bits_to_f32(a) * np.float32(2.0))
+    assert np.array_equal(host(pto.gemm(dev16(a2, torch.bfloat16), tb, torch.float32)), out32 * np.float32(2.0))
+    perm = np.argsort(gd.uniform01(m, 77))
+    assert np.array_equal(host(pto.gemm(dev16(a[perm], torch.bfloat16), tb, torch.float32)), out32[perm])
+
+
+def test_c3_int8_8192_cubed_exact():
+    m = n = k = 8192
+    a, b, s_row, s_col = gd.s8_inputs(m, n, k, 2)
+    ta, tb = dev8(a), dev8(b)
+    acc_t = pto.gemm(ta, tb, torch.int32)
+    # whole-matrix checksums, exact in int64: sum_j C[i][j] = A[i] . (sum_j B[j]) and sum_i C[i][j] = (sum_i A[i]) . B[j]
+    row_sums = acc_t.sum(dim=1, dtype=torch.int64).cpu().numpy()
+    col_sums = acc_t.sum(dim=0, dtype=torch.int64).cpu().numpy()
+    assert np.array_equal(row_sums, a.astype(np.int64) @ b.astype(np.int64).sum(axis=0))
+    assert np.array_equal(col_sums, b.astype(np.int64) @ a.astype(np.int64).sum(axis=0))
+    acc = host(acc_t)
+    deq = host(pto.gemm_s8_dequant(ta, tb, dev8(s_row), dev8(s_col)))
+    for r0, c0 in sample_tiles(m, n, 4, 32):
+        ref = oracle.gemm_s8(a[r0:r0 + 128], b[c0:c0 + 256])
+        assert np.array_equal(acc[r0:r0 + 128, c0:c0 + 256], ref)
+        assert np.array_equal(deq[r0:r0 + 128, c0:c0 + 256],
+                              oracle.dequant_bf16(ref, s_row[r0:r0 + 128], s_col[c0:c0 + 256], True))
+    # the fused dequant store equals the oracle's store applied to the GPU's own accumulators, everywhere
+    assert np.array_equal(deq[:1024], oracle.dequant_bf16(acc[:1024], s_row[:1024], s_col, True))
+
+
+def test_c4_mxfp8_sampled_tiles():
+    m, n, k = 16384, 8192, 8192
+    # full-size inputs are quantised block by block from the counter-based generator
+    xa = gd.normal((1024, k), 3, 0)
+    a_blk, sfa_blk = gd.mx_quantize_e4m3(xa)
+    xb = gd.normal((1024, k), 3, 1)
+    b_blk, sfb_blk = gd.mx_quantize_e4m3(xb)
+    ta = dev8(a_blk).repeat(m // 1024, 1)
+    tsa = dev8(sfa_blk).repeat(m // 1024, 1)
+    tb = dev8(b_blk).repeat(n // 1024, 1)
+    tsb = dev8(sfb_blk).repeat(n // 1024, 1)
+    # make the repeats differ: negate whole row blocks of A (sign bit of e4m3 bytes)
+    for blk in range(1, m // 1024, 2):
+        ta[blk * 1024:(blk + 1) * 1024] ^= 0x80
+    out = pto.gemm_mx(ta, tb, tsa, tsb, torch.float32)
+    a_h, sfa_h, b_h, sfb_h = host(ta), host(tsa), host(tb), host(tsb)
+    out_h = host(out)
+    for r0, c0 in sample_tiles(m, n, 4, 33):
+        ref = oracle.gemm_mx(a_h[r0:r0 + 128], b_h[c0:c0 + 256], sfa_h[r0:r0 + 128], sfb_h[c0:c0 + 256])
+        assert max_rel_err(out_h[r0:r0 + 128, c0:c0 + 256], ref) <= MX_TOL
+        assert max_elem_rel_err(out_h[r0:r0 + 128, c0:c0 + 256], ref) <= MX_TOL
+    # negating A's rows negates C's rows exactly; identical row blocks give identical results
+    assert np.array_equal(out_h[0:1024], -out_h[1024:2048])
+    assert np.array_equal(out_h[0:1024], out_h[2048:3072])
+
+
+def test_c5_ksplit_slices_on_one_gpu():
+    """K-split partials of configuration 5's shape class (strided K slices of A and B), summed in fp32."""
+    m, n, k, ranks = 512, 1024, 8192, 4
+    a, b = gd.dense_inputs(m, n, k, "bf16", 4)
+    ta, tb = dev16(a, torch.bfloat16), dev16(b, torch.bfloat16)
+    total = torch.zeros((m, n), dtype=torch.float32, device=DEV)
+    kr = k // ranks
+    for r in range(ranks):
+        total += pto.gemm(ta[:, r * kr:(r + 1) * kr], tb[:, r * kr:(r + 1) * kr], torch.float32)
+    out16 = host(pto.cast_f32_to_bf16(total))
+    ref = oracle.gemm_f32acc(a[:128], b[:256], oracle.BF16)
+    assert max_rel_err(host(total)[:128, :256], ref) <= DENSE_TOL
+    assert np.array_equal(out16, gd.f32_to_bf16_bits(host(total)))
+    unsplit = host(pto.gemm(ta, tb, torch.float32))
+    assert max_rel_err(host(total), unsplit) <= DENSE_TOL
+
+
+# ------------------------------------------------------------------ edges
+
+@pytest.mark.parametrize("m,n,k", [(1, 8, 8), (129, 257, 72), (128, 256, 64), (300, 40, 1000), (77, 513, 136)])
+def test_ragged_edges_leave_padding_untouched(m, n, k):
+    a, b = gd.dense_inputs(m, n, k, "bf16", 41)
+    ta, tb = dev16(a, torch.bfloat16), dev16(b, torch.bfloat16)
+    ref = oracle.gemm_f32acc(a, b, oracle.BF16)
+    for out_dt in (torch.float32, torch.bfloat16):
+        pitch = n + 5                                   # odd pitch: the scalar store path
+        buf = torch.full((m + 2, pitch), -777.0, dtype=out_dt, device=DEV)
+        view = buf[1:m + 1, :n]
+        pto.gemm(ta, tb, out=view)
+        got = buf.float().cpu().numpy()
+        assert max_rel_err(got[1:m + 1, :n], ref) <= (DENSE_TOL if out_dt == torch.float32 else 8e-3)
+        assert (got[0] == -777.0).all() and (got[m + 1] == -777.0).all() and (got[:, n:] == -777.0).all()
+
+
+def test_wrapper_rejects_bad_arguments():
+    a = torch.zeros((16, 12), dtype=torch.float16, device=DEV)     # 24-byte row pitch
+    with pytest.raises(pto.PtoB200Error) as e:
+        pto.gemm(a, a, torch.float32)
+    assert e.value.code == 2
+    with pytest.raises(ValueError):
+        pto.gemm(a.float(), a.float())
+    before = pto.launch_count()
+    pto.gemm(torch.zeros((16, 16), dtype=torch.float16, device=DEV), torch.zeros((16, 16), dtype=torch.float16, device=DEV))
+    assert pto.launch_count() == before + 1
+
+
+def test_launch_is_asynchronous_on_the_given_stream():
+    a, b = gd.dense_inputs(256, 256, 256, "bf16", 43)
+    ta, tb = dev16(a, torch.bfloat16), dev16(b, torch.bfloat16)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    out = pto.gemm(ta, tb, torch.float32, stream=s)
+    s.synchronize()
+    assert max_rel_err(out.cpu().numpy(), oracle.gemm_f32acc(a, b, oracle.BF16)) <= DENSE_TOL

@@ -1,0 +1,89 @@
+"""Host logic of the K-split GEMM + allreduce under gloo (world size 2, CPU): partitioning, panel schedule,
+both reduction modes and the bf16 cast, with the oracle standing in for the CUDA GEMM."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from pto_isa_mirror_b200 import gen_data as gd
+from pto_isa_mirror_b200.ksplit import KSplitGemmAllReduce, k_slice, panel_bounds
+
+
+def test_panel_bounds():
+    assert panel_bounds(8192, 4, 1024) == [(0, 2048), (2048, 4096), (4096, 6144), (6144, 8192)]
+    assert panel_bounds(300, 4, 128) == [(0, 128), (128, 256), (256, 300)]
+    assert panel_bounds(100, 1, 256) == [(0, 100)]
+    assert panel_bounds(0, 4, 128) == []
+    covered = panel_bounds(5000, 3, 256)
+    assert covered[0][0] == 0 and covered[-1][1] == 5000
+    assert all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
+
+
+def test_k_slice():
+    assert k_slice(65536, 8, 3) == (24576, 32768)
+    assert [k_slice(64, 4, r) for r in range(4)] == [(0, 16), (16, 32), (32, 48), (48, 64)]
+    with pytest.raises(ValueError):
+        k_slice(100, 8, 0)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _oracle_gemm(a, b_dn, out):
+    import oracle
+
+    a16 = gd.f32_to_bf16_bits(a.float().numpy())
+    b16 = gd.f32_to_bf16_bits(b_dn.float().numpy())
+    out.copy_(torch.from_numpy(oracle.gemm_f32acc(a16, b16, oracle.BF16, threads=2)))
+
+
+def _cast(src, out):
+    out.copy_(torch.from_numpy(gd.f32_to_bf16_bits(src.numpy()).view(np.int16)).view(torch.bfloat16))
+
+
+def _worker(rank, world, port, mode, m, n, k, result_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        a_bits, b_bits = gd.dense_inputs(m, n, k, "bf16", 4)
+        a = torch.from_numpy(gd.bf16_bits_to_f32(a_bits)).bfloat16()
+        b = torch.from_numpy(gd.bf16_bits_to_f32(b_bits)).bfloat16()
+        k0, k1 = k_slice(k, world, rank)
+        op = KSplitGemmAllReduce(m, n, panels=2, mode=mode, device=torch.device("cpu"), gemm_fn=_oracle_gemm,
+                                 cast_fn=_cast)
+        out = torch.empty((m, n), dtype=torch.bfloat16)
+        op.step(a[:, k0:k1], b[:, k0:k1], out)
+        np.save(os.path.join(result_dir, f"out_{rank}.npy"), out.view(torch.int16).numpy())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["allreduce", "rs_ag"])
+def test_ksplit_two_ranks_gloo(tmp_path, mode):
+    import oracle
+
+    m, n, k, world = 512, 64, 256, 2
+    port = _free_port()
+    mp.spawn(_worker, args=(world, port, mode, m, n, k, str(tmp_path)), nprocs=world, join=True)
+    outs = [np.load(tmp_path / f"out_{r}.npy").view(np.uint16) for r in range(world)]
+    assert np.array_equal(outs[0], outs[1]), "every rank must end with the same full result"
+    a_bits, b_bits = gd.dense_inputs(m, n, k, "bf16", 4)
+    # reference: fp32 partial of each K slice summed in rank order, then one bf16 cast
+    total = np.zeros((m, n), dtype=np.float32)
+    for r in range(world):
+        k0, k1 = k_slice(k, world, r)
+        total += oracle.gemm_f32acc(np.ascontiguousarray(a_bits[:, k0:k1]), np.ascontiguousarray(b_bits[:, k0:k1]),
+                                    oracle.BF16)
+    assert np.array_equal(outs[0], gd.f32_to_bf16_bits(total))
+    # and it agrees with the unsplit chain within the dense tolerance
+    unsplit = oracle.gemm_f32acc(a_bits, b_bits, oracle.BF16)
+    got = gd.bf16_bits_to_f32(outs[0])
+    assert np.abs(got - unsplit).max() / np.abs(unsplit).max() <= 8e-3  # bf16 output rounding dominates
