@@ -10,7 +10,7 @@ from typing import Optional
 
 import torch
 
-from . import gemm as _g
+from .gemm import gemm as _gemm
 from ._capi import B_DN
 
 _NP_VIEW = {torch.bfloat16: torch.int16, torch.float16: torch.int16}
@@ -43,7 +43,7 @@ class HostGemm:
         with torch.cuda.stream(self.stream):
             self.d_a.copy_(h_a, non_blocking=True)
             self.d_b.copy_(h_b_dn, non_blocking=True)
-            _g.gemm(self.d_a, self.d_b, b_layout=B_DN, out=self.d_c, stream=self.stream)
+            _gemm(self.d_a, self.d_b, b_layout=B_DN, out=self.d_c, stream=self.stream)
             self.h_c.copy_(self.d_c, non_blocking=True)
         self.stream.synchronize()
         return self.h_c

@@ -73,10 +73,11 @@ class KSplitGemmAllReduce:
         if self.mode == "rs_ag" and any((r1 - r0) % self.world_size for r0, r1 in self.panels):
             self.mode = "allreduce"
         if gemm_fn is None or cast_fn is None:
-            from . import gemm as _g
+            from .gemm import cast_f32_to_bf16 as _cast
+            from .gemm import gemm as _gemm
 
-            gemm_fn = gemm_fn or (lambda a, b, out: _g.gemm(a, b, out=out))
-            cast_fn = cast_fn or (lambda src, out: _g.cast_f32_to_bf16(src, out=out))
+            gemm_fn = gemm_fn or (lambda a, b, out: _gemm(a, b, out=out))
+            cast_fn = cast_fn or (lambda src, out: _cast(src, out=out))
         self.gemm_fn, self.cast_fn = gemm_fn, cast_fn
         self.partial = torch.empty((m, n), dtype=torch.float32, device=self.device)
         if self.mode == "rs_ag":

@@ -125,8 +125,12 @@ def test_bf16_golden_tiles(k):
     assert max_rel_err(out32, g["out"]) <= DENSE_TOL
     assert max_elem_rel_err(out32, g["out"]) <= DENSE_TOL
     out16 = host(pto.gemm(ta, tb, torch.bfloat16))
-    assert bf16_ulp_distance(out16, g["out_bf16"]) <= 1
     assert np.array_equal(out16, gd.f32_to_bf16_bits(out32))   # the store cast itself is exact RNE
+    # against the reference's bf16 store: at most one bf16 step apart wherever the value is not near zero
+    # (near zero an fp32 difference of 1e-6 of the matrix scale spans several tiny bf16 steps)
+    big = np.abs(g["out"]) >= np.sqrt(np.mean(g["out"] ** 2)) / 16
+    assert bf16_ulp_distance(out16[big], g["out_bf16"][big]) <= 1
+    assert max_rel_err(gd.bf16_bits_to_f32(out16), gd.bf16_bits_to_f32(g["out_bf16"])) <= DENSE_TOL + 2.0 ** -8
 
 
 @pytest.mark.parametrize("k", [1024, 8192])
@@ -196,7 +200,8 @@ def test_c2_bf16_4096_cubed():
     for r0, c0 in sample_tiles(m, n, 8, 31):
         ref = oracle.gemm_f32acc(a[r0:r0 + 128], b[c0:c0 + 256], oracle.BF16)
         assert max_rel_err(out32[r0:r0 + 128, c0:c0 + 256], ref) <= DENSE_TOL
-        assert bf16_ulp_distance(out16[r0:r0 + 128, c0:c0 + 256], gd.f32_to_bf16_bits(ref)) <= 1
+        big = np.abs(ref) >= np.sqrt(np.mean(ref ** 2)) / 16
+        assert bf16_ulp_distance(out16[r0:r0 + 128, c0:c0 + 256][big], gd.f32_to_bf16_bits(ref)[big]) <= 1
     # linearity in a power of two is exact, and a row permutation of A permutes C bit for bit
     a2 = gd.f32_to_bf16_bits(gd.bf16_bits_to_f32(a) * np.float32(2.0))
     assert np.array_equal(host(pto.gemm(dev16(a2, torch.bfloat16), tb, torch.float32)), out32 * np.float32(2.0))
@@ -277,12 +282,12 @@ def test_ragged_edges_leave_padding_untouched(m, n, k):
     ref = oracle.gemm_f32acc(a, b, oracle.BF16)
     for out_dt in (torch.float32, torch.bfloat16):
         pitch = n + 5                                   # odd pitch: the scalar store path
-        buf = torch.full((m + 2, pitch), -777.0, dtype=out_dt, device=DEV)
+        buf = torch.full((m + 2, pitch), -768.0, dtype=out_dt, device=DEV)
         view = buf[1:m + 1, :n]
         pto.gemm(ta, tb, out=view)
         got = buf.float().cpu().numpy()
         assert max_rel_err(got[1:m + 1, :n], ref) <= (DENSE_TOL if out_dt == torch.float32 else 8e-3)
-        assert (got[0] == -777.0).all() and (got[m + 1] == -777.0).all() and (got[:, n:] == -777.0).all()
+        assert (got[0] == -768.0).all() and (got[m + 1] == -768.0).all() and (got[:, n:] == -768.0).all()
 
 
 def test_wrapper_rejects_bad_arguments():
