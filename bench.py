@@ -211,7 +211,8 @@ def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=4, 
         a = _randn_scaled((m, kr), k, torch.bfloat16, gen, dev)
         b = _randn_scaled((n, kr), k, torch.bfloat16, gen, dev)
         out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
-        op = KSplitGemmAllReduce(m, n, panels=panels if world > 1 else 1, mode=mode, device=dev)
+        op = KSplitGemmAllReduce(m, n, panels=panels if world > 1 else 1, mode=mode, device=dev,
+                                 single_rank=(world == 1))
 
         def step(i):
             op.step(a, b, out)
@@ -386,7 +387,10 @@ def main():
     torch.cuda.set_device(dev)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+
+        # a short collective timeout: a rank that never joins ends the run with an error instead of hanging it
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
 
     name = args.workload or ("bf16_4096" if world == 1 else "ksplit_bf16_8192x65536x8192")
     spec = WORKLOADS[name]

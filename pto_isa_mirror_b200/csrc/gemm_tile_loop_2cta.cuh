@@ -1,0 +1,275 @@
+// Two-CTA form of the GEMM tile loop: a cluster of two CTAs (one per SM) owns a 256 x 256 output tile and
+// issues `tcgen05.mma.cta_group::2`. Each CTA stages its own 128 rows of A and its own 128 columns of B
+// (B column-major), so every B byte is loaded and read from shared memory once per pair instead of once per
+// CTA; each CTA's tensor memory holds its 128 rows of the accumulator, all 256 columns.
+//
+// Roles per CTA are those of gemm_tile_loop (TLOAD warp, MMA warp, four TSTORE warps); only the leader CTA
+// (cluster rank 0) issues MMAs. Hand-offs across the pair:
+//   full[stage]   lives in the leader; both CTAs' TMA loads complete their bytes on it (no multicast: each CTA
+//                 loads different data, the `.cta_group::2` form only lets the completion land in the peer)
+//   empty[stage]  one in each CTA, released by the leader's tcgen05.commit to both
+//   acc_full[a]   one in each CTA, published by the leader's tcgen05.commit to both
+//   acc_empty[a]  lives in the leader; the peer's TSTORE warps arrive on it across the cluster
+// Every wait is bounded as in gemm_tile_loop; the pair leaves through a cluster barrier so neither CTA's shared
+// or tensor memory disappears while the other can still touch it.
+#pragma once
+#include "gemm_tile_loop.cuh"
+
+namespace pto_b200 {
+
+constexpr int kPairBlockM = 256;
+constexpr int kPairBlockN = 256;
+
+template <int KIND, int STAGES>
+struct PairSmemLayout {
+    static constexpr int kABytes = kBlockM * kBlockKBytes;        // this CTA's 128 rows of A
+    static constexpr int kBBytes = (kPairBlockN / 2) * kBlockKBytes; // this CTA's 128 columns of B
+    static constexpr int kSfaBytes = (KIND == KIND_MXF8) ? 512 : 0;
+    static constexpr int kSfbBytes = (KIND == KIND_MXF8) ? 1024 : 0; // scales of all 256 columns, in both CTAs
+    static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+    static constexpr int kAOff = 0;
+    static constexpr int kBOff = STAGES * kABytes;
+    static constexpr int kSfaOff = kBOff + STAGES * kBBytes;
+    static constexpr int kSfbOff = kSfaOff + STAGES * kSfaBytes;
+    static constexpr int kBarOff = kSfbOff + STAGES * kSfbBytes;
+    static constexpr int kNumBars = 2 * STAGES + 4;
+    static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+    static constexpr int kTotal = kMiscOff + 16 + 1024;
+};
+
+template <int KIND, int STAGES, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+    gemm_tile_loop_2cta(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const GemmParams p)
+{
+    using L = PairSmemLayout<KIND, STAGES>;
+    constexpr int kNumAcc = (KIND == KIND_MXF8) ? 1 : 2;
+    constexpr int kAccCols = 256;
+    constexpr uint32_t kSfaCol = 256;
+    constexpr uint32_t kSfbCol = 260;
+    constexpr int kBlockKElems = (KIND == KIND_F16) ? 64 : 128;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_full_bar = empty_bar + STAGES;
+    uint64_t* acc_empty_bar = acc_full_bar + 2;
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
+    volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kMiscOff + 4);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = ptx::cluster_ctarank();
+    const bool leader = (cta_rank == 0);
+    const int pair = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+    const int total_tiles = p.m_tiles * p.n_tiles; // tiles of 256 x 256
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(&full_bar[s], 1);
+            ptx::mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(&acc_full_bar[a], 1);
+            ptx::mbar_init(&acc_empty_bar[a], 8); // four TSTORE warps in each CTA of the pair
+        }
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(tmem_base_slot, kTmemCols);
+        ptx::tmem_relinquish_alloc_permit_pair();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_arrive(); // the peer's barriers must exist before anything is signalled across the pair
+    ptx::cluster_wait();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_base_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TLOAD role (both CTAs)
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
+                int mi, ni;
+                tile_coords(tile, p, mi, ni);
+                const int row_a = mi * kPairBlockM + static_cast<int>(cta_rank) * kBlockM;
+                const int row_b = ni * kPairBlockN + static_cast<int>(cta_rank) * (kPairBlockN / 2);
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    ok = bounded_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, ST_PRODUCER_TIMEOUT);
+                    if (!ok) {
+                        break;
+                    }
+                    if (leader) {
+                        ptx::mbar_arrive_expect_tx(&full_bar[stage], 2u * L::kStageBytes);
+                    }
+                    const uint32_t full_addr = ptx::map_to_cta(ptx::smem_u32(&full_bar[stage]), 0);
+                    ptx::tma_load_2d_pair(smem + L::kAOff + stage * L::kABytes, &tmap_a, full_addr, kb * kBlockKElems,
+                                          row_a);
+                    ptx::tma_load_2d_pair(smem + L::kBOff + stage * L::kBBytes, &tmap_b, full_addr, kb * kBlockKElems,
+                                          row_b);
+                    if constexpr (KIND == KIND_MXF8) {
+                        // scale atoms: A rows of this CTA (row block 2*mi + rank), B columns of the whole tile
+                        const uint8_t* sfa_src =
+                            p.sfa + (static_cast<size_t>(kb) * (2 * p.m_tiles) + 2 * mi + cta_rank) * 512;
+                        const uint8_t* sfb_src = p.sfb + (static_cast<size_t>(kb) * p.n_tiles + ni) * 1024;
+                        asm volatile(
+                            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+                                "r"(ptx::smem_u32(smem + L::kSfaOff + stage * L::kSfaBytes)),
+                            "l"(reinterpret_cast<uint64_t>(sfa_src)), "r"(512), "r"(full_addr)
+                            : "memory");
+                        asm volatile(
+                            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+                                "r"(ptx::smem_u32(smem + L::kSfbOff + stage * L::kSfbBytes)),
+                            "l"(reinterpret_cast<uint64_t>(sfb_src)), "r"(1024), "r"(full_addr)
+                            : "memory");
+                    }
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- TMATMUL / TMATMUL_ACC role (leader only)
+        if (leader && lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
+                ok = bounded_wait(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag, p.status, ST_MMA_ACC_TIMEOUT);
+                if (!ok) {
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kAccCols);
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    ok = bounded_wait(&full_bar[stage], phase, abort_flag, p.status, ST_MMA_FULL_TIMEOUT);
+                    if (!ok) {
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_base = ptx::smem_u32(smem + L::kAOff + stage * L::kABytes);
+                    const uint32_t b_base = ptx::smem_u32(smem + L::kBOff + stage * L::kBBytes);
+                    if constexpr (KIND == KIND_MXF8) {
+                        const uint32_t sfa_base = ptx::smem_u32(smem + L::kSfaOff + stage * L::kSfaBytes);
+                        const uint32_t sfb_base = ptx::smem_u32(smem + L::kSfbOff + stage * L::kSfbBytes);
+                        ptx::tmem_cp_32x128b_warpx4_pair(tmem_base + kSfaCol,
+                                                         ptx::make_smem_desc(sfa_base, 0, 128, ptx::kSwizzleNone));
+                        ptx::tmem_cp_32x128b_warpx4_pair(tmem_base + kSfbCol,
+                                                         ptx::make_smem_desc(sfb_base, 0, 128, ptx::kSwizzleNone));
+                        ptx::tmem_cp_32x128b_warpx4_pair(tmem_base + kSfbCol + 4u,
+                                                         ptx::make_smem_desc(sfb_base + 512u, 0, 128, ptx::kSwizzleNone));
+                    }
+#pragma unroll
+                    for (int kk = 0; kk < kBlockKBytes / kUmmaKBytes; ++kk) {
+                        const uint64_t a_desc =
+                            ptx::make_smem_desc(a_base + kk * kUmmaKBytes, 16, 1024, ptx::kSwizzle128B);
+                        const uint64_t b_desc =
+                            ptx::make_smem_desc(b_base + kk * kUmmaKBytes, 16, 1024, ptx::kSwizzle128B);
+                        const uint32_t accumulate = (kb > 0 || kk > 0) ? 1u : 0u;
+                        if constexpr (KIND == KIND_F16) {
+                            ptx::umma_f16_pair(d_tmem, a_desc, b_desc, p.idesc, accumulate);
+                        } else if constexpr (KIND == KIND_I8) {
+                            ptx::umma_i8_pair(d_tmem, a_desc, b_desc, p.idesc, accumulate);
+                        } else {
+                            const uint32_t idesc =
+                                p.idesc | (static_cast<uint32_t>(kk) << 4) | (static_cast<uint32_t>(kk) << 29);
+                            ptx::umma_mxf8_pair(d_tmem, a_desc, b_desc, idesc, tmem_base + kSfaCol, tmem_base + kSfbCol,
+                                                accumulate);
+                        }
+                    }
+                    ptx::umma_commit_pair(&empty_bar[stage], 0x3);
+                    if (++stage == STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) {
+                    break;
+                }
+                ptx::umma_commit_pair(&acc_full_bar[acc], 0x3);
+                if (++acc == kNumAcc) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- TSTORE role (both CTAs)
+        const int quarter = warp & 3;
+        const int esize = (EPI == EPI_F32 || EPI == EPI_S32) ? 4 : 2;
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0) && (((p.ldc * esize) & 15) == 0);
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
+            int mi, ni;
+            tile_coords(tile, p, mi, ni);
+            ok = bounded_wait(&acc_full_bar[acc], acc_phase, abort_flag, p.status, ST_EPILOGUE_TIMEOUT);
+            ok = __all_sync(0xFFFFFFFFu, ok);
+            if (!ok) {
+                break;
+            }
+            ptx::tc_fence_after_sync();
+            const int row = mi * kPairBlockM + static_cast<int>(cta_rank) * kBlockM + quarter * 32 + lane;
+            float s_row = 1.0f;
+            if constexpr (EPI == EPI_DEQ_BF16) {
+                s_row = (row < p.m) ? __ldg(p.s_row + row) : 0.0f;
+            }
+            const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * kAccCols) +
+                                   (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+            for (int chunk = 0; chunk < kPairBlockN / 32; ++chunk) {
+                const int col0 = ni * kPairBlockN + chunk * 32;
+                if (col0 >= p.n) {
+                    break;
+                }
+                uint32_t v[32];
+                ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(chunk * 32), v);
+                ptx::tmem_ld_wait();
+                store_chunk<EPI>(v, p, row, col0, vec_ok, s_row);
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                if (leader) {
+                    ptx::mbar_arrive(&acc_empty_bar[acc]);
+                } else {
+                    ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&acc_empty_bar[acc]), 0));
+                }
+            }
+            if (++acc == kNumAcc) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
+        }
+    }
+
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag != 0) {
+        for (int i = 0; i < 2000; ++i) {
+            __nanosleep(1000);
+        }
+    }
+    // Both CTAs are past every access to the other's shared memory, barriers and tensor memory.
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+    }
+}
+
+} // namespace pto_b200

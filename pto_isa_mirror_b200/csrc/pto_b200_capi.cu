@@ -4,6 +4,7 @@
 
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -11,6 +12,7 @@
 #include <cuda_runtime.h>
 
 #include "gemm_tile_loop.cuh"
+#include "gemm_tile_loop_2cta.cuh"
 
 #if !defined(__CUDA_ARCH_LIST__)
 #error "pto_b200 is built with nvcc for sm_100a only"
@@ -33,6 +35,7 @@ struct DeviceInfo {
     int err = PTO_B200_OK;
     int sm_count = 0;
     int* status_ptr = nullptr;
+    bool force_1cta = false; // PTO_B200_FORCE_1CTA=1 in the environment: never pick the two-CTA kernels
 };
 
 constexpr int kMaxDevices = 64;
@@ -69,6 +72,8 @@ int device_info(DeviceInfo** out)
             d.err = PTO_B200_EDEVICE;
         } else {
             cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+            const char* force = std::getenv("PTO_B200_FORCE_1CTA");
+            d.force_1cta = (force != nullptr && force[0] == '1');
             d.err = note_cuda(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status_ptr), g_status_word),
                               "cudaGetSymbolAddress(status)");
             if (d.err == PTO_B200_OK && g_encode == nullptr) {
@@ -141,7 +146,8 @@ int make_tensor_map(CUtensorMap* map, int dtype, const void* base, long long row
 
 // tcgen05 instruction descriptor (dense kinds): D format [4,6), A format [7,10), B format [10,13),
 // A/B major bits 15/16 (0 = K-major), N >> 3 at [17,23), M >> 4 at [24,29).
-uint32_t make_idesc(int c_fmt, int a_fmt, int b_fmt, bool b_mn_major, int n, bool block_scaled_e8m0)
+uint32_t make_idesc(int c_fmt, int a_fmt, int b_fmt, bool b_mn_major, int n, bool block_scaled_e8m0,
+                    int m_inst = kBlockM)
 {
     uint32_t d = 0;
     if (!block_scaled_e8m0) {
@@ -154,9 +160,14 @@ uint32_t make_idesc(int c_fmt, int a_fmt, int b_fmt, bool b_mn_major, int n, boo
     if (block_scaled_e8m0) {
         d |= 1u << 23; // scale format e8m0
     }
-    d |= static_cast<uint32_t>(kBlockM >> 4) << 24;
+    d |= static_cast<uint32_t>(m_inst >> 4) << 24;
     return d;
 }
+
+struct Problem {
+    int m, n, k;
+    long long lda, ldb, ldc;
+};
 
 template <int KIND, int BLOCK_N, int EPI, bool B_MN>
 int launch_variant(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
@@ -192,6 +203,57 @@ int launch_block_n(int block_n, cudaStream_t stream, const CUtensorMap& ta, cons
     return launch_variant<KIND, 256, EPI, B_MN>(stream, ta, tb, p, sm_count);
 }
 
+// Two-CTA kernels: 256 x 256 tiles on clusters of two CTAs. Returns -1 when the problem should stay on the
+// one-CTA kernel (fewer tiles than CTA pairs the device can hold at once), otherwise a PTO_B200 code.
+template <int KIND, int EPI>
+int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, const Problem& q)
+{
+    constexpr int STAGES = 6;
+    using L = PairSmemLayout<KIND, STAGES>;
+    auto kernel = gemm_tile_loop_2cta<KIND, STAGES, EPI>;
+    static std::atomic<int> max_clusters[kMaxDevices];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(kNumThreads, 1, 1);
+    cfg.dynamicSmemBytes = L::kTotal;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = max_clusters[dev].load(std::memory_order_acquire);
+    if (clusters == 0) {
+        if (int rc = note_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal),
+                               "cudaFuncSetAttribute(pair)")) {
+            return rc;
+        }
+        cfg.gridDim = dim3(2, 1, 1);
+        int n = 0;
+        if (int rc = note_cuda(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg), "cudaOccupancyMaxActiveClusters")) {
+            return rc;
+        }
+        clusters = n > 0 ? n : -1;
+        max_clusters[dev].store(clusters, std::memory_order_release);
+    }
+    if (clusters < 0) {
+        return -1;
+    }
+    p.m_tiles = (q.m + kPairBlockM - 1) / kPairBlockM;
+    p.n_tiles = (q.n + kPairBlockN - 1) / kPairBlockN;
+    p.group_m = 8;
+    const int tiles = p.m_tiles * p.n_tiles;
+    if (tiles < clusters) {
+        return -1;
+    }
+    cfg.gridDim = dim3(2 * clusters, 1, 1);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return note_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, p), "gemm_tile_loop_2cta launch");
+}
+
 // 128-wide tiles when 256-wide ones would leave SMs without work and the narrower split fills more of them.
 int pick_block_n(int m, int n, int sm_count)
 {
@@ -203,10 +265,6 @@ int pick_block_n(int m, int n, int sm_count)
     return (t256 < sm_count) ? 128 : 256;
 }
 
-struct Problem {
-    int m, n, k;
-    long long lda, ldb, ldc;
-};
 
 int check_common(const void* out, const void* a, const void* b, const Problem& q, int a_es, int b_es, bool b_nd)
 {
@@ -288,11 +346,40 @@ extern "C" int pto_b200_gemm(void* stream, uint8_t* out, const uint8_t* src0, co
         }
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int fmt = (in_dtype == PTO_B200_BF16) ? 1 : 0;
+    if (!b_nd && !dev->force_1cta && m > kBlockM) {
+        // CTA pairs on 256 x 256 tiles when there are enough tiles to occupy every pair
+        CUtensorMap tb_half;
+        if (int rc = make_tensor_map(&tb_half, in_dtype, src1, n, k, ldb, kelems, kPairBlockN / 2)) {
+            return rc;
+        }
+        GemmParams pp = p;
+        int rc = -1;
+        if (is8) {
+            pp.idesc = make_idesc(2, 1, 1, false, kPairBlockN, false, kPairBlockM);
+            rc = launch_pair<KIND_I8, EPI_S32>(s, ta, tb_half, pp, q);
+        } else {
+            pp.idesc = make_idesc(1, fmt, fmt, false, kPairBlockN, false, kPairBlockM);
+            switch (out_dtype) {
+                case PTO_B200_F32:
+                    rc = launch_pair<KIND_F16, EPI_F32>(s, ta, tb_half, pp, q);
+                    break;
+                case PTO_B200_BF16:
+                    rc = launch_pair<KIND_F16, EPI_BF16>(s, ta, tb_half, pp, q);
+                    break;
+                default:
+                    rc = launch_pair<KIND_F16, EPI_F16>(s, ta, tb_half, pp, q);
+                    break;
+            }
+        }
+        if (rc != -1) {
+            return rc;
+        }
+    }
     if (is8) {
         p.idesc = make_idesc(2 /*S32*/, 1 /*S8*/, 1 /*S8*/, false, block_n, false);
         return launch_block_n<KIND_I8, EPI_S32, false>(block_n, s, ta, tb, p, dev->sm_count);
     }
-    const int fmt = (in_dtype == PTO_B200_BF16) ? 1 : 0;
     p.idesc = make_idesc(1 /*F32*/, fmt, fmt, b_nd, block_n, false);
     if (b_nd) {
         switch (out_dtype) {
@@ -341,6 +428,18 @@ extern "C" int pto_b200_gemm_s8_dequant(void* stream, uint8_t* out, const uint8_
     }
     if (int rc = make_tensor_map(&tb, PTO_B200_S8, src1, n, k, ldb, kBlockKBytes, block_n)) {
         return rc;
+    }
+    if (!dev->force_1cta && m > kBlockM) {
+        CUtensorMap tb_half;
+        if (int rc = make_tensor_map(&tb_half, PTO_B200_S8, src1, n, k, ldb, kBlockKBytes, kPairBlockN / 2)) {
+            return rc;
+        }
+        GemmParams pp = p;
+        pp.idesc = make_idesc(2, 1, 1, false, kPairBlockN, false, kPairBlockM);
+        const int rc = launch_pair<KIND_I8, EPI_DEQ_BF16>(static_cast<cudaStream_t>(stream), ta, tb_half, pp, q);
+        if (rc != -1) {
+            return rc;
+        }
     }
     return launch_block_n<KIND_I8, EPI_DEQ_BF16, false>(block_n, static_cast<cudaStream_t>(stream), ta, tb, p,
                                                         dev->sm_count);
@@ -502,3 +601,4 @@ extern "C" const char* pto_b200_error_string(int code)
 extern "C" const char* pto_b200_last_cuda_error(void) { return t_cuda_error; }
 
 extern "C" unsigned long long pto_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+

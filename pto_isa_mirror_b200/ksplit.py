@@ -58,13 +58,16 @@ class KSplitGemmAllReduce:
 
     def __init__(self, m: int, n: int, group: Optional[dist.ProcessGroup] = None, panels: int = 4,
                  mode: str = "rs_ag", device: Optional[torch.device] = None,
-                 gemm_fn: Optional[Callable] = None, cast_fn: Optional[Callable] = None):
+                 gemm_fn: Optional[Callable] = None, cast_fn: Optional[Callable] = None, single_rank: bool = False):
         if mode not in ("allreduce", "rs_ag"):
             raise ValueError("mode must be 'allreduce' or 'rs_ag'")
         self.m, self.n = m, n
         self.group = group
-        self.world_size = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        # single_rank: this instance multiplies the unsplit product on its own GPU and issues no collective, even
+        # inside an initialised process group (the one-GPU base case measured next to a multi-rank run)
+        distributed = dist.is_initialized() and not single_rank
+        self.world_size = dist.get_world_size(group) if distributed else 1
+        self.rank = dist.get_rank(group) if distributed else 0
         self.mode = mode if self.world_size > 1 else "allreduce"
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.on_cuda = self.device.type == "cuda"
