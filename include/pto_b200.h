@@ -50,7 +50,8 @@ enum {
     PTO_B200_EWORKSPACE = 4,  /* workspace missing, misaligned or too small                        */
     PTO_B200_ECUDA = 5,       /* a CUDA runtime / driver call failed (see pto_b200_last_cuda_error)*/
     PTO_B200_EDEVICE = 6,     /* current device is not compute capability 10.0                     */
-    PTO_B200_ETIMEOUT = 7     /* a kernel gave up on a bounded wait (see pto_b200_device_status)   */
+    PTO_B200_ETIMEOUT = 7,    /* a kernel gave up on a bounded wait (see pto_b200_device_status)   */
+    PTO_B200_ESCRATCH = 8     /* problem needs more than PTO_B200_MX_STATIC_SCRATCH_BYTES of built-in scratch */
 };
 
 /*
@@ -99,6 +100,34 @@ int pto_b200_gemm_mx(void* stream, uint8_t* out, const uint8_t* src0, const uint
                      int b_dtype, int out_dtype);
 
 size_t pto_b200_gemm_mx_workspace_bytes(int m, int n, int k);
+
+/*
+ * pto_b200_gemm_mx without a workspace argument. No counterpart in the reference (its launchers never need
+ * scratch); it exists for callers that have no way to obtain device memory at the moment of the call:
+ *   - code that keeps the reference's exact launcher shape, LaunchMxMatmul(out, src0, src1, src2, src3, stream),
+ *     and therefore has nowhere to pass a sixth buffer;
+ *   - processes whose device memory was handed out in full at start-up (a serving process that reserves the whole
+ *     HBM for its own pool), where a cudaMalloc made later fails or stalls the device.
+ * The re-tiled scale factors go into an array that lives inside this library's device image
+ * (PTO_B200_MX_STATIC_SCRATCH_BYTES, held on every GPU that loads the library until the process exits), so this
+ * call allocates nothing: no cudaMalloc, no cudaFree, no allocating library routine.
+ *
+ * Limits and rules:
+ *   - pto_b200_gemm_mx_workspace_bytes(m, n, k) must not exceed PTO_B200_MX_STATIC_SCRATCH_BYTES, otherwise the call
+ *     returns PTO_B200_ESCRATCH and launches nothing (8 MiB covers 16384 x 8192 x 8192 and 6144^3).
+ *   - The first call on each device looks up the array's device address (one cudaGetSymbolAddress with that device
+ *     current). Make that first call outside any stream capture.
+ *   - All calls on a device share the one array, and it keeps whatever the previous call left there. Each call
+ *     rewrites every byte it later reads, so nothing has to be cleared; but two calls whose kernels can overlap on
+ *     the GPU (different streams, no event between them) race on it. Serialise them, or use pto_b200_gemm_mx with
+ *     separate workspaces.
+ * Arguments, results and error codes are otherwise those of pto_b200_gemm_mx.
+ */
+#define PTO_B200_MX_STATIC_SCRATCH_BYTES (8u * 1024u * 1024u)
+int pto_b200_gemm_mx_static(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1,
+                            const uint8_t* src2, const uint8_t* src3, int m, int n, int k, long long lda,
+                            long long ldb, long long ldc, long long ld_sfa, long long ld_sfb, int a_dtype,
+                            int b_dtype, int out_dtype);
 
 /*
  * fp32 -> bf16 cast (round to nearest even) of `count` contiguous elements: the TSTORE cast applied to the

@@ -16,7 +16,8 @@ F16, BF16, F32, S8, S32, E4M3, E5M2 = range(7)
 # pto_b200_b_layout
 B_DN, B_ND = 0, 1
 # return codes
-OK, EINVAL, EALIGN, EDTYPE, EWORKSPACE, ECUDA, EDEVICE, ETIMEOUT = range(8)
+OK, EINVAL, EALIGN, EDTYPE, EWORKSPACE, ECUDA, EDEVICE, ETIMEOUT, ESCRATCH = range(9)
+MX_STATIC_SCRATCH_BYTES = 8 * 1024 * 1024
 
 # every symbol include/pto_b200.h declares: name -> (restype, argtypes)
 _u8p = ctypes.c_void_p
@@ -34,6 +35,10 @@ SYMBOLS = {
          _i, _i, _i],
     ),
     "pto_b200_gemm_mx_workspace_bytes": (ctypes.c_size_t, [_i, _i, _i]),
+    "pto_b200_gemm_mx_static": (
+        _i,
+        [ctypes.c_void_p, _u8p, _u8p, _u8p, _u8p, _u8p, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _i, _i, _i],
+    ),
     "pto_b200_cast_f32_to_bf16": (_i, [ctypes.c_void_p, _u8p, _u8p, _ll]),
     "call_kernel": (None, [ctypes.c_uint32, ctypes.c_void_p, _u8p, _u8p, _u8p]),
     "pto_b200_device_status": (_i, [ctypes.POINTER(_i)]),

@@ -593,6 +593,8 @@ extern "C" const char* pto_b200_error_string(int code)
             return "current device is not an sm_100 GPU";
         case PTO_B200_ETIMEOUT:
             return "a kernel gave up on a bounded wait";
+        case PTO_B200_ESCRATCH:
+            return "problem needs more scratch than the library's built-in static array (PTO_B200_MX_STATIC_SCRATCH_BYTES)";
         default:
             return "unknown error code";
     }
@@ -602,3 +604,76 @@ extern "C" const char* pto_b200_last_cuda_error(void) { return t_cuda_error; }
 
 extern "C" unsigned long long pto_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// MX GEMM for callers that cannot allocate device memory.
+//
+// Some users of this library have no buffer to give as the scale-factor workspace and no way to get one when they
+// call: a launcher that must keep the reference's six-argument LaunchMxMatmul shape, or a process that gave all of
+// its device memory to its own pool at start-up so that a later cudaMalloc fails or stalls the GPU. For them the
+// scratch is this array inside the library's device image. It costs PTO_B200_MX_STATIC_SCRATCH_BYTES on every GPU
+// that loads the library, for the life of the process.
+//
+// g_mx_static_scratch, as written in host code, is only the host-side handle of the symbol, not a device address;
+// the address a kernel can use comes from cudaGetSymbolAddress, asked once per device with that device current.
+// Every call shares the array and finds the previous call's bytes in it. The re-tile kernels overwrite every atom
+// the GEMM kernel reads (rows and K blocks past the end included), so nothing needs clearing; calls that can
+// overlap on the GPU race on it and must be serialised by the caller.
+namespace pto_b200 {
+namespace {
+
+static __device__ __align__(256) uint8_t g_mx_static_scratch[PTO_B200_MX_STATIC_SCRATCH_BYTES];
+
+struct StaticScratch {
+    bool ready = false;
+    int err = PTO_B200_OK;
+    uint8_t* ptr = nullptr;
+};
+StaticScratch g_static_scratch[kMaxDevices];
+
+// First use on the current device: resolve the device address of the array. Later uses return the cached pointer.
+int static_scratch_for_current_device(uint8_t** out)
+{
+    int dev = 0;
+    if (int rc = note_cuda(cudaGetDevice(&dev), "cudaGetDevice")) {
+        return rc;
+    }
+    if (dev < 0 || dev >= kMaxDevices) {
+        return PTO_B200_EDEVICE;
+    }
+    std::lock_guard<std::mutex> lock(g_mutex);
+    StaticScratch& s = g_static_scratch[dev];
+    if (!s.ready) {
+        void* p = nullptr;
+        s.err = note_cuda(cudaGetSymbolAddress(&p, g_mx_static_scratch), "cudaGetSymbolAddress(mx static scratch)");
+        s.ptr = static_cast<uint8_t*>(p);
+        if (s.err == PTO_B200_OK && s.ptr == nullptr) {
+            s.err = PTO_B200_ECUDA;
+        }
+        s.ready = true;
+    }
+    *out = s.ptr;
+    return s.err;
+}
+
+} // namespace
+} // namespace pto_b200
+
+extern "C" int pto_b200_gemm_mx_static(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1,
+                                       const uint8_t* src2, const uint8_t* src3, int m, int n, int k, long long lda,
+                                       long long ldb, long long ldc, long long ld_sfa, long long ld_sfb, int a_dtype,
+                                       int b_dtype, int out_dtype)
+{
+    if (m <= 0 || n <= 0 || k <= 0) {
+        return PTO_B200_EINVAL;
+    }
+    if (pto_b200_gemm_mx_workspace_bytes(m, n, k) > static_cast<size_t>(PTO_B200_MX_STATIC_SCRATCH_BYTES)) {
+        return PTO_B200_ESCRATCH;
+    }
+    uint8_t* scratch = nullptr;
+    if (int rc = static_scratch_for_current_device(&scratch)) {
+        return rc;
+    }
+    return pto_b200_gemm_mx(stream, out, src0, src1, src2, src3, scratch, PTO_B200_MX_STATIC_SCRATCH_BYTES, m, n, k,
+                            lda, ldb, ldc, ld_sfa, ld_sfb, a_dtype, b_dtype, out_dtype);
+}

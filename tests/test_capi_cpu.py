@@ -32,7 +32,7 @@ def test_header_symbols_are_exported(lib):
 
 
 def test_error_strings(lib):
-    for code in range(8):
+    for code in range(9):
         assert lib.pto_b200_error_string(code)
     assert b"unknown" in lib.pto_b200_error_string(99)
 
