@@ -150,7 +150,7 @@ def mx_quantize_torch(x):
     return y.to(torch.float8_e4m3fn).view(torch.uint8).view(rows, k), e8m0.to(torch.uint8)
 
 
-def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=4, mode="rs_ag"):
+def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=4, mode="rs_ag", gemm_blocks=0):
     """Returns (step_fn, flops_per_step, working_set_bytes, launches_hint). step_fn(i) enqueues one pass."""
     import torch
 
@@ -212,7 +212,7 @@ def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=4, 
         b = _randn_scaled((n, kr), k, torch.bfloat16, gen, dev)
         out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
         op = KSplitGemmAllReduce(m, n, panels=panels if world > 1 else 1, mode=mode, device=dev,
-                                 single_rank=(world == 1))
+                                 single_rank=(world == 1), launch_block_count=gemm_blocks)
 
         def step(i):
             op.step(a, b, out)
@@ -361,6 +361,8 @@ def main():
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--panels", type=int, default=4)
     ap.add_argument("--mode", default="rs_ag", choices=["rs_ag", "allreduce"])
+    ap.add_argument("--gemm-blocks", type=int, default=0,
+                    help="K-split only: thread blocks (SMs) the GEMM may occupy beside the reduction, 0 = all")
     ap.add_argument("--no-extras", action="store_true", help="skip all_configs / cpu_baseline / e2e (profiling runs)")
     ap.add_argument("--cpu-budget", type=float, default=10.0)
     args = ap.parse_args()
@@ -396,7 +398,7 @@ def main():
     spec = WORKLOADS[name]
     peaks = load_peaks()
     step, flops, ws_bytes, sets = make_step(name, spec, dev, seed=1, world=world, rank=rank, panels=args.panels,
-                                            mode=args.mode)
+                                            mode=args.mode, gemm_blocks=args.gemm_blocks)
 
     launches0 = pto.launch_count()
     with ClockSampler(local_rank) as clk:
@@ -423,7 +425,8 @@ def main():
                    "l2": (f"rotating {sets} input/output sets, {ws_bytes / 2**20:.0f} MiB > 126 MiB L2"
                           if sets > 1 else f"working set {ws_bytes / 2**20:.0f} MiB > 126 MiB L2"),
                    "inputs": "seeded torch.randn on device, N(0,1)/sqrt(K)" if kind in ("dense", "ksplit") else "seeded",
-                   **({"parallelism": f"ksplit{world}", "panels": args.panels, "reduce": args.mode}
+                   **({"parallelism": f"ksplit{world}", "panels": args.panels, "reduce": args.mode,
+                       "gemm_blocks": args.gemm_blocks}
                       if kind == "ksplit" else {})},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak, "traffic": NCU_DRAM_TRAFFIC.get(name),

@@ -69,6 +69,16 @@ int pto_b200_gemm(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t
                   long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype, int b_layout);
 
 /*
+ * pto_b200_gemm with the number of thread blocks capped, the `launch_block_count` argument of the reference's
+ * launchGemmCompute (kernels/manual/a2a3/gemm_ar/gemm_compute_kernel.cpp:254-259): the GEMM then occupies at most
+ * that many SMs and leaves the rest to a communication kernel running beside it on another stream
+ * (kernels/manual/a2a3/gemm_ar/README.md:327 describes the same trade). 0 = use every SM.
+ */
+int pto_b200_gemm_ex(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, int m, int n, int k,
+                     long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype, int b_layout,
+                     int launch_block_count);
+
+/*
  * int8 x int8 -> int32 GEMM with the dequantising store fused:
  *   out[i][j] = bf16( (float(acc[i][j]) * s_col[j]) * s_row[i] ),  two separately rounded fp32 multiplies.
  * Replaces: TMATMUL/TMATMUL_ACC on int8 tiles + TSTORE_FP per-column dequant

@@ -25,6 +25,7 @@ _ll = ctypes.c_longlong
 _i = ctypes.c_int
 SYMBOLS = {
     "pto_b200_gemm": (_i, [ctypes.c_void_p, _u8p, _u8p, _u8p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i]),
+    "pto_b200_gemm_ex": (_i, [ctypes.c_void_p, _u8p, _u8p, _u8p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _i]),
     "pto_b200_gemm_s8_dequant": (
         _i,
         [ctypes.c_void_p, _u8p, _u8p, _u8p, ctypes.c_void_p, ctypes.c_void_p, _i, _i, _i, _ll, _ll, _ll],

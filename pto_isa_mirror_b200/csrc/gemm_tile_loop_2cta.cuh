@@ -40,6 +40,7 @@ struct PairSmemLayout {
 template <int KIND, int STAGES, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
     gemm_tile_loop_2cta(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                         const GemmParams p)
 {
     using L = PairSmemLayout<KIND, STAGES>;
@@ -116,20 +117,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                     ptx::tma_load_2d_pair(smem + L::kBOff + stage * L::kBBytes, &tmap_b, full_addr, kb * kBlockKElems,
                                           row_b);
                     if constexpr (KIND == KIND_MXF8) {
-                        // scale atoms: A rows of this CTA (row block 2*mi + rank), B columns of the whole tile
-                        const uint8_t* sfa_src =
-                            p.sfa + (static_cast<size_t>(kb) * (2 * p.m_tiles) + 2 * mi + cta_rank) * 512;
-                        const uint8_t* sfb_src = p.sfb + (static_cast<size_t>(kb) * p.n_tiles + ni) * 1024;
-                        asm volatile(
-                            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
-                                "r"(ptx::smem_u32(smem + L::kSfaOff + stage * L::kSfaBytes)),
-                            "l"(reinterpret_cast<uint64_t>(sfa_src)), "r"(512), "r"(full_addr)
-                            : "memory");
-                        asm volatile(
-                            "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
-                                "r"(ptx::smem_u32(smem + L::kSfbOff + stage * L::kSfbBytes)),
-                            "l"(reinterpret_cast<uint64_t>(sfb_src)), "r"(1024), "r"(full_addr)
-                            : "memory");
+                        // Scale atoms through tensor maps over the re-tiled workspace viewed as rows of 256 bytes
+                        // (an atom is two rows): A rows of this CTA (row block 2*mi + rank), B columns of the whole
+                        // tile (two atoms). The tensor form lets the bytes complete on the leader's barrier.
+                        const int sfa_row = (kb * (2 * p.m_tiles) + 2 * mi + static_cast<int>(cta_rank)) * 2;
+                        const int sfb_row = (kb * p.n_tiles + ni) * 4;
+                        ptx::tma_load_2d_pair(smem + L::kSfaOff + stage * L::kSfaBytes, &tmap_sfa, full_addr, 0,
+                                              sfa_row);
+                        ptx::tma_load_2d_pair(smem + L::kSfbOff + stage * L::kSfbBytes, &tmap_sfb, full_addr, 0,
+                                              sfb_row);
                     }
                     if (++stage == STAGES) {
                         stage = 0;

@@ -114,7 +114,7 @@ int elem_size(int dtype)
 
 // 2-D row-major view [rows, cols] with leading dimension ld (elements), 128-byte swizzled boxes.
 int make_tensor_map(CUtensorMap* map, int dtype, const void* base, long long rows, long long cols, long long ld,
-                    int box_cols, int box_rows)
+                    int box_cols, int box_rows, bool swizzle128 = true)
 {
     CUtensorMapDataType dt;
     switch (dtype) {
@@ -134,7 +134,8 @@ int make_tensor_map(CUtensorMap* map, int dtype, const void* base, long long row
     cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = g_encode(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         std::snprintf(t_cuda_error, sizeof(t_cuda_error), "cuTensorMapEncodeTiled failed with CUresult %d",
@@ -171,7 +172,7 @@ struct Problem {
 
 template <int KIND, int BLOCK_N, int EPI, bool B_MN>
 int launch_variant(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
-                   int sm_count)
+                   int sm_count, int block_limit = 0)
 {
     constexpr int STAGES = 4;
     using L = SmemLayout<KIND, BLOCK_N, STAGES>;
@@ -187,7 +188,10 @@ int launch_variant(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap
         attr_done[dev].store(1, std::memory_order_release);
     }
     const int tiles = p.m_tiles * p.n_tiles;
-    const int grid = tiles < sm_count ? tiles : sm_count;
+    int grid = tiles < sm_count ? tiles : sm_count;
+    if (block_limit > 0 && block_limit < grid) {
+        grid = block_limit;
+    }
     kernel<<<grid, kNumThreads, L::kTotal, stream>>>(ta, tb, p);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return note_cuda(cudaGetLastError(), "gemm_tile_loop launch");
@@ -195,18 +199,19 @@ int launch_variant(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap
 
 template <int KIND, int EPI, bool B_MN>
 int launch_block_n(int block_n, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb,
-                   const GemmParams& p, int sm_count)
+                   const GemmParams& p, int sm_count, int block_limit = 0)
 {
     if (block_n == 128) {
-        return launch_variant<KIND, 128, EPI, B_MN>(stream, ta, tb, p, sm_count);
+        return launch_variant<KIND, 128, EPI, B_MN>(stream, ta, tb, p, sm_count, block_limit);
     }
-    return launch_variant<KIND, 256, EPI, B_MN>(stream, ta, tb, p, sm_count);
+    return launch_variant<KIND, 256, EPI, B_MN>(stream, ta, tb, p, sm_count, block_limit);
 }
 
 // Two-CTA kernels: 256 x 256 tiles on clusters of two CTAs. Returns -1 when the problem should stay on the
 // one-CTA kernel (fewer tiles than CTA pairs the device can hold at once), otherwise a PTO_B200 code.
 template <int KIND, int EPI>
-int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, const Problem& q)
+int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, const Problem& q,
+                const CUtensorMap* sfa_map = nullptr, const CUtensorMap* sfb_map = nullptr, int block_limit = 0)
 {
     constexpr int STAGES = 6;
     using L = PairSmemLayout<KIND, STAGES>;
@@ -249,9 +254,16 @@ int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& t
     if (tiles < clusters) {
         return -1;
     }
-    cfg.gridDim = dim3(2 * clusters, 1, 1);
+    int pairs = clusters;
+    if (block_limit > 0 && block_limit / 2 < pairs) {
+        pairs = block_limit / 2 > 0 ? block_limit / 2 : 1;
+    }
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
     g_launches.fetch_add(1, std::memory_order_relaxed);
-    return note_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, p), "gemm_tile_loop_2cta launch");
+    // the scale maps are only read by the block-scaled instantiations; the others get copies of the A map
+    const CUtensorMap& ma = sfa_map ? *sfa_map : ta;
+    const CUtensorMap& mb = sfb_map ? *sfb_map : ta;
+    return note_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, ma, mb, p), "gemm_tile_loop_2cta launch");
 }
 
 // 128-wide tiles when 256-wide ones would leave SMs without work and the narrower split fills more of them.
@@ -304,6 +316,16 @@ using namespace pto_b200;
 extern "C" int pto_b200_gemm(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, int m, int n, int k,
                              long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype, int b_layout)
 {
+    return pto_b200_gemm_ex(stream, out, src0, src1, m, n, k, lda, ldb, ldc, in_dtype, out_dtype, b_layout, 0);
+}
+
+extern "C" int pto_b200_gemm_ex(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, int m, int n,
+                                int k, long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype,
+                                int b_layout, int launch_block_count)
+{
+    if (launch_block_count < 0) {
+        return PTO_B200_EINVAL;
+    }
     const bool is16 = (in_dtype == PTO_B200_F16 || in_dtype == PTO_B200_BF16);
     const bool is8 = (in_dtype == PTO_B200_S8);
     if (!is16 && !is8) {
@@ -357,18 +379,18 @@ extern "C" int pto_b200_gemm(void* stream, uint8_t* out, const uint8_t* src0, co
         int rc = -1;
         if (is8) {
             pp.idesc = make_idesc(2, 1, 1, false, kPairBlockN, false, kPairBlockM);
-            rc = launch_pair<KIND_I8, EPI_S32>(s, ta, tb_half, pp, q);
+            rc = launch_pair<KIND_I8, EPI_S32>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count);
         } else {
             pp.idesc = make_idesc(1, fmt, fmt, false, kPairBlockN, false, kPairBlockM);
             switch (out_dtype) {
                 case PTO_B200_F32:
-                    rc = launch_pair<KIND_F16, EPI_F32>(s, ta, tb_half, pp, q);
+                    rc = launch_pair<KIND_F16, EPI_F32>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count);
                     break;
                 case PTO_B200_BF16:
-                    rc = launch_pair<KIND_F16, EPI_BF16>(s, ta, tb_half, pp, q);
+                    rc = launch_pair<KIND_F16, EPI_BF16>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count);
                     break;
                 default:
-                    rc = launch_pair<KIND_F16, EPI_F16>(s, ta, tb_half, pp, q);
+                    rc = launch_pair<KIND_F16, EPI_F16>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count);
                     break;
             }
         }
@@ -378,26 +400,26 @@ extern "C" int pto_b200_gemm(void* stream, uint8_t* out, const uint8_t* src0, co
     }
     if (is8) {
         p.idesc = make_idesc(2 /*S32*/, 1 /*S8*/, 1 /*S8*/, false, block_n, false);
-        return launch_block_n<KIND_I8, EPI_S32, false>(block_n, s, ta, tb, p, dev->sm_count);
+        return launch_block_n<KIND_I8, EPI_S32, false>(block_n, s, ta, tb, p, dev->sm_count, launch_block_count);
     }
     p.idesc = make_idesc(1 /*F32*/, fmt, fmt, b_nd, block_n, false);
     if (b_nd) {
         switch (out_dtype) {
             case PTO_B200_F32:
-                return launch_block_n<KIND_F16, EPI_F32, true>(block_n, s, ta, tb, p, dev->sm_count);
+                return launch_block_n<KIND_F16, EPI_F32, true>(block_n, s, ta, tb, p, dev->sm_count, launch_block_count);
             case PTO_B200_BF16:
-                return launch_block_n<KIND_F16, EPI_BF16, true>(block_n, s, ta, tb, p, dev->sm_count);
+                return launch_block_n<KIND_F16, EPI_BF16, true>(block_n, s, ta, tb, p, dev->sm_count, launch_block_count);
             default:
-                return launch_block_n<KIND_F16, EPI_F16, true>(block_n, s, ta, tb, p, dev->sm_count);
+                return launch_block_n<KIND_F16, EPI_F16, true>(block_n, s, ta, tb, p, dev->sm_count, launch_block_count);
         }
     }
     switch (out_dtype) {
         case PTO_B200_F32:
-            return launch_block_n<KIND_F16, EPI_F32, false>(block_n, s, ta, tb, p, dev->sm_count);
+            return launch_block_n<KIND_F16, EPI_F32, false>(block_n, s, ta, tb, p, dev->sm_count, launch_block_count);
         case PTO_B200_BF16:
-            return launch_block_n<KIND_F16, EPI_BF16, false>(block_n, s, ta, tb, p, dev->sm_count);
+            return launch_block_n<KIND_F16, EPI_BF16, false>(block_n, s, ta, tb, p, dev->sm_count, launch_block_count);
         default:
-            return launch_block_n<KIND_F16, EPI_F16, false>(block_n, s, ta, tb, p, dev->sm_count);
+            return launch_block_n<KIND_F16, EPI_F16, false>(block_n, s, ta, tb, p, dev->sm_count, launch_block_count);
     }
 }
 
@@ -450,10 +472,11 @@ extern "C" size_t pto_b200_gemm_mx_workspace_bytes(int m, int n, int k)
     if (m <= 0 || n <= 0 || k <= 0) {
         return 0;
     }
-    const size_t m_tiles = (static_cast<size_t>(m) + kBlockM - 1) / kBlockM;
+    // 128-row scale blocks, counted in pairs so that either tile shape (128- or 256-row tiles) fits
+    const size_t m_blocks = 2 * ((static_cast<size_t>(m) + 255) / 256);
     const size_t n_blocks = 2 * ((static_cast<size_t>(n) + 255) / 256);
     const size_t k_blocks = (static_cast<size_t>(k) + kBlockKBytes - 1) / kBlockKBytes;
-    return k_blocks * (m_tiles + n_blocks) * 512;
+    return k_blocks * (m_blocks + n_blocks) * 512;
 }
 
 extern "C" int pto_b200_gemm_mx(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1,
@@ -484,39 +507,77 @@ extern "C" int pto_b200_gemm_mx(void* stream, uint8_t* out, const uint8_t* src0,
     if (int rc = device_info(&dev)) {
         return rc;
     }
-    const int block_n = pick_block_n(m, n, dev->sm_count);
-    GemmParams p;
-    fill_params(p, out, q, block_n, kBlockKBytes, dev->status_ptr);
-    const int n_blocks = p.n_tiles * (block_n / 128);
-    uint8_t* sfa_ws = workspace;
-    uint8_t* sfb_ws = workspace + static_cast<size_t>(p.k_blocks) * p.m_tiles * 512;
-    p.sfa = sfa_ws;
-    p.sfb = sfb_ws;
-    p.idesc = make_idesc(0, a_dtype == PTO_B200_E5M2 ? 1 : 0, b_dtype == PTO_B200_E5M2 ? 1 : 0, false, block_n, true);
-    CUtensorMap ta, tb;
-    if (int rc = make_tensor_map(&ta, a_dtype, src0, m, k, lda, kBlockKBytes, kBlockM)) {
-        return rc;
-    }
-    if (int rc = make_tensor_map(&tb, b_dtype, src1, n, k, ldb, kBlockKBytes, block_n)) {
-        return rc;
-    }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    {
-        const long long ta_items = static_cast<long long>(p.m_tiles) * p.k_blocks * 128;
-        const long long tb_items = static_cast<long long>(n_blocks) * p.k_blocks * 128;
+    const int a_fmt = a_dtype == PTO_B200_E5M2 ? 1 : 0;
+    const int b_fmt = b_dtype == PTO_B200_E5M2 ? 1 : 0;
+    // Re-tile the scales, then the GEMM. `pairs` picks the two-CTA kernel (256 x 256 tiles, scale row blocks in
+    // units of 128 rows: 2 per row-tile of A, 2 per column-tile of B) when the problem has enough tiles for it.
+    auto run = [&](bool pairs, int block_n) -> int {
+        GemmParams p;
+        fill_params(p, out, q, block_n, kBlockKBytes, dev->status_ptr);
+        int a_blocks = p.m_tiles;
+        int b_blocks = p.n_tiles * (block_n / 128);
+        if (pairs) {
+            p.m_tiles = (m + kPairBlockM - 1) / kPairBlockM;
+            p.n_tiles = (n + kPairBlockN - 1) / kPairBlockN;
+            a_blocks = 2 * p.m_tiles;
+            b_blocks = 2 * p.n_tiles;
+        }
+        uint8_t* sfa_ws = workspace;
+        uint8_t* sfb_ws = workspace + static_cast<size_t>(p.k_blocks) * a_blocks * 512;
+        p.sfa = sfa_ws;
+        p.sfb = sfb_ws;
+        CUtensorMap ta, tb, tsa, tsb;
+        if (int rc = make_tensor_map(&ta, a_dtype, src0, m, k, lda, kBlockKBytes, kBlockM)) {
+            return rc;
+        }
+        if (int rc = make_tensor_map(&tb, b_dtype, src1, n, k, ldb, kBlockKBytes, pairs ? kPairBlockN / 2 : block_n)) {
+            return rc;
+        }
+        if (pairs) {
+            const long long rows_a = static_cast<long long>(p.k_blocks) * a_blocks * 2;
+            const long long rows_b = static_cast<long long>(p.k_blocks) * b_blocks * 2;
+            if (int rc = make_tensor_map(&tsa, PTO_B200_S8, sfa_ws, rows_a, 256, 256, 256, 2, false)) {
+                return rc;
+            }
+            if (int rc = make_tensor_map(&tsb, PTO_B200_S8, sfb_ws, rows_b, 256, 256, 256, 4, false)) {
+                return rc;
+            }
+            // refuse early (before the re-tile kernels) if the pair kernel would decline this shape
+            p.idesc = make_idesc(0, a_fmt, b_fmt, false, kPairBlockN, true, kPairBlockM);
+        } else {
+            p.idesc = make_idesc(0, a_fmt, b_fmt, false, block_n, true);
+        }
+        const long long ta_items = static_cast<long long>(a_blocks) * p.k_blocks * 128;
+        const long long tb_items = static_cast<long long>(b_blocks) * p.k_blocks * 128;
         const int ga = static_cast<int>((ta_items + 255) / 256 < 4096 ? (ta_items + 255) / 256 : 4096);
         const int gb = static_cast<int>((tb_items + 255) / 256 < 4096 ? (tb_items + 255) / 256 : 4096);
-        retile_scales_kernel<<<ga, 256, 0, s>>>(src2, sfa_ws, m, k / 32, ld_sfa, p.m_tiles, p.k_blocks);
-        retile_scales_kernel<<<gb, 256, 0, s>>>(src3, sfb_ws, n, k / 32, ld_sfb, n_blocks, p.k_blocks);
+        retile_scales_kernel<<<ga, 256, 0, s>>>(src2, sfa_ws, m, k / 32, ld_sfa, a_blocks, p.k_blocks);
+        retile_scales_kernel<<<gb, 256, 0, s>>>(src3, sfb_ws, n, k / 32, ld_sfb, b_blocks, p.k_blocks);
         g_launches.fetch_add(2, std::memory_order_relaxed);
         if (int rc = note_cuda(cudaGetLastError(), "retile_scales launch")) {
             return rc;
         }
+        if (pairs) {
+            if (out_dtype == PTO_B200_F32) {
+                return launch_pair<KIND_MXF8, EPI_F32>(s, ta, tb, p, q, &tsa, &tsb);
+            }
+            return launch_pair<KIND_MXF8, EPI_BF16>(s, ta, tb, p, q, &tsa, &tsb);
+        }
+        if (out_dtype == PTO_B200_F32) {
+            return launch_block_n<KIND_MXF8, EPI_F32, false>(block_n, s, ta, tb, p, dev->sm_count);
+        }
+        return launch_block_n<KIND_MXF8, EPI_BF16, false>(block_n, s, ta, tb, p, dev->sm_count);
+    };
+    // the pair kernel wants at least one 256 x 256 tile per CTA pair (74 pairs on a full B200)
+    const long long tiles256 = static_cast<long long>((m + kPairBlockM - 1) / kPairBlockM) * ((n + kPairBlockN - 1) / kPairBlockN);
+    if (!dev->force_1cta && m > kBlockM && tiles256 >= dev->sm_count / 2) {
+        const int rc = run(true, kPairBlockN);
+        if (rc != -1) {
+            return rc;
+        }
     }
-    if (out_dtype == PTO_B200_F32) {
-        return launch_block_n<KIND_MXF8, EPI_F32, false>(block_n, s, ta, tb, p, dev->sm_count);
-    }
-    return launch_block_n<KIND_MXF8, EPI_BF16, false>(block_n, s, ta, tb, p, dev->sm_count);
+    return run(false, pick_block_n(m, n, dev->sm_count));
 }
 
 extern "C" int pto_b200_cast_f32_to_bf16(void* stream, uint8_t* out, const uint8_t* in, long long count)

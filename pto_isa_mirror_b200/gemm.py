@@ -42,8 +42,12 @@ def _require_cuda_2d(t: torch.Tensor, name: str) -> None:
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype = torch.float32, b_layout: int = B_DN,
-         out: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+         out: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None,
+         launch_block_count: int = 0) -> torch.Tensor:
     """C = A @ B with fp32 (int32 for int8 inputs) accumulation over the whole K.
+
+    ``launch_block_count`` caps the thread blocks (SMs) the GEMM occupies, 0 = all of them: the knob the reference's
+    launchGemmCompute has for leaving cores to the communication kernel that runs beside it.
 
     a: [M, K] row-major (row stride >= K). b: [N, K] when ``b_layout == B_DN`` (column-major K x N, the
     layout of gemm_performance) or [K, N] when ``B_ND`` (the CPU demo's layout). Strided views are allowed,
@@ -68,9 +72,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype = torch.float3
         if tuple(out.shape) != (m, n):
             raise ValueError("out has the wrong shape")
         out_dtype = out.dtype
-    rc = lib.pto_b200_gemm(_stream_ptr(stream), out.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, a.stride(0),
-                           b.stride(0), out.stride(0), _TORCH_TO_PTO[a.dtype], _TORCH_TO_PTO[out_dtype], b_layout)
-    _capi.check(rc, "pto_b200_gemm")
+    rc = lib.pto_b200_gemm_ex(_stream_ptr(stream), out.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, a.stride(0),
+                              b.stride(0), out.stride(0), _TORCH_TO_PTO[a.dtype], _TORCH_TO_PTO[out_dtype], b_layout,
+                              launch_block_count)
+    _capi.check(rc, "pto_b200_gemm_ex")
     return out
 
 

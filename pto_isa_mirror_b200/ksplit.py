@@ -58,7 +58,8 @@ class KSplitGemmAllReduce:
 
     def __init__(self, m: int, n: int, group: Optional[dist.ProcessGroup] = None, panels: int = 4,
                  mode: str = "rs_ag", device: Optional[torch.device] = None,
-                 gemm_fn: Optional[Callable] = None, cast_fn: Optional[Callable] = None, single_rank: bool = False):
+                 gemm_fn: Optional[Callable] = None, cast_fn: Optional[Callable] = None, single_rank: bool = False,
+                 launch_block_count: int = 0):
         if mode not in ("allreduce", "rs_ag"):
             raise ValueError("mode must be 'allreduce' or 'rs_ag'")
         self.m, self.n = m, n
@@ -79,7 +80,9 @@ class KSplitGemmAllReduce:
             from .gemm import cast_f32_to_bf16 as _cast
             from .gemm import gemm as _gemm
 
-            gemm_fn = gemm_fn or (lambda a, b, out: _gemm(a, b, out=out))
+            # launch_block_count: SMs the GEMM may occupy while a reduction runs beside it (0 = all)
+            lbc = launch_block_count if self.world_size > 1 else 0
+            gemm_fn = gemm_fn or (lambda a, b, out: _gemm(a, b, out=out, launch_block_count=lbc))
             cast_fn = cast_fn or (lambda src, out: _cast(src, out=out))
         self.gemm_fn, self.cast_fn = gemm_fn, cast_fn
         self.partial = torch.empty((m, n), dtype=torch.float32, device=self.device)

@@ -72,8 +72,8 @@ def test_argument_errors_come_before_any_launch(lib):
 def test_mx_workspace_size(lib):
     ws = lib.pto_b200_gemm_mx_workspace_bytes
     assert ws(0, 16, 32) == 0
-    # 512-byte atoms: one per (128-row block, 128-wide K block) of A plus two per 256-column tile of B
-    assert ws(128, 256, 128) == 512 * (1 + 2)
+    # 512-byte atoms per 128-wide K block: two per 256-row tile of A plus two per 256-column tile of B
+    assert ws(128, 256, 128) == 512 * (2 + 2)
     assert ws(129, 257, 129) == 2 * 512 * (2 + 4)
     assert ws(16384, 8192, 8192) == 64 * 512 * (128 + 64)
 
