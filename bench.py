@@ -150,7 +150,8 @@ def mx_quantize_torch(x):
     return y.to(torch.float8_e4m3fn).view(torch.uint8).view(rows, k), e8m0.to(torch.uint8)
 
 
-def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=4, mode="rs_ag", gemm_blocks=0):
+def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=4, mode="rs_ag", gemm_blocks=0,
+              reduce_blocks=48, panel_rows=None):
     """Returns (step_fn, flops_per_step, working_set_bytes, launches_hint). step_fn(i) enqueues one pass."""
     import torch
 
@@ -210,13 +211,48 @@ def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=4, 
         gen.manual_seed(seed * 1000 + rank)
         a = _randn_scaled((m, kr), k, torch.bfloat16, gen, dev)
         b = _randn_scaled((n, kr), k, torch.bfloat16, gen, dev)
-        out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
-        op = KSplitGemmAllReduce(m, n, panels=panels if world > 1 else 1, mode=mode, device=dev,
-                                 single_rank=(world == 1), launch_block_count=gemm_blocks)
+        op = None
+        reduce_used = mode
+        if world > 1 and mode == "p2p":
+            from pto_isa_mirror_b200.ksplit import KSplitGemmP2P
 
-        def step(i):
-            op.step(a, b, out)
+            align = 128 * world
+            rows = [h for h in (panel_rows or []) if h % align == 0]
+            try:
+                op = KSplitGemmP2P(m, n, panels=panels, device=dev, reduce_blocks=reduce_blocks,
+                                   launch_block_count=gemm_blocks,
+                                   panel_rows=rows if rows and len(rows) == len(panel_rows) else None)
+                ok = torch.ones(1, device=dev)
+            except Exception as e:  # noqa: BLE001  (peer mapping unavailable on this box: use the NCCL reduction)
+                if rank == 0:
+                    print(f"[bench] peer-memory reduction unavailable ({e!r}); using NCCL rs_ag", file=sys.stderr)
+                ok = torch.zeros(1, device=dev)
+                op = None
+            import torch.distributed as dist
 
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)      # every rank takes the same path
+            if ok.item() == 0:
+                op = None
+        if op is not None:
+            out = op.out
+            p2p = op
+
+            def step(i):
+                p2p.step(a, b)
+
+            step.panel_rows = [r1 - r0 for r0, r1 in op.panels]
+        else:
+            if mode == "p2p":
+                reduce_used = "rs_ag" if world > 1 else "none"
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+            nccl = KSplitGemmAllReduce(m, n, panels=panels if world > 1 else 1,
+                                       mode=mode if mode != "p2p" else "rs_ag", device=dev,
+                                       single_rank=(world == 1), launch_block_count=gemm_blocks)
+
+            def step(i):
+                nccl.step(a, b, out)
+
+        step.reduce_used = reduce_used
         step.tensors = (a, b, out)
         return step, flops, (m + n) * kr * 2 + m * n * 6, 1
     raise ValueError(kind)
@@ -360,7 +396,11 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--panels", type=int, default=4)
-    ap.add_argument("--mode", default="rs_ag", choices=["rs_ag", "allreduce"])
+    ap.add_argument("--mode", default="p2p", choices=["p2p", "rs_ag", "allreduce"],
+                    help="K-split reduction: p2p = this library's kernels over peer memory; rs_ag / allreduce = NCCL")
+    ap.add_argument("--reduce-blocks", type=int, default=148)
+    ap.add_argument("--panel-rows", default="",
+                    help="p2p mode: row-panel heights (comma separated); empty = --panels equal panels")
     ap.add_argument("--gemm-blocks", type=int, default=0,
                     help="K-split only: thread blocks (SMs) the GEMM may occupy beside the reduction, 0 = all")
     ap.add_argument("--no-extras", action="store_true", help="skip all_configs / cpu_baseline / e2e (profiling runs)")
@@ -398,7 +438,9 @@ def main():
     spec = WORKLOADS[name]
     peaks = load_peaks()
     step, flops, ws_bytes, sets = make_step(name, spec, dev, seed=1, world=world, rank=rank, panels=args.panels,
-                                            mode=args.mode, gemm_blocks=args.gemm_blocks)
+                                            mode=args.mode, gemm_blocks=args.gemm_blocks,
+                                            reduce_blocks=args.reduce_blocks,
+                                            panel_rows=[int(x) for x in args.panel_rows.split(",") if x])
 
     launches0 = pto.launch_count()
     with ClockSampler(local_rank) as clk:
@@ -425,8 +467,10 @@ def main():
                    "l2": (f"rotating {sets} input/output sets, {ws_bytes / 2**20:.0f} MiB > 126 MiB L2"
                           if sets > 1 else f"working set {ws_bytes / 2**20:.0f} MiB > 126 MiB L2"),
                    "inputs": "seeded torch.randn on device, N(0,1)/sqrt(K)" if kind in ("dense", "ksplit") else "seeded",
-                   **({"parallelism": f"ksplit{world}", "panels": args.panels, "reduce": args.mode,
-                       "gemm_blocks": args.gemm_blocks}
+                   **({"parallelism": f"ksplit{world}", "panels": args.panels,
+                       "reduce": getattr(step, "reduce_used", args.mode),
+                       "gemm_blocks": args.gemm_blocks, "reduce_blocks": args.reduce_blocks,
+                       "panel_rows": getattr(step, "panel_rows", None)}
                       if kind == "ksplit" else {})},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak, "traffic": NCU_DRAM_TRAFFIC.get(name),

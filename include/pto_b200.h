@@ -146,6 +146,33 @@ int pto_b200_gemm_mx_static(void* stream, uint8_t* out, const uint8_t* src0, con
 int pto_b200_cast_f32_to_bf16(void* stream, uint8_t* out, const uint8_t* in, long long count);
 
 /*
+ * K-split reduction over peer memory: the reduce-scatter / all-gather half of the reference's GEMM + AllReduce
+ * (kernels/manual/a2a3/gemm_ar/comm_kernel.cpp:165-210 reduce-scatter into the owner's window, :377-400 all-gather,
+ * :111-123 and :528-590 the TNOTIFY / TWAIT counters), one process per GPU, buffers mapped into every rank
+ * (the reference's HCCL windows; here any peer-mapped allocation, e.g. torch symmetric memory). All pointer arrays
+ * are HOST arrays of `world` device pointers, entry r = rank r's buffer as mapped in this process. Flag arrays hold
+ * PTO_B200_KSPLIT_FLAG_STRIDE ints per slot and must be zero before the first step; epochs start at 1 and only grow.
+ *
+ *   pto_b200_ksplit_signal : on the GEMM's stream after the GEMM of one row panel; stores ready[slot][rank] = epoch
+ *                            into every rank's ready-flag array.
+ *   pto_b200_ksplit_reduce : waits (bounded) until ready[slot][r] >= epoch for every r in this rank's array, then
+ *                            for rows [row0, row0 + rows) - this rank's shard of the panel - sums the fp32 partials
+ *                            of all ranks in rank order, casts to bf16 (round to nearest even) and stores the result
+ *                            into every rank's output; finally stores done[slot][rank] = epoch into every rank's
+ *                            done-flag array. launch_block_count = thread blocks to use (0 = 32).
+ *   pto_b200_ksplit_wait   : waits (bounded) until done[slot][r] >= epoch for slots [slot0, slot0 + slots), all r.
+ * A wait that gives up records a code in the status word (pto_b200_device_status) and the kernel returns.
+ */
+#define PTO_B200_KSPLIT_MAX_RANKS 8
+#define PTO_B200_KSPLIT_FLAG_STRIDE 8
+int pto_b200_ksplit_signal(void* stream, void* const* flag_arrays, int world, int rank, int slot, int epoch);
+int pto_b200_ksplit_reduce(void* stream, void* const* partial_ptrs, void* const* out_ptrs, void* const* done_arrays,
+                           const int* ready_local, int* cta_counters_local, int world, int rank, int slot, int epoch,
+                           long long row0, int rows, int n, long long ld_partial, long long ld_out,
+                           int launch_block_count);
+int pto_b200_ksplit_wait(void* stream, const int* done_local, int world, int slot0, int slots, int epoch);
+
+/*
  * Fixed-shape launchers with the reference's exact signatures.
  * call_kernel: demos/torch_jit/gemm/gemm_kernel.cpp:263-266 (fp16 6144^3, B column-major, fp32 out; blockDim ignored).
  */

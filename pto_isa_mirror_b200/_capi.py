@@ -41,6 +41,13 @@ SYMBOLS = {
         [ctypes.c_void_p, _u8p, _u8p, _u8p, _u8p, _u8p, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _i, _i, _i],
     ),
     "pto_b200_cast_f32_to_bf16": (_i, [ctypes.c_void_p, _u8p, _u8p, _ll]),
+    "pto_b200_ksplit_signal": (_i, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), _i, _i, _i, _i]),
+    "pto_b200_ksplit_reduce": (
+        _i,
+        [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p),
+         ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.c_void_p, _i, _i, _i, _i, _ll, _i, _i, _ll, _ll, _i],
+    ),
+    "pto_b200_ksplit_wait": (_i, [ctypes.c_void_p, ctypes.c_void_p, _i, _i, _i, _i]),
     "call_kernel": (None, [ctypes.c_uint32, ctypes.c_void_p, _u8p, _u8p, _u8p]),
     "pto_b200_device_status": (_i, [ctypes.POINTER(_i)]),
     "pto_b200_error_string": (ctypes.c_char_p, [_i]),

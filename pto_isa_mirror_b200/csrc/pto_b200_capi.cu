@@ -13,6 +13,7 @@
 
 #include "gemm_tile_loop.cuh"
 #include "gemm_tile_loop_2cta.cuh"
+#include "ksplit_reduce.cuh"
 
 #if !defined(__CUDA_ARCH_LIST__)
 #error "pto_b200 is built with nvcc for sm_100a only"
@@ -211,7 +212,8 @@ int launch_block_n(int block_n, cudaStream_t stream, const CUtensorMap& ta, cons
 // one-CTA kernel (fewer tiles than CTA pairs the device can hold at once), otherwise a PTO_B200 code.
 template <int KIND, int EPI>
 int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, const Problem& q,
-                const CUtensorMap* sfa_map = nullptr, const CUtensorMap* sfb_map = nullptr, int block_limit = 0)
+                const CUtensorMap* sfa_map = nullptr, const CUtensorMap* sfb_map = nullptr, int block_limit = 0,
+                const CUtensorMap* tb_tail = nullptr, uint32_t idesc_tail = 0)
 {
     constexpr int STAGES = 6;
     using L = PairSmemLayout<KIND, STAGES>;
@@ -259,11 +261,23 @@ int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& t
         pairs = block_limit / 2 > 0 ? block_limit / 2 : 1;
     }
     cfg.gridDim = dim3(2 * pairs, 1, 1);
+    // Last wave: when the leftover tiles would occupy at most half of the pairs, halve them along N so that the
+    // leftover spreads over (almost) all pairs and the wave takes about half as long.
+    const int leftover = tiles % pairs;
+    p.tail_first_unit = tiles;
+    p.tail_split = 1;
+    p.idesc_tail = p.idesc;
+    if (tb_tail != nullptr && leftover > 0 && 2 * leftover <= pairs) {
+        p.tail_first_unit = tiles - leftover;
+        p.tail_split = 2;
+        p.idesc_tail = idesc_tail;
+    }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     // the scale maps are only read by the block-scaled instantiations; the others get copies of the A map
     const CUtensorMap& ma = sfa_map ? *sfa_map : ta;
     const CUtensorMap& mb = sfb_map ? *sfb_map : ta;
-    return note_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, ma, mb, p), "gemm_tile_loop_2cta launch");
+    const CUtensorMap& mt = tb_tail ? *tb_tail : tb;
+    return note_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, mt, ma, mb, p), "gemm_tile_loop_2cta launch");
 }
 
 // 128-wide tiles when 256-wide ones would leave SMs without work and the narrower split fills more of them.
@@ -306,6 +320,8 @@ void fill_params(GemmParams& p, void* out, const Problem& q, int block_n, int k_
     p.k_blocks = (q.k + k_elems_per_block - 1) / k_elems_per_block;
     p.group_m = 16;
     p.status = status;
+    static const int debug = std::getenv("PTO_B200_DEBUG") ? std::atoi(std::getenv("PTO_B200_DEBUG")) : 0;
+    p.debug = debug;
 }
 
 } // namespace
@@ -375,22 +391,28 @@ extern "C" int pto_b200_gemm_ex(void* stream, uint8_t* out, const uint8_t* src0,
         if (int rc = make_tensor_map(&tb_half, in_dtype, src1, n, k, ldb, kelems, kPairBlockN / 2)) {
             return rc;
         }
+        CUtensorMap tb_tail;
+        if (int rc = make_tensor_map(&tb_tail, in_dtype, src1, n, k, ldb, kelems, kPairBlockN / 4)) {
+            return rc;
+        }
         GemmParams pp = p;
         int rc = -1;
+        const uint32_t idesc_tail = is8 ? make_idesc(2, 1, 1, false, kPairBlockN / 2, false, kPairBlockM)
+                                        : make_idesc(1, fmt, fmt, false, kPairBlockN / 2, false, kPairBlockM);
         if (is8) {
             pp.idesc = make_idesc(2, 1, 1, false, kPairBlockN, false, kPairBlockM);
-            rc = launch_pair<KIND_I8, EPI_S32>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count);
+            rc = launch_pair<KIND_I8, EPI_S32>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count, &tb_tail, idesc_tail);
         } else {
             pp.idesc = make_idesc(1, fmt, fmt, false, kPairBlockN, false, kPairBlockM);
             switch (out_dtype) {
                 case PTO_B200_F32:
-                    rc = launch_pair<KIND_F16, EPI_F32>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count);
+                    rc = launch_pair<KIND_F16, EPI_F32>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count, &tb_tail, idesc_tail);
                     break;
                 case PTO_B200_BF16:
-                    rc = launch_pair<KIND_F16, EPI_BF16>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count);
+                    rc = launch_pair<KIND_F16, EPI_BF16>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count, &tb_tail, idesc_tail);
                     break;
                 default:
-                    rc = launch_pair<KIND_F16, EPI_F16>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count);
+                    rc = launch_pair<KIND_F16, EPI_F16>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count, &tb_tail, idesc_tail);
                     break;
             }
         }
@@ -456,9 +478,15 @@ extern "C" int pto_b200_gemm_s8_dequant(void* stream, uint8_t* out, const uint8_
         if (int rc = make_tensor_map(&tb_half, PTO_B200_S8, src1, n, k, ldb, kBlockKBytes, kPairBlockN / 2)) {
             return rc;
         }
+        CUtensorMap tb_tail;
+        if (int rc = make_tensor_map(&tb_tail, PTO_B200_S8, src1, n, k, ldb, kBlockKBytes, kPairBlockN / 4)) {
+            return rc;
+        }
         GemmParams pp = p;
         pp.idesc = make_idesc(2, 1, 1, false, kPairBlockN, false, kPairBlockM);
-        const int rc = launch_pair<KIND_I8, EPI_DEQ_BF16>(static_cast<cudaStream_t>(stream), ta, tb_half, pp, q);
+        const int rc = launch_pair<KIND_I8, EPI_DEQ_BF16>(static_cast<cudaStream_t>(stream), ta, tb_half, pp, q, nullptr,
+                                                          nullptr, 0, &tb_tail,
+                                                          make_idesc(2, 1, 1, false, kPairBlockN / 2, false, kPairBlockM));
         if (rc != -1) {
             return rc;
         }
@@ -602,6 +630,104 @@ extern "C" int pto_b200_cast_f32_to_bf16(void* stream, uint8_t* out, const uint8
         reinterpret_cast<const float*>(in), reinterpret_cast<__nv_bfloat16*>(out), count);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return note_cuda(cudaGetLastError(), "cast_f32_bf16 launch");
+}
+
+// ---------------------------------------------------------------- K-split reduction over peer memory
+
+static int fill_peers(PeerPointers& pp, void* const* ptrs, int world)
+{
+    if (ptrs == nullptr) {
+        return PTO_B200_EINVAL;
+    }
+    for (int r = 0; r < kMaxRanks; ++r) {
+        pp.p[r] = (r < world) ? ptrs[r] : nullptr;
+        if (r < world && ptrs[r] == nullptr) {
+            return PTO_B200_EINVAL;
+        }
+    }
+    return PTO_B200_OK;
+}
+
+extern "C" int pto_b200_ksplit_signal(void* stream, void* const* flag_arrays, int world, int rank, int slot, int epoch)
+{
+    if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || slot < 0 || epoch < 1) {
+        return PTO_B200_EINVAL;
+    }
+    PeerPointers fp;
+    if (int rc = fill_peers(fp, flag_arrays, world)) {
+        return rc;
+    }
+    ksplit_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(fp, world, rank, slot, epoch);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return note_cuda(cudaGetLastError(), "ksplit_signal launch");
+}
+
+extern "C" int pto_b200_ksplit_reduce(void* stream, void* const* partial_ptrs, void* const* out_ptrs,
+                                      void* const* done_arrays, const int* ready_local, int* cta_counters_local,
+                                      int world, int rank, int slot, int epoch, long long row0, int rows, int n,
+                                      long long ld_partial, long long ld_out, int launch_block_count)
+{
+    if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || slot < 0 || epoch < 1 || rows <= 0 || n <= 0 ||
+        ready_local == nullptr || cta_counters_local == nullptr || ld_partial < n || ld_out < n || row0 < 0) {
+        return PTO_B200_EINVAL;
+    }
+    if ((n & 3) || (ld_partial & 3) || (ld_out & 3)) {
+        return PTO_B200_EALIGN;
+    }
+    KsplitReduceArgs a;
+    if (int rc = fill_peers(a.partial, partial_ptrs, world)) {
+        return rc;
+    }
+    if (int rc = fill_peers(a.out, out_ptrs, world)) {
+        return rc;
+    }
+    if (int rc = fill_peers(a.done, done_arrays, world)) {
+        return rc;
+    }
+    for (int r = 0; r < world; ++r) {
+        if ((reinterpret_cast<uintptr_t>(partial_ptrs[r]) & 15u) || (reinterpret_cast<uintptr_t>(out_ptrs[r]) & 7u)) {
+            return PTO_B200_EALIGN;
+        }
+    }
+    DeviceInfo* dev = nullptr;
+    if (int rc = device_info(&dev)) {
+        return rc;
+    }
+    a.ready = ready_local;
+    a.cta_counter = cta_counters_local;
+    a.status = dev->status_ptr;
+    a.world = world;
+    a.rank = rank;
+    a.slot = slot;
+    a.epoch = epoch;
+    a.row0 = row0;
+    a.rows = rows;
+    a.n = n;
+    a.ld_partial = ld_partial;
+    a.ld_out = ld_out;
+    const long long work = (static_cast<long long>(rows) * (n / 4) + 511) / 512;
+    int grid = launch_block_count > 0 ? launch_block_count : 32;
+    if (work < grid) {
+        grid = static_cast<int>(work);
+    }
+    ksplit_reduce_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return note_cuda(cudaGetLastError(), "ksplit_reduce launch");
+}
+
+extern "C" int pto_b200_ksplit_wait(void* stream, const int* done_local, int world, int slot0, int slots, int epoch)
+{
+    if (done_local == nullptr || world < 1 || world > kMaxRanks || slot0 < 0 || slots < 1 || epoch < 1) {
+        return PTO_B200_EINVAL;
+    }
+    DeviceInfo* dev = nullptr;
+    if (int rc = device_info(&dev)) {
+        return rc;
+    }
+    ksplit_wait_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(done_local, world, slot0, slots, epoch,
+                                                                         dev->status_ptr);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return note_cuda(cudaGetLastError(), "ksplit_wait launch");
 }
 
 extern "C" void call_kernel(uint32_t blockDim, void* stream, uint8_t* out, uint8_t* src0, uint8_t* src1)

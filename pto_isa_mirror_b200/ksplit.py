@@ -41,6 +41,21 @@ def panel_bounds(m: int, panels: int, align: int) -> List[tuple]:
     return out
 
 
+def panels_from_rows(m: int, rows: List[int], align: int) -> List[tuple]:
+    """Row panels of the given heights (each a multiple of ``align``; the last one absorbs what is left of m)."""
+    out, r0 = [], 0
+    for h in rows:
+        if h <= 0 or h % align:
+            raise ValueError(f"panel height {h} is not a positive multiple of {align}")
+        if r0 >= m:
+            break
+        out.append((r0, min(m, r0 + h)))
+        r0 += h
+    if r0 < m:
+        out.append((r0, m))
+    return out
+
+
 def k_slice(k: int, world_size: int, rank: int) -> tuple:
     """The K range owned by ``rank``: K is partitioned evenly (the benchmark's K-split configuration)."""
     if k % world_size != 0:
@@ -132,3 +147,107 @@ class KSplitGemmAllReduce:
             self.gemm_fn(a_slice[r0:r1], b_slice_dn, self.partial[r0:r1])
             self._reduce_panel(r0, r1, out)
         return out
+
+
+class KSplitGemmP2P:
+    """K-split GEMM with the reduction done by this library's own kernels over peer memory (NVLink / NVSwitch).
+
+    The structure is the reference's (kernels/manual/a2a3/gemm_ar): symmetric buffers mapped into every rank
+    (its HCCL windows; here torch symmetric memory), a per-rank GEMM stream and a communication stream
+    (main.cpp:761-800), reduce-scatter into the owner of each row shard followed by an all-gather of the finished
+    shard (comm_kernel.cpp:165-210, 377-400), and flag counters between the two (comm_kernel.cpp:111-123, 528-590).
+    Per row panel: GEMM -> fp32 partial in this rank's symmetric buffer -> ready flag to every rank; on the second
+    stream the owner of each shard pulls that shard from every rank, sums in rank order, casts to bf16 and pushes the
+    result into every rank's output, so a panel's reduction runs under the next panel's GEMM. No NCCL call is made
+    on the data path. Partials are double-buffered by step parity, so a rank never overwrites a partial that a
+    slower peer may still be reading.
+
+    ``step`` returns this rank's output buffer (symmetric memory, rewritten by the next ``step``).
+    """
+
+    def __init__(self, m: int, n: int, group: Optional[dist.ProcessGroup] = None, panels: int = 4,
+                 device: Optional[torch.device] = None, reduce_blocks: int = 148, launch_block_count: int = 0,
+                 panel_rows: Optional[List[int]] = None, reduce_blocks_last: int = 0):
+        """``panels`` equal row panels, or explicit ``panel_rows`` heights (decreasing heights leave only a small
+        reduction exposed after the last GEMM). ``reduce_blocks`` thread blocks run each reduction beside the next
+        GEMM; ``reduce_blocks_last`` (0 = four times that) run the last one, which has the GPU to itself."""
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _capi
+
+        if not dist.is_initialized():
+            raise RuntimeError("KSplitGemmP2P needs an initialised process group (one process per GPU)")
+        self._ctypes = ctypes
+        self._capi = _capi
+        self.lib = _capi.load()
+        self.group = group if group is not None else dist.group.WORLD
+        self.world_size = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world_size > 8:
+            raise ValueError("at most 8 ranks (one NVSwitch domain)")
+        self.m, self.n = m, n
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        align = 128 * self.world_size
+        self.panels = panels_from_rows(m, panel_rows, align) if panel_rows else panel_bounds(m, panels, align)
+        if any((r1 - r0) % self.world_size for r0, r1 in self.panels) or n % 4:
+            raise ValueError("panel rows must divide by the rank count and n by 4")
+        self.reduce_blocks = reduce_blocks
+        self.reduce_blocks_last = reduce_blocks_last if reduce_blocks_last > 0 else 4 * reduce_blocks
+        self.launch_block_count = launch_block_count
+        self.num_slots = 2 * len(self.panels)
+        # symmetric allocations: two fp32 partial buffers, the bf16 output, ready + done flags
+        self.partial = symm_mem.empty((2, m, n), dtype=torch.float32, device=self.device)
+        self.out = symm_mem.empty((m, n), dtype=torch.bfloat16, device=self.device)
+        self.flags = symm_mem.empty((2, self.num_slots, 8), dtype=torch.int32, device=self.device)
+        self.flags.zero_()
+        self.cta_counters = torch.zeros(self.num_slots, dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize(self.device)
+        h_partial = symm_mem.rendezvous(self.partial, self.group)
+        h_out = symm_mem.rendezvous(self.out, self.group)
+        h_flags = symm_mem.rendezvous(self.flags, self.group)
+        self._handles = (h_partial, h_out, h_flags)
+        ws = self.world_size
+        PtrArray = ctypes.c_void_p * ws
+        pbytes = m * n * 4
+        self._partial_ptrs = [PtrArray(*[int(h_partial.buffer_ptrs[r]) + b * pbytes for r in range(ws)]) for b in (0, 1)]
+        self._out_ptrs = PtrArray(*[int(h_out.buffer_ptrs[r]) for r in range(ws)])
+        fbytes = self.num_slots * 8 * 4
+        self._ready_ptrs = PtrArray(*[int(h_flags.buffer_ptrs[r]) for r in range(ws)])
+        self._done_ptrs = PtrArray(*[int(h_flags.buffer_ptrs[r]) + fbytes for r in range(ws)])
+        self._ready_local = self.flags[0].data_ptr()
+        self._done_local = self.flags[1].data_ptr()
+        self.epoch = 0
+        self.comm_stream = torch.cuda.Stream(device=self.device)
+        self.events = [torch.cuda.Event() for _ in self.panels]
+        dist.barrier(self.group)          # every rank's flags are zero and mapped before anyone signals
+        torch.cuda.synchronize(self.device)
+
+    def step(self, a_slice: torch.Tensor, b_slice_dn: torch.Tensor) -> torch.Tensor:
+        from .gemm import gemm as _gemm
+
+        lib, check = self.lib, self._capi.check
+        self.epoch += 1
+        buf = self.epoch & 1
+        partial = self.partial[buf]
+        main = torch.cuda.current_stream(self.device)
+        ws, rank, npan = self.world_size, self.rank, len(self.panels)
+        self.comm_stream.wait_stream(main)
+        for i, (r0, r1) in enumerate(self.panels):
+            slot = buf * npan + i
+            _gemm(a_slice[r0:r1], b_slice_dn, out=partial[r0:r1], launch_block_count=self.launch_block_count)
+            check(lib.pto_b200_ksplit_signal(main.cuda_stream, self._ready_ptrs, ws, rank, slot, self.epoch),
+                  "pto_b200_ksplit_signal")
+            self.events[i].record(main)
+            self.comm_stream.wait_event(self.events[i])
+            shard = (r1 - r0) // ws
+            check(lib.pto_b200_ksplit_reduce(self.comm_stream.cuda_stream, self._partial_ptrs[buf], self._out_ptrs,
+                                             self._done_ptrs, self._ready_local, self.cta_counters.data_ptr(), ws, rank,
+                                             slot, self.epoch, r0 + rank * shard, shard, self.n, self.n, self.n,
+                                             self.reduce_blocks_last if i == npan - 1 else self.reduce_blocks),
+                  "pto_b200_ksplit_reduce")
+        check(lib.pto_b200_ksplit_wait(self.comm_stream.cuda_stream, self._done_local, ws, buf * npan, npan, self.epoch),
+              "pto_b200_ksplit_wait")
+        main.wait_stream(self.comm_stream)
+        return self.out

@@ -10,7 +10,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from pto_isa_mirror_b200 import gen_data as gd
-from pto_isa_mirror_b200.ksplit import KSplitGemmAllReduce, k_slice, panel_bounds
+from pto_isa_mirror_b200.ksplit import KSplitGemmAllReduce, k_slice, panel_bounds, panels_from_rows
 
 
 def test_panel_bounds():
@@ -21,6 +21,14 @@ def test_panel_bounds():
     covered = panel_bounds(5000, 3, 256)
     assert covered[0][0] == 0 and covered[-1][1] == 5000
     assert all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
+
+
+def test_panels_from_rows():
+    assert panels_from_rows(8192, [4096, 2048, 1024, 1024], 1024) == [(0, 4096), (4096, 6144), (6144, 7168), (7168, 8192)]
+    assert panels_from_rows(8192, [6144], 1024) == [(0, 6144), (6144, 8192)]          # the remainder becomes a panel
+    assert panels_from_rows(2048, [1024, 1024, 1024], 1024) == [(0, 1024), (1024, 2048)]
+    with pytest.raises(ValueError):
+        panels_from_rows(8192, [1000], 1024)
 
 
 def test_k_slice():

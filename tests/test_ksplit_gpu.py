@@ -1,4 +1,4 @@
-"""K-split GEMM + allreduce on real GPUs over NCCL (needs at least two GPUs; skipped otherwise)."""
+"""K-split GEMM + allreduce on real GPUs, NCCL and peer-memory reductions (needs at least two GPUs; skipped otherwise)."""
 import os
 import socket
 
@@ -32,18 +32,35 @@ def _worker(rank, world, port, mode, m, n, k, result_dir):
         k0, k1 = k_slice(k, world, rank)
         a = torch.from_numpy(a_bits.view(np.int16)).to(dev).view(torch.bfloat16)
         b = torch.from_numpy(b_bits.view(np.int16)).to(dev).view(torch.bfloat16)
-        op = KSplitGemmAllReduce(m, n, panels=2, mode=mode, device=dev)
-        out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
-        for _ in range(2):                      # twice: buffers and streams are reused across steps
-            op.step(a[:, k0:k1], b[:, k0:k1], out)
+        if mode == "p2p":
+            from pto_isa_mirror_b200.ksplit import KSplitGemmP2P
+
+            op = KSplitGemmP2P(m, n, panels=2, device=dev, reduce_blocks=8)
+            for _ in range(3):                  # three steps: both partial buffers and growing epochs
+                out = op.step(a[:, k0:k1], b[:, k0:k1])
+        else:
+            op = KSplitGemmAllReduce(m, n, panels=2, mode=mode, device=dev)
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+            for _ in range(2):                  # twice: buffers and streams are reused across steps
+                op.step(a[:, k0:k1], b[:, k0:k1], out)
         torch.cuda.synchronize(dev)
         assert pto.device_status() == 0
+        if mode == "p2p":
+            # the reduction is a rank-ordered fp32 sum of the ranks' GEMM partials followed by one bf16 cast:
+            # recompute it from this rank's view of every partial (gathered with NCCL) and compare bit for bit
+            mine = pto.gemm(a[:, k0:k1], b[:, k0:k1], torch.float32)
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(parts, mine)
+            total = parts[0].clone()
+            for r in range(1, world):
+                total += parts[r]
+            assert torch.equal(pto.cast_f32_to_bf16(total), out)
         np.save(os.path.join(result_dir, f"out_{rank}.npy"), out.view(torch.int16).cpu().numpy())
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["allreduce", "rs_ag"])
+@pytest.mark.parametrize("mode", ["allreduce", "rs_ag", "p2p"])
 def test_ksplit_nccl(tmp_path, mode):
     import torch.multiprocessing as mp
 
@@ -63,3 +80,4 @@ def test_ksplit_nccl(tmp_path, mode):
     ref = oracle.gemm_f32acc(a_bits[:256], b_bits, oracle.BF16)     # unsplit sequential chain, first 256 rows
     got = gd.bf16_bits_to_f32(outs[0][:256])
     assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-3 + 2.0 ** -8   # dense tolerance + one bf16 rounding
+
