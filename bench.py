@@ -151,7 +151,7 @@ def mx_quantize_torch(x):
 
 
 def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=4, mode="rs_ag", gemm_blocks=0,
-              reduce_blocks=48, panel_rows=None):
+              reduce_blocks=48, panel_rows=None, use_multicast=True, gemm_streams=2):
     """Returns (step_fn, flops_per_step, working_set_bytes, launches_hint). step_fn(i) enqueues one pass."""
     import torch
 
@@ -220,7 +220,8 @@ def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=4, 
             rows = [h for h in (panel_rows or []) if h % align == 0]
             try:
                 op = KSplitGemmP2P(m, n, panels=panels, device=dev, reduce_blocks=reduce_blocks,
-                                   launch_block_count=gemm_blocks,
+                                   launch_block_count=gemm_blocks, use_multicast=use_multicast,
+                                   gemm_streams=gemm_streams,
                                    panel_rows=rows if rows and len(rows) == len(panel_rows) else None)
                 ok = torch.ones(1, device=dev)
             except Exception as e:  # noqa: BLE001  (peer mapping unavailable on this box: use the NCCL reduction)
@@ -241,6 +242,7 @@ def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=4, 
                 p2p.step(a, b)
 
             step.panel_rows = [r1 - r0 for r0, r1 in op.panels]
+            reduce_used = "p2p_nvls_multimem" if op.multicast else "p2p_peer_loads"
         else:
             if mode == "p2p":
                 reduce_used = "rs_ag" if world > 1 else "none"
@@ -395,10 +397,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
-    ap.add_argument("--panels", type=int, default=4)
+    ap.add_argument("--panels", type=int, default=8)
     ap.add_argument("--mode", default="p2p", choices=["p2p", "rs_ag", "allreduce"],
                     help="K-split reduction: p2p = this library's kernels over peer memory; rs_ag / allreduce = NCCL")
-    ap.add_argument("--reduce-blocks", type=int, default=148)
+    ap.add_argument("--reduce-blocks", type=int, default=32)
+    ap.add_argument("--gemm-streams", type=int, default=2, help="p2p mode: streams the panel GEMMs alternate between")
+    ap.add_argument("--no-multicast", action="store_true", help="p2p mode: plain peer loads instead of NVLS multimem")
     ap.add_argument("--panel-rows", default="",
                     help="p2p mode: row-panel heights (comma separated); empty = --panels equal panels")
     ap.add_argument("--gemm-blocks", type=int, default=0,
@@ -440,7 +444,8 @@ def main():
     step, flops, ws_bytes, sets = make_step(name, spec, dev, seed=1, world=world, rank=rank, panels=args.panels,
                                             mode=args.mode, gemm_blocks=args.gemm_blocks,
                                             reduce_blocks=args.reduce_blocks,
-                                            panel_rows=[int(x) for x in args.panel_rows.split(",") if x])
+                                            panel_rows=[int(x) for x in args.panel_rows.split(",") if x],
+                                            use_multicast=not args.no_multicast, gemm_streams=args.gemm_streams)
 
     launches0 = pto.launch_count()
     with ClockSampler(local_rank) as clk:
@@ -470,6 +475,7 @@ def main():
                    **({"parallelism": f"ksplit{world}", "panels": args.panels,
                        "reduce": getattr(step, "reduce_used", args.mode),
                        "gemm_blocks": args.gemm_blocks, "reduce_blocks": args.reduce_blocks,
+                       "gemm_streams": args.gemm_streams,
                        "panel_rows": getattr(step, "panel_rows", None)}
                       if kind == "ksplit" else {})},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",

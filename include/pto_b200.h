@@ -160,6 +160,10 @@ int pto_b200_cast_f32_to_bf16(void* stream, uint8_t* out, const uint8_t* in, lon
  *                            of all ranks in rank order, casts to bf16 (round to nearest even) and stores the result
  *                            into every rank's output; finally stores done[slot][rank] = epoch into every rank's
  *                            done-flag array. launch_block_count = thread blocks to use (0 = 32).
+ *                            multicast_partial / multicast_out: NVSwitch multicast addresses of the same partial /
+ *                            output buffers (NVLS), or null. With them the sum is formed inside the switch
+ *                            (multimem.ld_reduce, the switch's own fixed order) and the result is broadcast with one
+ *                            multimem.st; without them plain peer loads are summed in rank order and stored per rank.
  *   pto_b200_ksplit_wait   : waits (bounded) until done[slot][r] >= epoch for slots [slot0, slot0 + slots), all r.
  * A wait that gives up records a code in the status word (pto_b200_device_status) and the kernel returns.
  */
@@ -169,7 +173,7 @@ int pto_b200_ksplit_signal(void* stream, void* const* flag_arrays, int world, in
 int pto_b200_ksplit_reduce(void* stream, void* const* partial_ptrs, void* const* out_ptrs, void* const* done_arrays,
                            const int* ready_local, int* cta_counters_local, int world, int rank, int slot, int epoch,
                            long long row0, int rows, int n, long long ld_partial, long long ld_out,
-                           int launch_block_count);
+                           int launch_block_count, const void* multicast_partial, void* multicast_out);
 int pto_b200_ksplit_wait(void* stream, const int* done_local, int world, int slot0, int slots, int epoch);
 
 /*

@@ -45,7 +45,8 @@ SYMBOLS = {
     "pto_b200_ksplit_reduce": (
         _i,
         [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p),
-         ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.c_void_p, _i, _i, _i, _i, _ll, _i, _i, _ll, _ll, _i],
+         ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.c_void_p, _i, _i, _i, _i, _ll, _i, _i, _ll, _ll, _i,
+         ctypes.c_void_p, ctypes.c_void_p],
     ),
     "pto_b200_ksplit_wait": (_i, [ctypes.c_void_p, ctypes.c_void_p, _i, _i, _i, _i]),
     "call_kernel": (None, [ctypes.c_uint32, ctypes.c_void_p, _u8p, _u8p, _u8p]),

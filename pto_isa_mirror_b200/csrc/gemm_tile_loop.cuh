@@ -46,11 +46,6 @@ struct GemmParams {
     const uint8_t* sfa; // scale factors re-tiled to 512-byte atoms, index (k_block, m_block)
     const uint8_t* sfb; // same, index (k_block, n_block)
     int* status;
-    // CTA-pair kernels only: work units >= tail_first_unit are column slices of the last, partly filled wave
-    int tail_first_unit; // first unit of the sliced tail (= number of tiles when nothing is sliced)
-    int tail_split;      // column slices per tail tile (1 or 2)
-    uint32_t idesc_tail; // instruction descriptor for a slice (N = 256 / tail_split)
-    int debug;           // timing experiments only (PTO_B200_DEBUG): bit 0 = copy scales to TMEM only for k-block 0
 };
 
 constexpr int kBlockM = 128;

@@ -37,42 +37,11 @@ struct PairSmemLayout {
     static constexpr int kTotal = kMiscOff + 16 + 1024;
 };
 
-// One unit of work of a CTA pair: a whole 256 x 256 tile, or (in the last, partly filled wave of the grid) a
-// 256 x (256 / tail_split) column slice of one, so that the leftover tiles spread over all pairs.
-struct PairUnit {
-    int mi, ni;
-    int n_off;   // first column of the slice inside the tile
-    int n_width; // 256, or 128 for a slice
-    bool tail;
-};
-
-__device__ __forceinline__ bool pair_unit(int u, const GemmParams& p, PairUnit& w)
-{
-    const int total_tiles = p.m_tiles * p.n_tiles;
-    if (u < p.tail_first_unit) {
-        tile_coords(u, p, w.mi, w.ni);
-        w.n_off = 0;
-        w.n_width = kPairBlockN;
-        w.tail = false;
-        return true;
-    }
-    const int t = u - p.tail_first_unit;
-    const int tile = p.tail_first_unit + t / p.tail_split;
-    if (tile >= total_tiles) {
-        return false;
-    }
-    tile_coords(tile, p, w.mi, w.ni);
-    w.n_width = kPairBlockN / p.tail_split;
-    w.n_off = (t % p.tail_split) * w.n_width;
-    w.tail = (p.tail_split > 1);
-    return true;
-}
-
 template <int KIND, int STAGES, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
     gemm_tile_loop_2cta(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                        const __grid_constant__ CUtensorMap tmap_b_tail, const __grid_constant__ CUtensorMap tmap_sfa,
-                        const __grid_constant__ CUtensorMap tmap_sfb, const GemmParams p)
+                        const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                        const GemmParams p)
 {
     using L = PairSmemLayout<KIND, STAGES>;
     constexpr int kNumAcc = (KIND == KIND_MXF8) ? 1 : 2;
@@ -96,6 +65,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
     const bool leader = (cta_rank == 0);
     const int pair = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
+    const int total_tiles = p.m_tiles * p.n_tiles; // tiles of 256 x 256
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -128,27 +98,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            PairUnit w;
-            for (int u = pair; ok && pair_unit(u, p, w); u += num_pairs) {
-                const int mi = w.mi, ni = w.ni;
+            for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
+                int mi, ni;
+                tile_coords(tile, p, mi, ni);
                 const int row_a = mi * kPairBlockM + static_cast<int>(cta_rank) * kBlockM;
-                const int row_b = ni * kPairBlockN + w.n_off + static_cast<int>(cta_rank) * (w.n_width / 2);
-                // bytes both CTAs deliver per stage: A 128 rows + B n_width/2 rows each (+ scales)
-                const uint32_t tx_bytes =
-                    2u * static_cast<uint32_t>(L::kABytes + (w.n_width / 2) * kBlockKBytes + L::kSfaBytes + L::kSfbBytes);
-                const CUtensorMap* b_map = w.tail ? &tmap_b_tail : &tmap_b;
+                const int row_b = ni * kPairBlockN + static_cast<int>(cta_rank) * (kPairBlockN / 2);
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
                     ok = bounded_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, ST_PRODUCER_TIMEOUT);
                     if (!ok) {
                         break;
                     }
                     if (leader) {
-                        ptx::mbar_arrive_expect_tx(&full_bar[stage], tx_bytes);
+                        ptx::mbar_arrive_expect_tx(&full_bar[stage], 2u * L::kStageBytes);
                     }
                     const uint32_t full_addr = ptx::map_to_cta(ptx::smem_u32(&full_bar[stage]), 0);
                     ptx::tma_load_2d_pair(smem + L::kAOff + stage * L::kABytes, &tmap_a, full_addr, kb * kBlockKElems,
                                           row_a);
-                    ptx::tma_load_2d_pair(smem + L::kBOff + stage * L::kBBytes, b_map, full_addr, kb * kBlockKElems,
+                    ptx::tma_load_2d_pair(smem + L::kBOff + stage * L::kBBytes, &tmap_b, full_addr, kb * kBlockKElems,
                                           row_b);
                     if constexpr (KIND == KIND_MXF8) {
                         // Scale atoms through tensor maps over the re-tiled workspace viewed as rows of 256 bytes
@@ -176,16 +142,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            PairUnit w;
-            uint32_t sf_buf = 0;   // block-scaled look-ahead: which TMEM scale buffer the current k-block uses
-            bool sf_ready = false; // ... and whether its scales were already copied there
-            for (int u = pair; ok && pair_unit(u, p, w); u += num_pairs) {
-                const uint32_t unit_idesc = w.tail ? p.idesc_tail : p.idesc;
-                PairUnit w_next;
-                const bool next_unit = pair_unit(u + num_pairs, p, w_next);
-                (void)sf_buf;
-                (void)sf_ready;
-                (void)next_unit;
+            for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
                 ok = bounded_wait(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag, p.status, ST_MMA_ACC_TIMEOUT);
                 if (!ok) {
                     break;
@@ -200,45 +157,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                     ptx::tc_fence_after_sync();
                     const uint32_t a_base = ptx::smem_u32(smem + L::kAOff + stage * L::kABytes);
                     const uint32_t b_base = ptx::smem_u32(smem + L::kBOff + stage * L::kBBytes);
-                    uint32_t sf_col = 0; // column offset of the scale buffer this k-block's MMAs read
                     if constexpr (KIND == KIND_MXF8) {
-                        auto copy_scales = [&](int st, uint32_t col) {
-                            const uint32_t sfa_base = ptx::smem_u32(smem + L::kSfaOff + st * L::kSfaBytes);
-                            const uint32_t sfb_base = ptx::smem_u32(smem + L::kSfbOff + st * L::kSfbBytes);
-                            ptx::tmem_cp_32x128b_warpx4_pair(tmem_base + kSfaCol + col,
-                                                             ptx::make_smem_desc(sfa_base, 0, 128, ptx::kSwizzleNone));
-                            ptx::tmem_cp_32x128b_warpx4_pair(tmem_base + kSfbCol + col,
-                                                             ptx::make_smem_desc(sfb_base, 0, 128, ptx::kSwizzleNone));
-                            ptx::tmem_cp_32x128b_warpx4_pair(
-                                tmem_base + kSfbCol + col + 4u,
-                                ptx::make_smem_desc(sfb_base + 512u, 0, 128, ptx::kSwizzleNone));
-                        };
-                        if (!(p.debug & 2)) {
-                            if (kb == 0 || !(p.debug & 1)) {
-                                copy_scales(stage, 0);
-                            }
-                        } else {
-                            // Look-ahead: the scales of k-block i+1 are copied into the other TMEM scale buffer
-                            // before the MMAs of k-block i are issued, so the copy is not on the MMAs' critical path.
-                            if (!sf_ready) {
-                                copy_scales(stage, 16u * sf_buf);
-                            }
-                            const bool has_next = (kb + 1 < p.k_blocks) || next_unit;
-                            sf_ready = false;
-                            if (has_next) {
-                                const int ns = (stage + 1 == STAGES) ? 0 : stage + 1;
-                                const uint32_t nphase = (ns == 0) ? (phase ^ 1u) : phase;
-                                ok = bounded_wait(&full_bar[ns], nphase, abort_flag, p.status, ST_MMA_FULL_TIMEOUT);
-                                if (!ok) {
-                                    break;
-                                }
-                                ptx::tc_fence_after_sync();
-                                copy_scales(ns, 16u * (sf_buf ^ 1u));
-                                sf_ready = true;
-                            }
-                            sf_col = 16u * sf_buf;
-                            sf_buf ^= 1u;
-                        }
+                        const uint32_t sfa_base = ptx::smem_u32(smem + L::kSfaOff + stage * L::kSfaBytes);
+                        const uint32_t sfb_base = ptx::smem_u32(smem + L::kSfbOff + stage * L::kSfbBytes);
+                        ptx::tmem_cp_32x128b_warpx4_pair(tmem_base + kSfaCol,
+                                                         ptx::make_smem_desc(sfa_base, 0, 128, ptx::kSwizzleNone));
+                        ptx::tmem_cp_32x128b_warpx4_pair(tmem_base + kSfbCol,
+                                                         ptx::make_smem_desc(sfb_base, 0, 128, ptx::kSwizzleNone));
+                        ptx::tmem_cp_32x128b_warpx4_pair(tmem_base + kSfbCol + 4u,
+                                                         ptx::make_smem_desc(sfb_base + 512u, 0, 128, ptx::kSwizzleNone));
                     }
 #pragma unroll
                     for (int kk = 0; kk < kBlockKBytes / kUmmaKBytes; ++kk) {
@@ -248,14 +175,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                             ptx::make_smem_desc(b_base + kk * kUmmaKBytes, 16, 1024, ptx::kSwizzle128B);
                         const uint32_t accumulate = (kb > 0 || kk > 0) ? 1u : 0u;
                         if constexpr (KIND == KIND_F16) {
-                            ptx::umma_f16_pair(d_tmem, a_desc, b_desc, unit_idesc, accumulate);
+                            ptx::umma_f16_pair(d_tmem, a_desc, b_desc, p.idesc, accumulate);
                         } else if constexpr (KIND == KIND_I8) {
-                            ptx::umma_i8_pair(d_tmem, a_desc, b_desc, unit_idesc, accumulate);
+                            ptx::umma_i8_pair(d_tmem, a_desc, b_desc, p.idesc, accumulate);
                         } else {
                             const uint32_t idesc =
-                                unit_idesc | (static_cast<uint32_t>(kk) << 4) | (static_cast<uint32_t>(kk) << 29);
-                            ptx::umma_mxf8_pair(d_tmem, a_desc, b_desc, idesc, tmem_base + kSfaCol + sf_col,
-                                                tmem_base + kSfbCol + sf_col, accumulate);
+                                p.idesc | (static_cast<uint32_t>(kk) << 4) | (static_cast<uint32_t>(kk) << 29);
+                            ptx::umma_mxf8_pair(d_tmem, a_desc, b_desc, idesc, tmem_base + kSfaCol, tmem_base + kSfbCol,
+                                                accumulate);
                         }
                     }
                     ptx::umma_commit_pair(&empty_bar[stage], 0x3);
@@ -282,9 +209,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        PairUnit w;
-        for (int u = pair; ok && pair_unit(u, p, w); u += num_pairs) {
-            const int mi = w.mi, ni = w.ni;
+        for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
+            int mi, ni;
+            tile_coords(tile, p, mi, ni);
             ok = bounded_wait(&acc_full_bar[acc], acc_phase, abort_flag, p.status, ST_EPILOGUE_TIMEOUT);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) {
@@ -299,8 +226,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
             const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * kAccCols) +
                                    (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
-            for (int chunk = 0; chunk < w.n_width / 32; ++chunk) {
-                const int col0 = ni * kPairBlockN + w.n_off + chunk * 32;
+            for (int chunk = 0; chunk < kPairBlockN / 32; ++chunk) {
+                const int col0 = ni * kPairBlockN + chunk * 32;
                 if (col0 >= p.n) {
                     break;
                 }

@@ -47,6 +47,23 @@ __device__ __forceinline__ float4 ld_peer_f4(const float* ptr)
     return v;
 }
 
+// In-switch reduction (NVLS): one load through the multicast address returns the fp32 sum of the same 16 bytes of
+// every rank's buffer, added inside the NVSwitch; one store through it writes 8 bytes into every rank's buffer.
+__device__ __forceinline__ float4 multimem_ld_reduce_f4(const float* mc_ptr)
+{
+    float4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(mc_ptr)
+                 : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void multimem_st_b64(void* mc_ptr, uint64_t v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.b64 [%0], %1;" ::"l"(mc_ptr), "l"(v) : "memory");
+}
+
 __device__ __forceinline__ void st_release_sys(int* ptr, int v)
 {
     asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
@@ -84,6 +101,8 @@ struct KsplitReduceArgs {
     PeerPointers partial; // every rank's fp32 partial buffer [m, ld_partial] (peer pointers, own rank included)
     PeerPointers out;     // every rank's bf16 output [m, ld_out]
     PeerPointers done;    // every rank's done-flag array
+    const float* mc_partial; // multicast address of the partial buffers (NVLS), or null: sum with plain peer loads
+    void* mc_out;            // multicast address of the output buffers, or null: one plain store per rank
     const int* ready;     // this rank's ready-flag array
     int* cta_counter;     // local scratch: one int per slot, zero between uses
     int* status;
@@ -111,39 +130,71 @@ __global__ void __launch_bounds__(512) ksplit_reduce_kernel(const KsplitReduceAr
         const int n4 = a.n / 4;
         const long long total = static_cast<long long>(a.rows) * n4;
         const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-        for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += stride) {
-            const long long row = a.row0 + i / n4;
-            const int c = static_cast<int>(i % n4) * 4;
-            const long long src_off = row * a.ld_partial + c;
-            // all loads first (one per rank in flight), then a fixed summation order (rank 0, 1, ...): every element
-            // is reduced once, by its owner, so all ranks receive identical bits
-            float4 v[kMaxRanks];
+        const long long first = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+        if (a.mc_partial != nullptr) {
+            // NVLS path: the switch adds the ranks' values (its own fixed order) and one store reaches every rank.
+            // Four independent loads per thread keep enough requests in flight to cover the switch round trip.
+            constexpr int kUnroll = 4;
+            for (long long i0 = first; i0 < total; i0 += stride * kUnroll) {
+                float4 acc[kUnroll];
+                long long off[kUnroll];
 #pragma unroll
-            for (int r = 0; r < kMaxRanks; ++r) {
-                if (r < a.world) {
-                    v[r] = ld_peer_f4(static_cast<const float*>(a.partial.p[r]) + src_off);
+                for (int u = 0; u < kUnroll; ++u) {
+                    const long long i = i0 + u * stride;
+                    off[u] = -1;
+                    if (i < total) {
+                        const long long row = a.row0 + i / n4;
+                        const int c = static_cast<int>(i % n4) * 4;
+                        acc[u] = multimem_ld_reduce_f4(a.mc_partial + row * a.ld_partial + c);
+                        off[u] = row * a.ld_out + c;
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) {
+                    if (off[u] >= 0) {
+                        const __nv_bfloat162 lo = __floats2bfloat162_rn(acc[u].x, acc[u].y);
+                        const __nv_bfloat162 hi = __floats2bfloat162_rn(acc[u].z, acc[u].w);
+                        const uint64_t packed = static_cast<uint64_t>(*reinterpret_cast<const uint32_t*>(&lo)) |
+                                                (static_cast<uint64_t>(*reinterpret_cast<const uint32_t*>(&hi)) << 32);
+                        multimem_st_b64(static_cast<__nv_bfloat16*>(a.mc_out) + off[u], packed);
+                    }
                 }
             }
-            float4 acc = v[0];
+        } else {
+            for (long long i = first; i < total; i += stride) {
+                const long long row = a.row0 + i / n4;
+                const int c = static_cast<int>(i % n4) * 4;
+                const long long src_off = row * a.ld_partial + c;
+                // all loads first (one per rank in flight), then a fixed summation order (rank 0, 1, ...): every
+                // element is reduced once, by its owner, so all ranks receive identical bits
+                float4 v[kMaxRanks];
 #pragma unroll
-            for (int r = 1; r < kMaxRanks; ++r) {
-                if (r < a.world) {
-                    acc.x += v[r].x;
-                    acc.y += v[r].y;
-                    acc.z += v[r].z;
-                    acc.w += v[r].w;
+                for (int r = 0; r < kMaxRanks; ++r) {
+                    if (r < a.world) {
+                        v[r] = ld_peer_f4(static_cast<const float*>(a.partial.p[r]) + src_off);
+                    }
                 }
-            }
-            const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
-            const __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
-            uint2 packed;
-            packed.x = *reinterpret_cast<const uint32_t*>(&lo);
-            packed.y = *reinterpret_cast<const uint32_t*>(&hi);
-            const long long dst_off = row * a.ld_out + c;
+                float4 acc = v[0];
 #pragma unroll
-            for (int r = 0; r < kMaxRanks; ++r) {
-                if (r < a.world) {
-                    *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(a.out.p[r]) + dst_off) = packed;
+                for (int r = 1; r < kMaxRanks; ++r) {
+                    if (r < a.world) {
+                        acc.x += v[r].x;
+                        acc.y += v[r].y;
+                        acc.z += v[r].z;
+                        acc.w += v[r].w;
+                    }
+                }
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
+                const __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
+                uint2 packed;
+                packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+                packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+                const long long dst_off = row * a.ld_out + c;
+#pragma unroll
+                for (int r = 0; r < kMaxRanks; ++r) {
+                    if (r < a.world) {
+                        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(a.out.p[r]) + dst_off) = packed;
+                    }
                 }
             }
         }

@@ -212,10 +212,12 @@ int launch_block_n(int block_n, cudaStream_t stream, const CUtensorMap& ta, cons
 // one-CTA kernel (fewer tiles than CTA pairs the device can hold at once), otherwise a PTO_B200 code.
 template <int KIND, int EPI>
 int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, const Problem& q,
-                const CUtensorMap* sfa_map = nullptr, const CUtensorMap* sfb_map = nullptr, int block_limit = 0,
-                const CUtensorMap* tb_tail = nullptr, uint32_t idesc_tail = 0)
+                const CUtensorMap* sfa_map = nullptr, const CUtensorMap* sfb_map = nullptr, int block_limit = 0)
 {
-    constexpr int STAGES = 6;
+#ifndef PTO_B200_PAIR_STAGES
+#define PTO_B200_PAIR_STAGES 6
+#endif
+    constexpr int STAGES = (KIND == KIND_MXF8) ? 6 : PTO_B200_PAIR_STAGES;
     using L = PairSmemLayout<KIND, STAGES>;
     auto kernel = gemm_tile_loop_2cta<KIND, STAGES, EPI>;
     static std::atomic<int> max_clusters[kMaxDevices];
@@ -261,23 +263,11 @@ int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& t
         pairs = block_limit / 2 > 0 ? block_limit / 2 : 1;
     }
     cfg.gridDim = dim3(2 * pairs, 1, 1);
-    // Last wave: when the leftover tiles would occupy at most half of the pairs, halve them along N so that the
-    // leftover spreads over (almost) all pairs and the wave takes about half as long.
-    const int leftover = tiles % pairs;
-    p.tail_first_unit = tiles;
-    p.tail_split = 1;
-    p.idesc_tail = p.idesc;
-    if (tb_tail != nullptr && leftover > 0 && 2 * leftover <= pairs) {
-        p.tail_first_unit = tiles - leftover;
-        p.tail_split = 2;
-        p.idesc_tail = idesc_tail;
-    }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     // the scale maps are only read by the block-scaled instantiations; the others get copies of the A map
     const CUtensorMap& ma = sfa_map ? *sfa_map : ta;
     const CUtensorMap& mb = sfb_map ? *sfb_map : ta;
-    const CUtensorMap& mt = tb_tail ? *tb_tail : tb;
-    return note_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, mt, ma, mb, p), "gemm_tile_loop_2cta launch");
+    return note_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, ma, mb, p), "gemm_tile_loop_2cta launch");
 }
 
 // 128-wide tiles when 256-wide ones would leave SMs without work and the narrower split fills more of them.
@@ -320,8 +310,6 @@ void fill_params(GemmParams& p, void* out, const Problem& q, int block_n, int k_
     p.k_blocks = (q.k + k_elems_per_block - 1) / k_elems_per_block;
     p.group_m = 16;
     p.status = status;
-    static const int debug = std::getenv("PTO_B200_DEBUG") ? std::atoi(std::getenv("PTO_B200_DEBUG")) : 0;
-    p.debug = debug;
 }
 
 } // namespace
@@ -391,28 +379,22 @@ extern "C" int pto_b200_gemm_ex(void* stream, uint8_t* out, const uint8_t* src0,
         if (int rc = make_tensor_map(&tb_half, in_dtype, src1, n, k, ldb, kelems, kPairBlockN / 2)) {
             return rc;
         }
-        CUtensorMap tb_tail;
-        if (int rc = make_tensor_map(&tb_tail, in_dtype, src1, n, k, ldb, kelems, kPairBlockN / 4)) {
-            return rc;
-        }
         GemmParams pp = p;
         int rc = -1;
-        const uint32_t idesc_tail = is8 ? make_idesc(2, 1, 1, false, kPairBlockN / 2, false, kPairBlockM)
-                                        : make_idesc(1, fmt, fmt, false, kPairBlockN / 2, false, kPairBlockM);
         if (is8) {
             pp.idesc = make_idesc(2, 1, 1, false, kPairBlockN, false, kPairBlockM);
-            rc = launch_pair<KIND_I8, EPI_S32>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count, &tb_tail, idesc_tail);
+            rc = launch_pair<KIND_I8, EPI_S32>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count);
         } else {
             pp.idesc = make_idesc(1, fmt, fmt, false, kPairBlockN, false, kPairBlockM);
             switch (out_dtype) {
                 case PTO_B200_F32:
-                    rc = launch_pair<KIND_F16, EPI_F32>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count, &tb_tail, idesc_tail);
+                    rc = launch_pair<KIND_F16, EPI_F32>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count);
                     break;
                 case PTO_B200_BF16:
-                    rc = launch_pair<KIND_F16, EPI_BF16>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count, &tb_tail, idesc_tail);
+                    rc = launch_pair<KIND_F16, EPI_BF16>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count);
                     break;
                 default:
-                    rc = launch_pair<KIND_F16, EPI_F16>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count, &tb_tail, idesc_tail);
+                    rc = launch_pair<KIND_F16, EPI_F16>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count);
                     break;
             }
         }
@@ -478,15 +460,9 @@ extern "C" int pto_b200_gemm_s8_dequant(void* stream, uint8_t* out, const uint8_
         if (int rc = make_tensor_map(&tb_half, PTO_B200_S8, src1, n, k, ldb, kBlockKBytes, kPairBlockN / 2)) {
             return rc;
         }
-        CUtensorMap tb_tail;
-        if (int rc = make_tensor_map(&tb_tail, PTO_B200_S8, src1, n, k, ldb, kBlockKBytes, kPairBlockN / 4)) {
-            return rc;
-        }
         GemmParams pp = p;
         pp.idesc = make_idesc(2, 1, 1, false, kPairBlockN, false, kPairBlockM);
-        const int rc = launch_pair<KIND_I8, EPI_DEQ_BF16>(static_cast<cudaStream_t>(stream), ta, tb_half, pp, q, nullptr,
-                                                          nullptr, 0, &tb_tail,
-                                                          make_idesc(2, 1, 1, false, kPairBlockN / 2, false, kPairBlockM));
+        const int rc = launch_pair<KIND_I8, EPI_DEQ_BF16>(static_cast<cudaStream_t>(stream), ta, tb_half, pp, q);
         if (rc != -1) {
             return rc;
         }
@@ -665,7 +641,8 @@ extern "C" int pto_b200_ksplit_signal(void* stream, void* const* flag_arrays, in
 extern "C" int pto_b200_ksplit_reduce(void* stream, void* const* partial_ptrs, void* const* out_ptrs,
                                       void* const* done_arrays, const int* ready_local, int* cta_counters_local,
                                       int world, int rank, int slot, int epoch, long long row0, int rows, int n,
-                                      long long ld_partial, long long ld_out, int launch_block_count)
+                                      long long ld_partial, long long ld_out, int launch_block_count,
+                                      const void* multicast_partial, void* multicast_out)
 {
     if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || slot < 0 || epoch < 1 || rows <= 0 || n <= 0 ||
         ready_local == nullptr || cta_counters_local == nullptr || ld_partial < n || ld_out < n || row0 < 0) {
@@ -693,6 +670,11 @@ extern "C" int pto_b200_ksplit_reduce(void* stream, void* const* partial_ptrs, v
     if (int rc = device_info(&dev)) {
         return rc;
     }
+    if ((reinterpret_cast<uintptr_t>(multicast_partial) & 15u) || (reinterpret_cast<uintptr_t>(multicast_out) & 7u)) {
+        return PTO_B200_EALIGN;
+    }
+    a.mc_partial = static_cast<const float*>(multicast_partial);
+    a.mc_out = multicast_out;
     a.ready = ready_local;
     a.cta_counter = cta_counters_local;
     a.status = dev->status_ptr;

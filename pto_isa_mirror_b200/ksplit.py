@@ -166,8 +166,9 @@ class KSplitGemmP2P:
     """
 
     def __init__(self, m: int, n: int, group: Optional[dist.ProcessGroup] = None, panels: int = 4,
-                 device: Optional[torch.device] = None, reduce_blocks: int = 148, launch_block_count: int = 0,
-                 panel_rows: Optional[List[int]] = None, reduce_blocks_last: int = 0):
+                 device: Optional[torch.device] = None, reduce_blocks: int = 32, launch_block_count: int = 0,
+                 panel_rows: Optional[List[int]] = None, reduce_blocks_last: int = 0, use_multicast: bool = True,
+                 gemm_streams: int = 2):
         """``panels`` equal row panels, or explicit ``panel_rows`` heights (decreasing heights leave only a small
         reduction exposed after the last GEMM). ``reduce_blocks`` thread blocks run each reduction beside the next
         GEMM; ``reduce_blocks_last`` (0 = four times that) run the last one, which has the GPU to itself."""
@@ -216,11 +217,23 @@ class KSplitGemmP2P:
         fbytes = self.num_slots * 8 * 4
         self._ready_ptrs = PtrArray(*[int(h_flags.buffer_ptrs[r]) for r in range(ws)])
         self._done_ptrs = PtrArray(*[int(h_flags.buffer_ptrs[r]) + fbytes for r in range(ws)])
+        # NVSwitch multicast addresses (NVLS) of the partial and output buffers, when the platform maps them:
+        # the reduction then happens inside the switch (multimem.ld_reduce) and the result is broadcast by one store
+        mc_p = int(getattr(h_partial, "multicast_ptr", 0) or 0) if use_multicast else 0
+        mc_o = int(getattr(h_out, "multicast_ptr", 0) or 0) if use_multicast else 0
+        self.multicast = bool(mc_p and mc_o)
+        self._mc_partial = [mc_p + b * pbytes if self.multicast else None for b in (0, 1)]
+        self._mc_out = mc_o if self.multicast else None
         self._ready_local = self.flags[0].data_ptr()
         self._done_local = self.flags[1].data_ptr()
         self.epoch = 0
         self.comm_stream = torch.cuda.Stream(device=self.device)
+        # With two GEMM streams consecutive panels' persistent GEMM kernels overlap at their edges: the CTAs of panel
+        # p+1 start on the SMs that ran out of tiles in the last wave of panel p, so the partly filled last wave is
+        # paid once per step instead of once per panel.
+        self.aux_stream = torch.cuda.Stream(device=self.device) if gemm_streams > 1 else None
         self.events = [torch.cuda.Event() for _ in self.panels]
+        self.start_event = torch.cuda.Event()
         dist.barrier(self.group)          # every rank's flags are zero and mapped before anyone signals
         torch.cuda.synchronize(self.device)
 
@@ -234,18 +247,22 @@ class KSplitGemmP2P:
         main = torch.cuda.current_stream(self.device)
         ws, rank, npan = self.world_size, self.rank, len(self.panels)
         self.comm_stream.wait_stream(main)
+        if self.aux_stream is not None:
+            self.aux_stream.wait_stream(main)
         for i, (r0, r1) in enumerate(self.panels):
             slot = buf * npan + i
-            _gemm(a_slice[r0:r1], b_slice_dn, out=partial[r0:r1], launch_block_count=self.launch_block_count)
-            check(lib.pto_b200_ksplit_signal(main.cuda_stream, self._ready_ptrs, ws, rank, slot, self.epoch),
+            gs = self.aux_stream if (self.aux_stream is not None and i % 2 == 1) else main
+            _gemm(a_slice[r0:r1], b_slice_dn, out=partial[r0:r1], launch_block_count=self.launch_block_count, stream=gs)
+            check(lib.pto_b200_ksplit_signal(gs.cuda_stream, self._ready_ptrs, ws, rank, slot, self.epoch),
                   "pto_b200_ksplit_signal")
-            self.events[i].record(main)
+            self.events[i].record(gs)
             self.comm_stream.wait_event(self.events[i])
             shard = (r1 - r0) // ws
             check(lib.pto_b200_ksplit_reduce(self.comm_stream.cuda_stream, self._partial_ptrs[buf], self._out_ptrs,
                                              self._done_ptrs, self._ready_local, self.cta_counters.data_ptr(), ws, rank,
                                              slot, self.epoch, r0 + rank * shard, shard, self.n, self.n, self.n,
-                                             self.reduce_blocks_last if i == npan - 1 else self.reduce_blocks),
+                                             self.reduce_blocks_last if i == npan - 1 else self.reduce_blocks,
+                                             self._mc_partial[buf], self._mc_out),
                   "pto_b200_ksplit_reduce")
         check(lib.pto_b200_ksplit_wait(self.comm_stream.cuda_stream, self._done_local, ws, buf * npan, npan, self.epoch),
               "pto_b200_ksplit_wait")
