@@ -79,6 +79,21 @@ int pto_b200_gemm_ex(void* stream, uint8_t* out, const uint8_t* src0, const uint
                      int launch_block_count);
 
 /*
+ * pto_b200_gemm_ex with an optional workspace for the last, partly filled wave of tiles. The reference assigns each
+ * core a fixed sub-matrix (InitGMOffsets, gemm_performance_kernel.cpp:48-67) and has no counterpart; on 148 SMs a
+ * 4096^3 problem leaves the last wave 46 % full, so with a workspace each leftover tile is cut into two K halves
+ * that run on two CTA pairs at once: the first half parks its 32-bit accumulators in the workspace, the second adds
+ * them to its own and stores. Results differ from the unsplit chain only by the fp32 summation order (int32: exact).
+ *   workspace : device memory of pto_b200_gemm_workspace_bytes() bytes, 16-byte aligned, ZERO before its first use
+ *               (the kernel leaves its counters zero again), or NULL = never split. One workspace must not be used
+ *               by two launches that can overlap on the GPU (use one per stream).
+ */
+size_t pto_b200_gemm_workspace_bytes(void);
+int pto_b200_gemm_ws(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, int m, int n, int k,
+                     long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype, int b_layout,
+                     int launch_block_count, uint8_t* workspace, size_t workspace_bytes);
+
+/*
  * int8 x int8 -> int32 GEMM with the dequantising store fused:
  *   out[i][j] = bf16( (float(acc[i][j]) * s_col[j]) * s_row[i] ),  two separately rounded fp32 multiplies.
  * Replaces: TMATMUL/TMATMUL_ACC on int8 tiles + TSTORE_FP per-column dequant

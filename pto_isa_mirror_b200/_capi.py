@@ -26,6 +26,11 @@ _i = ctypes.c_int
 SYMBOLS = {
     "pto_b200_gemm": (_i, [ctypes.c_void_p, _u8p, _u8p, _u8p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i]),
     "pto_b200_gemm_ex": (_i, [ctypes.c_void_p, _u8p, _u8p, _u8p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _i]),
+    "pto_b200_gemm_workspace_bytes": (ctypes.c_size_t, []),
+    "pto_b200_gemm_ws": (
+        _i,
+        [ctypes.c_void_p, _u8p, _u8p, _u8p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _i, _u8p, ctypes.c_size_t],
+    ),
     "pto_b200_gemm_s8_dequant": (
         _i,
         [ctypes.c_void_p, _u8p, _u8p, _u8p, ctypes.c_void_p, ctypes.c_void_p, _i, _i, _i, _ll, _ll, _ll],

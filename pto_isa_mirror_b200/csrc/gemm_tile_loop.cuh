@@ -46,6 +46,12 @@ struct GemmParams {
     const uint8_t* sfa; // scale factors re-tiled to 512-byte atoms, index (k_block, m_block)
     const uint8_t* sfb; // same, index (k_block, n_block)
     int* status;
+    // CTA-pair kernels, last partly filled wave: each leftover tile is cut in two K halves that run on two pairs at
+    // once; the first half parks its fp32 / int32 accumulators in the workspace, the second half adds them and stores.
+    int tail_first_unit; // first work unit of the split tail (= number of tiles when nothing is split)
+    int tail_tiles;      // leftover tiles that are split (0 = none)
+    uint32_t* ws_partial; // [tail_tiles][256][256] 32-bit accumulators
+    int* ws_flags;        // [2 * tail_tiles]: arrivals of the first halves' store warps, departures of the readers
 };
 
 constexpr int kBlockM = 128;

@@ -20,6 +20,15 @@ namespace pto_b200 {
 constexpr int kPairBlockM = 256;
 constexpr int kPairBlockN = 256;
 
+constexpr int ST_TAIL_TIMEOUT = 5;
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* ptr)
+{
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+    return v;
+}
+
 template <int KIND, int STAGES>
 struct PairSmemLayout {
     static constexpr int kABytes = kBlockM * kBlockKBytes;        // this CTA's 128 rows of A
@@ -36,6 +45,39 @@ struct PairSmemLayout {
     static constexpr int kMiscOff = kBarOff + kNumBars * 8;
     static constexpr int kTotal = kMiscOff + 16 + 1024;
 };
+
+// One unit of work of a CTA pair: a whole 256 x 256 tile, or one K half of a tile of the last, partly filled wave.
+struct PairUnit {
+    int mi, ni;
+    int kb0, kb1; // k-block range
+    int role;     // 0 whole tile; 1 first K half (parks its accumulators); 2 second K half (adds them, stores)
+    int tail_idx; // index of the tile among the split ones
+};
+
+__device__ __forceinline__ bool pair_unit(int u, const GemmParams& p, PairUnit& w)
+{
+    if (u < p.tail_first_unit) {
+        tile_coords(u, p, w.mi, w.ni);
+        w.kb0 = 0;
+        w.kb1 = p.k_blocks;
+        w.role = 0;
+        w.tail_idx = 0;
+        return true;
+    }
+    const int t = u - p.tail_first_unit;
+    if (t >= 2 * p.tail_tiles) {
+        return false;
+    }
+    w.tail_idx = t >> 1;
+    tile_coords(p.tail_first_unit + w.tail_idx, p, w.mi, w.ni);
+    const int mid = p.k_blocks / 2;
+    w.role = 1 + (t & 1);
+    w.kb0 = (w.role == 1) ? 0 : mid;
+    w.kb1 = (w.role == 1) ? mid : p.k_blocks;
+    return true;
+}
+
+constexpr int kTailWarps = 8; // store warps of a pair: four in each CTA
 
 template <int KIND, int STAGES, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
@@ -65,7 +107,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
     const bool leader = (cta_rank == 0);
     const int pair = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
-    const int total_tiles = p.m_tiles * p.n_tiles; // tiles of 256 x 256
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -98,12 +139,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
-                int mi, ni;
-                tile_coords(tile, p, mi, ni);
+            PairUnit w;
+            for (int u = pair; ok && pair_unit(u, p, w); u += num_pairs) {
+                const int mi = w.mi, ni = w.ni;
                 const int row_a = mi * kPairBlockM + static_cast<int>(cta_rank) * kBlockM;
                 const int row_b = ni * kPairBlockN + static_cast<int>(cta_rank) * (kPairBlockN / 2);
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     ok = bounded_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, ST_PRODUCER_TIMEOUT);
                     if (!ok) {
                         break;
@@ -142,14 +183,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
             int acc = 0;
             uint32_t acc_phase = 0;
             bool ok = true;
-            for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
+            PairUnit w;
+            for (int u = pair; ok && pair_unit(u, p, w); u += num_pairs) {
                 ok = bounded_wait(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag, p.status, ST_MMA_ACC_TIMEOUT);
                 if (!ok) {
                     break;
                 }
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kAccCols);
-                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     ok = bounded_wait(&full_bar[stage], phase, abort_flag, p.status, ST_MMA_FULL_TIMEOUT);
                     if (!ok) {
                         break;
@@ -173,7 +215,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                             ptx::make_smem_desc(a_base + kk * kUmmaKBytes, 16, 1024, ptx::kSwizzle128B);
                         const uint64_t b_desc =
                             ptx::make_smem_desc(b_base + kk * kUmmaKBytes, 16, 1024, ptx::kSwizzle128B);
-                        const uint32_t accumulate = (kb > 0 || kk > 0) ? 1u : 0u;
+                        const uint32_t accumulate = (kb > w.kb0 || kk > 0) ? 1u : 0u;
                         if constexpr (KIND == KIND_F16) {
                             ptx::umma_f16_pair(d_tmem, a_desc, b_desc, p.idesc, accumulate);
                         } else if constexpr (KIND == KIND_I8) {
@@ -209,9 +251,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
         int acc = 0;
         uint32_t acc_phase = 0;
         bool ok = true;
-        for (int tile = pair; ok && tile < total_tiles; tile += num_pairs) {
-            int mi, ni;
-            tile_coords(tile, p, mi, ni);
+        PairUnit w;
+        for (int u = pair; ok && pair_unit(u, p, w); u += num_pairs) {
+            const int mi = w.mi, ni = w.ni;
             ok = bounded_wait(&acc_full_bar[acc], acc_phase, abort_flag, p.status, ST_EPILOGUE_TIMEOUT);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) {
@@ -225,6 +267,35 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
             }
             const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * kAccCols) +
                                    (static_cast<uint32_t>(quarter * 32) << 16);
+            // this thread's row of the parked accumulators of a split tile
+            uint32_t* ws_row = nullptr;
+            int* ws_arrive = nullptr;
+            if (w.role != 0) {
+                ws_row = p.ws_partial + (static_cast<size_t>(w.tail_idx) * kPairBlockM +
+                                         cta_rank * kBlockM + quarter * 32 + lane) * kPairBlockN;
+                ws_arrive = p.ws_flags + 2 * w.tail_idx;
+            }
+            if (w.role == 2) {
+                // second K half: wait (bounded) until every store warp of the first half has parked its rows
+                bool parked = true;
+                if (lane == 0) {
+                    const long long t0 = clock64();
+                    while (ld_acquire_gpu(ws_arrive) < kTailWarps) {
+                        __nanosleep(32);
+                        if (*abort_flag != 0 || clock64() - t0 > kWaitLimitCycles) {
+                            *abort_flag = 1;
+                            atomicCAS(p.status, 0, ST_TAIL_TIMEOUT);
+                            parked = false;
+                            break;
+                        }
+                    }
+                }
+                parked = __all_sync(0xFFFFFFFFu, parked);
+                if (!parked) {
+                    ok = false;
+                    break;
+                }
+            }
 #pragma unroll 1
             for (int chunk = 0; chunk < kPairBlockN / 32; ++chunk) {
                 const int col0 = ni * kPairBlockN + chunk * 32;
@@ -234,7 +305,47 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                 uint32_t v[32];
                 ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(chunk * 32), v);
                 ptx::tmem_ld_wait();
+                if (w.role == 1) {
+                    uint4* d4 = reinterpret_cast<uint4*>(ws_row + chunk * 32);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        d4[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    }
+                    continue;
+                }
+                if (w.role == 2) {
+                    const uint4* s4 = reinterpret_cast<const uint4*>(ws_row + chunk * 32);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint4 q = __ldcg(s4 + i);
+                        const uint32_t qa[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if constexpr (EPI == EPI_S32 || EPI == EPI_DEQ_BF16) {
+                                v[4 * i + j] += qa[j]; // int32 accumulators: exact
+                            } else {
+                                v[4 * i + j] = __float_as_uint(__uint_as_float(qa[j]) + __uint_as_float(v[4 * i + j]));
+                            }
+                        }
+                    }
+                }
                 store_chunk<EPI>(v, p, row, col0, vec_ok, s_row);
+            }
+            if (w.role == 1) {
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) {
+                    atomicAdd(ws_arrive, 1);
+                }
+            } else if (w.role == 2) {
+                __syncwarp();
+                if (lane == 0) {
+                    // the last reader to leave clears both counters for the next launch
+                    if (atomicAdd(ws_arrive + 1, 1) == kTailWarps - 1) {
+                        ws_arrive[0] = 0;
+                        ws_arrive[1] = 0;
+                    }
+                }
             }
             ptx::tc_fence_before_sync();
             __syncwarp();

@@ -166,6 +166,11 @@ uint32_t make_idesc(int c_fmt, int a_fmt, int b_fmt, bool b_mn_major, int n, boo
     return d;
 }
 
+// Workspace of the split last wave: counters first, then up to kGemmWorkspaceTiles parked 256 x 256 accumulators.
+constexpr int kGemmWorkspaceTiles = 40;
+constexpr size_t kGemmWorkspaceFlagBytes = 4096;
+constexpr size_t kGemmWorkspaceBytes = kGemmWorkspaceFlagBytes + static_cast<size_t>(kGemmWorkspaceTiles) * 256 * 256 * 4;
+
 struct Problem {
     int m, n, k;
     long long lda, ldb, ldc;
@@ -212,7 +217,8 @@ int launch_block_n(int block_n, cudaStream_t stream, const CUtensorMap& ta, cons
 // one-CTA kernel (fewer tiles than CTA pairs the device can hold at once), otherwise a PTO_B200 code.
 template <int KIND, int EPI>
 int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, const Problem& q,
-                const CUtensorMap* sfa_map = nullptr, const CUtensorMap* sfb_map = nullptr, int block_limit = 0)
+                const CUtensorMap* sfa_map = nullptr, const CUtensorMap* sfb_map = nullptr, int block_limit = 0,
+                uint8_t* workspace = nullptr, size_t workspace_bytes = 0)
 {
 #ifndef PTO_B200_PAIR_STAGES
 #define PTO_B200_PAIR_STAGES 6
@@ -263,6 +269,18 @@ int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& t
         pairs = block_limit / 2 > 0 ? block_limit / 2 : 1;
     }
     cfg.gridDim = dim3(2 * pairs, 1, 1);
+    // Last wave: when the leftover tiles would occupy at most half of the pairs, cut each of them into two K halves
+    // that run on two pairs at once (accumulators of the first half parked in the caller's workspace).
+    const int leftover = tiles % pairs;
+    p.tail_first_unit = tiles;
+    p.tail_tiles = 0;
+    if (workspace != nullptr && workspace_bytes >= kGemmWorkspaceBytes && leftover > 0 && 2 * leftover <= pairs &&
+        leftover <= kGemmWorkspaceTiles && p.k_blocks >= 2) {
+        p.tail_first_unit = tiles - leftover;
+        p.tail_tiles = leftover;
+        p.ws_flags = reinterpret_cast<int*>(workspace);
+        p.ws_partial = reinterpret_cast<uint32_t*>(workspace + kGemmWorkspaceFlagBytes);
+    }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     // the scale maps are only read by the block-scaled instantiations; the others get copies of the A map
     const CUtensorMap& ma = sfa_map ? *sfa_map : ta;
@@ -327,8 +345,21 @@ extern "C" int pto_b200_gemm_ex(void* stream, uint8_t* out, const uint8_t* src0,
                                 int k, long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype,
                                 int b_layout, int launch_block_count)
 {
+    return pto_b200_gemm_ws(stream, out, src0, src1, m, n, k, lda, ldb, ldc, in_dtype, out_dtype, b_layout,
+                            launch_block_count, nullptr, 0);
+}
+
+extern "C" size_t pto_b200_gemm_workspace_bytes(void) { return kGemmWorkspaceBytes; }
+
+extern "C" int pto_b200_gemm_ws(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, int m, int n,
+                                int k, long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype,
+                                int b_layout, int launch_block_count, uint8_t* workspace, size_t workspace_bytes)
+{
     if (launch_block_count < 0) {
         return PTO_B200_EINVAL;
+    }
+    if (workspace != nullptr && ((reinterpret_cast<uintptr_t>(workspace) & 15u) || workspace_bytes < kGemmWorkspaceBytes)) {
+        return PTO_B200_EWORKSPACE;
     }
     const bool is16 = (in_dtype == PTO_B200_F16 || in_dtype == PTO_B200_BF16);
     const bool is8 = (in_dtype == PTO_B200_S8);
@@ -383,18 +414,18 @@ extern "C" int pto_b200_gemm_ex(void* stream, uint8_t* out, const uint8_t* src0,
         int rc = -1;
         if (is8) {
             pp.idesc = make_idesc(2, 1, 1, false, kPairBlockN, false, kPairBlockM);
-            rc = launch_pair<KIND_I8, EPI_S32>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count);
+            rc = launch_pair<KIND_I8, EPI_S32>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count, workspace, workspace_bytes);
         } else {
             pp.idesc = make_idesc(1, fmt, fmt, false, kPairBlockN, false, kPairBlockM);
             switch (out_dtype) {
                 case PTO_B200_F32:
-                    rc = launch_pair<KIND_F16, EPI_F32>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count);
+                    rc = launch_pair<KIND_F16, EPI_F32>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count, workspace, workspace_bytes);
                     break;
                 case PTO_B200_BF16:
-                    rc = launch_pair<KIND_F16, EPI_BF16>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count);
+                    rc = launch_pair<KIND_F16, EPI_BF16>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count, workspace, workspace_bytes);
                     break;
                 default:
-                    rc = launch_pair<KIND_F16, EPI_F16>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count);
+                    rc = launch_pair<KIND_F16, EPI_F16>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count, workspace, workspace_bytes);
                     break;
             }
         }

@@ -194,8 +194,8 @@ def test_c2_bf16_4096_cubed():
     m = n = k = 4096
     a, b = gd.dense_inputs(m, n, k, "bf16", 1)
     ta, tb = dev16(a, torch.bfloat16), dev16(b, torch.bfloat16)
-    out32 = host(pto.gemm(ta, tb, torch.float32))
-    out16 = host(pto.gemm(ta, tb, torch.bfloat16))
+    out32 = host(pto.gemm(ta, tb, torch.float32, workspace="auto"))      # with the split last wave
+    out16 = host(pto.gemm(ta, tb, torch.bfloat16, workspace="auto"))
     assert np.array_equal(out16, gd.f32_to_bf16_bits(out32))
     for r0, c0 in sample_tiles(m, n, 8, 31):
         ref = oracle.gemm_f32acc(a[r0:r0 + 128], b[c0:c0 + 256], oracle.BF16)
@@ -204,9 +204,16 @@ def test_c2_bf16_4096_cubed():
         assert bf16_ulp_distance(out16[r0:r0 + 128, c0:c0 + 256][big], gd.f32_to_bf16_bits(ref)[big]) <= 1
     # linearity in a power of two is exact, and a row permutation of A permutes C bit for bit
     a2 = gd.f32_to_bf16_bits(gd.bf16_bits_to_f32(a) * np.float32(2.0))
-    assert np.array_equal(host(pto.gemm(dev16(a2, torch.bfloat16), tb, torch.float32)), out32 * np.float32(2.0))
+    assert np.array_equal(host(pto.gemm(dev16(a2, torch.bfloat16), tb, torch.float32, workspace="auto")),
+                          out32 * np.float32(2.0))
+    # without the workspace no tile is split along K, and then a row permutation of A permutes C bit for bit
+    plain = host(pto.gemm(ta, tb, torch.float32, workspace=None))
     perm = np.argsort(gd.uniform01(m, 77))
-    assert np.array_equal(host(pto.gemm(dev16(a[perm], torch.bfloat16), tb, torch.float32)), out32[perm])
+    assert np.array_equal(host(pto.gemm(dev16(a[perm], torch.bfloat16), tb, torch.float32, workspace=None)), plain[perm])
+    # with it the 34 leftover tiles of the fourth wave are summed as two K halves: same values up to
+    # the fp32 summation order, and most tiles are untouched
+    assert max_rel_err(out32, plain) <= 1e-5
+    assert (out32 == plain).mean() > 0.8 and (out32 != plain).any()
 
 
 def test_c3_int8_8192_cubed_exact():
@@ -228,6 +235,23 @@ def test_c3_int8_8192_cubed_exact():
                               oracle.dequant_bf16(ref, s_row[r0:r0 + 128], s_col[c0:c0 + 256], True))
     # the fused dequant store equals the oracle's store applied to the GPU's own accumulators, everywhere
     assert np.array_equal(deq[:1024], oracle.dequant_bf16(acc[:1024], s_row[:1024], s_col, True))
+
+
+def test_split_last_wave_int8_exact():
+    """4096 x 4096 leaves 34 tiles for the fourth wave on 74 CTA pairs; they are computed as two K halves. Integer
+    accumulators must come out identical with and without the split."""
+    m = n = 4096
+    k = 1024
+    a, b, s_row, s_col = gd.s8_inputs(m, n, k, 6)
+    ta, tb = dev8(a), dev8(b)
+    split = pto.gemm(ta, tb, torch.int32, workspace="auto")
+    plain = pto.gemm(ta, tb, torch.int32, workspace=None)
+    assert torch.equal(split, plain)
+    row_sums = split.sum(dim=1, dtype=torch.int64).cpu().numpy()
+    assert np.array_equal(row_sums, a.astype(np.int64) @ b.astype(np.int64).sum(axis=0))
+    # twice more on the same workspace: its counters must have been left clean
+    for _ in range(2):
+        assert torch.equal(pto.gemm(ta, tb, torch.int32, workspace="auto"), plain)
 
 
 def test_c4_mxfp8_sampled_tiles():
