@@ -296,22 +296,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                     break;
                 }
             }
-#pragma unroll 1
-            for (int chunk = 0; chunk < kPairBlockN / 32; ++chunk) {
+            // one 32-column chunk of this thread's row: park it (first K half), add the parked half (second K half),
+            // then cast / scale and store
+            auto finish_chunk = [&](uint32_t (&v)[32], int chunk) {
                 const int col0 = ni * kPairBlockN + chunk * 32;
                 if (col0 >= p.n) {
-                    break;
+                    return;
                 }
-                uint32_t v[32];
-                ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(chunk * 32), v);
-                ptx::tmem_ld_wait();
                 if (w.role == 1) {
                     uint4* d4 = reinterpret_cast<uint4*>(ws_row + chunk * 32);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         d4[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
                     }
-                    continue;
+                    return;
                 }
                 if (w.role == 2) {
                     const uint4* s4 = reinterpret_cast<const uint4*>(ws_row + chunk * 32);
@@ -330,6 +328,28 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                     }
                 }
                 store_chunk<EPI>(v, p, row, col0, vec_ok, s_row);
+            };
+            // Accumulator read-back in groups of 64 columns, software-pipelined: the TMEM loads of the next group are
+            // in flight while the current group is converted and stored (columns past N are loaded but never stored).
+            {
+                uint32_t va[32], vb[32], vc[32], vd[32];
+                ptx::tmem_ld_32x32b_x32(t_row + 0u, va);
+                ptx::tmem_ld_32x32b_x32(t_row + 32u, vb);
+#pragma unroll
+                for (int g = 0; g < kPairBlockN / 128; ++g) {
+                    ptx::tmem_ld_wait();
+                    ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(g * 128 + 64), vc);
+                    ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(g * 128 + 96), vd);
+                    finish_chunk(va, g * 4 + 0);
+                    finish_chunk(vb, g * 4 + 1);
+                    ptx::tmem_ld_wait();
+                    if (g + 1 < kPairBlockN / 128) {
+                        ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(g * 128 + 128), va);
+                        ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(g * 128 + 160), vb);
+                    }
+                    finish_chunk(vc, g * 4 + 2);
+                    finish_chunk(vd, g * 4 + 3);
+                }
             }
             if (w.role == 1) {
                 __threadfence();

@@ -113,7 +113,9 @@ struct KsplitReduceArgs {
     long long ld_partial, ld_out;
 };
 
-__global__ void __launch_bounds__(512) ksplit_reduce_kernel(const KsplitReduceArgs a)
+constexpr int kReduceThreads = 256; // small enough to share an SM's registers with a resident GEMM CTA
+
+__global__ void __launch_bounds__(kReduceThreads) ksplit_reduce_kernel(const KsplitReduceArgs a)
 {
     __shared__ int ok_flag;
     if (threadIdx.x == 0) {

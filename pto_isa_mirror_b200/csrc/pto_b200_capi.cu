@@ -718,12 +718,12 @@ extern "C" int pto_b200_ksplit_reduce(void* stream, void* const* partial_ptrs, v
     a.n = n;
     a.ld_partial = ld_partial;
     a.ld_out = ld_out;
-    const long long work = (static_cast<long long>(rows) * (n / 4) + 511) / 512;
-    int grid = launch_block_count > 0 ? launch_block_count : 32;
+    const long long work = (static_cast<long long>(rows) * (n / 4) + kReduceThreads - 1) / kReduceThreads;
+    int grid = launch_block_count > 0 ? launch_block_count : 64;
     if (work < grid) {
         grid = static_cast<int>(work);
     }
-    ksplit_reduce_kernel<<<grid, 512, 0, static_cast<cudaStream_t>(stream)>>>(a);
+    ksplit_reduce_kernel<<<grid, kReduceThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return note_cuda(cudaGetLastError(), "ksplit_reduce launch");
 }
