@@ -30,7 +30,7 @@ FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_g
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu captures
 # summarised under profiles/ (None = not captured for that workload).
 NCU_DRAM_TRAFFIC = {
-    "bf16_4096": 91912704,  # profiles/gemm_tile_loop_bf16_4096_1cta.md: 78.36 MB read + 13.55 MB written
+    "bf16_4096": 98895360,  # profiles/gemm_tile_loop_2cta_bf16_4096.md: 85.00 MB read + 13.89 MB written
 }
 
 WORKLOADS = {
