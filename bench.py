@@ -400,7 +400,7 @@ def main():
     ap.add_argument("--panels", type=int, default=8)
     ap.add_argument("--mode", default="p2p", choices=["p2p", "rs_ag", "allreduce"],
                     help="K-split reduction: p2p = this library's kernels over peer memory; rs_ag / allreduce = NCCL")
-    ap.add_argument("--reduce-blocks", type=int, default=64)
+    ap.add_argument("--reduce-blocks", type=int, default=32)
     ap.add_argument("--gemm-streams", type=int, default=2, help="p2p mode: streams the panel GEMMs alternate between")
     ap.add_argument("--no-multicast", action="store_true", help="p2p mode: plain peer loads instead of NVLS multimem")
     ap.add_argument("--panel-rows", default="",

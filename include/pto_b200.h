@@ -174,7 +174,7 @@ int pto_b200_cast_f32_to_bf16(void* stream, uint8_t* out, const uint8_t* in, lon
  *                            for rows [row0, row0 + rows) - this rank's shard of the panel - sums the fp32 partials
  *                            of all ranks in rank order, casts to bf16 (round to nearest even) and stores the result
  *                            into every rank's output; finally stores done[slot][rank] = epoch into every rank's
- *                            done-flag array. launch_block_count = thread blocks to use (0 = 64).
+ *                            done-flag array. launch_block_count = thread blocks to use (0 = 32).
  *                            multicast_partial / multicast_out: NVSwitch multicast addresses of the same partial /
  *                            output buffers (NVLS), or null. With them the sum is formed inside the switch
  *                            (multimem.ld_reduce, the switch's own fixed order) and the result is broadcast with one

@@ -329,26 +329,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                 }
                 store_chunk<EPI>(v, p, row, col0, vec_ok, s_row);
             };
-            // Accumulator read-back in groups of 64 columns, software-pipelined: the TMEM loads of the next group are
-            // in flight while the current group is converted and stored (columns past N are loaded but never stored).
+            // Accumulator read-back, software-pipelined over 32-column chunks: the TMEM load of the next chunk is in
+            // flight while the current one is converted and stored (columns past N are loaded but never stored).
+            // Two chunks of registers keep the kernel near 128 registers per thread, so that a reduction CTA of the
+            // K-split path still fits beside this CTA on the SM.
             {
-                uint32_t va[32], vb[32], vc[32], vd[32];
+                uint32_t va[32], vb[32];
                 ptx::tmem_ld_32x32b_x32(t_row + 0u, va);
-                ptx::tmem_ld_32x32b_x32(t_row + 32u, vb);
 #pragma unroll
-                for (int g = 0; g < kPairBlockN / 128; ++g) {
+                for (int g = 0; g < kPairBlockN / 64; ++g) {
                     ptx::tmem_ld_wait();
-                    ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(g * 128 + 64), vc);
-                    ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(g * 128 + 96), vd);
-                    finish_chunk(va, g * 4 + 0);
-                    finish_chunk(vb, g * 4 + 1);
+                    ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(g * 64 + 32), vb);
+                    finish_chunk(va, g * 2 + 0);
                     ptx::tmem_ld_wait();
-                    if (g + 1 < kPairBlockN / 128) {
-                        ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(g * 128 + 128), va);
-                        ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(g * 128 + 160), vb);
+                    if (g + 1 < kPairBlockN / 64) {
+                        ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(g * 64 + 64), va);
                     }
-                    finish_chunk(vc, g * 4 + 2);
-                    finish_chunk(vd, g * 4 + 3);
+                    finish_chunk(vb, g * 2 + 1);
                 }
             }
             if (w.role == 1) {

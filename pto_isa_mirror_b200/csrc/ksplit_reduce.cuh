@@ -113,7 +113,7 @@ struct KsplitReduceArgs {
     long long ld_partial, ld_out;
 };
 
-constexpr int kReduceThreads = 256; // small enough to share an SM's registers with a resident GEMM CTA
+constexpr int kReduceThreads = 512; // 512 x 64 registers: fits beside a resident GEMM CTA (192 threads, <= 128 registers)
 
 __global__ void __launch_bounds__(kReduceThreads) ksplit_reduce_kernel(const KsplitReduceArgs a)
 {

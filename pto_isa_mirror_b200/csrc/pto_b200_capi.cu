@@ -719,7 +719,7 @@ extern "C" int pto_b200_ksplit_reduce(void* stream, void* const* partial_ptrs, v
     a.ld_partial = ld_partial;
     a.ld_out = ld_out;
     const long long work = (static_cast<long long>(rows) * (n / 4) + kReduceThreads - 1) / kReduceThreads;
-    int grid = launch_block_count > 0 ? launch_block_count : 64;
+    int grid = launch_block_count > 0 ? launch_block_count : 32;
     if (work < grid) {
         grid = static_cast<int>(work);
     }

@@ -166,7 +166,7 @@ class KSplitGemmP2P:
     """
 
     def __init__(self, m: int, n: int, group: Optional[dist.ProcessGroup] = None, panels: int = 4,
-                 device: Optional[torch.device] = None, reduce_blocks: int = 64, launch_block_count: int = 0,
+                 device: Optional[torch.device] = None, reduce_blocks: int = 32, launch_block_count: int = 0,
                  panel_rows: Optional[List[int]] = None, reduce_blocks_last: int = 0, use_multicast: bool = True,
                  gemm_streams: int = 2):
         """``panels`` equal row panels, or explicit ``panel_rows`` heights (decreasing heights leave only a small
