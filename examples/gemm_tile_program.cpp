@@ -1,9 +1,10 @@
 // gemm_tile_program.cpp - the reference's two GEMM tile programs written against include/pto/pto-inst.hpp and run
 // on a B200: (1) the CPU demo's TLOAD / TMOV / TMATMUL / TSTORE sequence (demos/cpu/gemm_demo/gemm_demo.cpp:83-121,
 // B row-major), (2) the gemm_performance K loop with TEXTRACT slices and TMATMUL / TMATMUL_ACC
-// (kernels/manual/a2a3/gemm_performance/gemm_performance_kernel.cpp:69-131, B column-major), plus the fixed-signature
-// launcher. Inputs are small integers so the fp32 results are exact; the program checks them against a host loop
-// and prints "tile programs ok".
+// (kernels/manual/a2a3/gemm_performance/gemm_performance_kernel.cpp:69-131, B column-major), (3) the fixed-signature
+// launcher, (4) the bias form of the K loop (TMATMUL_BIAS then TMATMUL_ACC, tests/cpu/st/testcase/tmatmul/
+// tmatmul_kernel.cpp:86-96) and (5) a one-row TGEMV_BIAS. Inputs are small integers so the fp32 results are exact;
+// the program checks them against a host loop and prints "tile programs ok".
 //
 // Build (one line): g++ -std=c++17 -I include -I /usr/local/cuda/include examples/gemm_tile_program.cpp
 //   -L pto_isa_mirror_b200/lib -lpto_b200 -L /usr/local/cuda/lib64 -lcudart -o examples/gemm_tile_program
@@ -137,6 +138,61 @@ int main()
         LaunchGEMME2E<uint16_t>(reinterpret_cast<uint8_t*>(dC), reinterpret_cast<uint8_t*>(dA),
                                 reinterpret_cast<uint8_t*>(dBdn), nullptr, {M, N, K});
         check("LaunchGEMME2E<uint16_t>");
+    }
+    { // (4) TMATMUL_BIAS on the first K chunk, TMATMUL_ACC on the rest (tests/cpu/st/testcase/tmatmul bias cases)
+        std::vector<float> bias(N);
+        for (int j = 0; j < N; ++j) bias[j] = static_cast<float>((j * 3) % 11 - 5);
+        float* dBias = to_device(bias);
+        for (int i = 0; i < M; ++i)
+            for (int j = 0; j < N; ++j) ref[i * N + j] += bias[j];
+        using GlobalA = GlobalTensor<half, TileShape2D<half, M, baseK, Layout::ND>, BaseShape2D<half, M, K, Layout::ND>>;
+        using GlobalB = GlobalTensor<half, TileShape2D<half, baseK, N, Layout::DN>, BaseShape2D<half, K, N, Layout::DN>,
+                                     Layout::DN>;
+        using GlobalBias = GlobalTensor<float, Shape<1, 1, 1, 1, N>, Stride<N, N, N, N, 1>>;
+        using GlobalC = GlobalTensor<float, Shape<1, 1, 1, M, N>, Stride<M * N, M * N, M * N, N, 1>>;
+        TileLeft<half, M, baseK, M, baseK> aTile;
+        TileRight<half, baseK, N, baseK, N> bTile;
+        TileAcc<float, M, N, M, N> cTile;
+        Tile<TileType::Bias, float, 1, N, BLayout::RowMajor, 1, N> biasTile;
+        GlobalBias biasGlobal(dBias);
+        TLOAD(biasTile, biasGlobal);
+        for (int kIter = 0; kIter < K / baseK; ++kIter) {
+            GlobalA gmA(dA + kIter * baseK);
+            GlobalB gmB(dBdn + kIter * baseK);
+            TLOAD(aTile, gmA);
+            TLOAD(bTile, gmB);
+            if (kIter == 0) {
+                TMATMUL_BIAS(cTile, aTile, bTile, biasTile);
+            } else {
+                TMATMUL_ACC(cTile, cTile, aTile, bTile);
+            }
+        }
+        GlobalC cGlobal(dC);
+        TSTORE(cGlobal, cTile);
+        check("bias program (TMATMUL_BIAS/TMATMUL_ACC, B column-major)");
+        { // (5) TGEMV_BIAS: the first row alone, streamed without tensor-core tiles; compare with row 0 of (4)
+            using GlobalRow = GlobalTensor<half, Shape<1, 1, 1, 1, K>, Stride<K, K, K, K, 1>>;
+            using GlobalMatB = GlobalTensor<half, TileShape2D<half, K, N, Layout::DN>, BaseShape2D<half, K, N, Layout::DN>,
+                                            Layout::DN>;
+            using GlobalRowOut = GlobalTensor<float, Shape<1, 1, 1, 1, N>, Stride<N, N, N, N, 1>>;
+            TileLeft<half, 1, K, 1, K> xTile;
+            TileRight<half, K, N, K, N> wTile;
+            TileAcc<float, 1, N, 1, N> yTile;
+            GlobalRow xGlobal(dA);
+            GlobalMatB wGlobal(dBdn);
+            GlobalRowOut yGlobal(dC);
+            TLOAD(xTile, xGlobal);
+            TLOAD(wTile, wGlobal);
+            TGEMV_BIAS(yTile, xTile, wTile, biasTile);
+            TSTORE(yGlobal, yTile);
+            cudaDeviceSynchronize();
+            cudaMemcpy(out.data(), dC, N * sizeof(float), cudaMemcpyDeviceToHost);
+            int n = 0;
+            for (int j = 0; j < N; ++j) n += (out[j] != ref[j]);
+            std::printf("one-row program (TGEMV_BIAS): %d mismatches\n", n);
+            bad += n;
+        }
+        cudaFree(dBias);
     }
     int status = 0;
     pto_b200_device_status(&status);

@@ -215,6 +215,8 @@ struct Tile {
     // host-side state of the lazily executed tile program
     b200::View view;                      // Mat / Left / Right / Scale tiles: where the data lives
     std::vector<b200::Product> products;  // Acc tiles: the pending TMATMUL(+_ACC) chain
+    b200::View bias;                      // Acc tiles: the bias row of a TMATMUL_BIAS / TGEMV_BIAS chain, if any
+    bool one_row = false;                 // Acc tiles: the chain was started by TGEMV (one left row)
     uint64_t assigned_addr = 0;           // TASSIGN bookkeeping only
 };
 
@@ -321,9 +323,46 @@ PTO_INST RecordEvent TMATMUL(TileRes& cMatrix, TileLeft_& aMatrix, TileRight_& b
 {
     b200::check_mad_valid<TileRes, TileLeft_, TileRight_>();
     cMatrix.products.clear();
+    cMatrix.bias = b200::View{};
+    cMatrix.one_row = false;
     cMatrix.products.push_back(b200::Product{aMatrix.view, bMatrix.view, {}, {}, false,
                                              b200::dtype_of<typename TileLeft_::DType>::value,
                                              b200::dtype_of<typename TileRight_::DType>::value});
+    return {};
+}
+
+// Bias legality (CheckBiasValid, cpu/TMatmul.hpp:159-167): bias type == accumulator type, one row-major row.
+template <AccPhase Phase = AccPhase::Unspecified, typename TileRes, typename TileLeft_, typename TileRight_,
+          typename TileBias_>
+PTO_INST RecordEvent TMATMUL_BIAS(TileRes& cMatrix, TileLeft_& aMatrix, TileRight_& bMatrix, TileBias_& biasData)
+{
+    static_assert(std::is_same_v<typename TileRes::DType, typename TileBias_::DType>, "[PTO][SA] No supported bias data type");
+    static_assert(TileBias_::Loc == TileType::Bias && TileBias_::Rows == 1 && TileBias_::isRowMajor,
+                  "[PTO][SA] Non-conforming bias fractal");
+    TMATMUL<Phase>(cMatrix, aMatrix, bMatrix);
+    if (!biasData.view.bound()) {
+        b200::fail("TMATMUL_BIAS: bias tile was never loaded", 0);
+    }
+    cMatrix.bias = biasData.view;
+    return {};
+}
+
+// One left row (cpu/TMatmul.hpp:232-252: the TMATMUL arithmetic): TSTORE then streams B once instead of running
+// 128-row tensor-core tiles.
+template <AccPhase Phase = AccPhase::Unspecified, typename TileRes, typename TileLeft_, typename TileRight_>
+PTO_INST RecordEvent TGEMV(TileRes& cMatrix, TileLeft_& aMatrix, TileRight_& bMatrix)
+{
+    TMATMUL<Phase>(cMatrix, aMatrix, bMatrix);
+    cMatrix.one_row = true;
+    return {};
+}
+
+template <AccPhase Phase = AccPhase::Unspecified, typename TileRes, typename TileLeft_, typename TileRight_,
+          typename TileBias_>
+PTO_INST RecordEvent TGEMV_BIAS(TileRes& cMatrix, TileLeft_& aMatrix, TileRight_& bMatrix, TileBias_& biasData)
+{
+    TMATMUL_BIAS<Phase>(cMatrix, aMatrix, bMatrix, biasData);
+    cMatrix.one_row = true;
     return {};
 }
 
@@ -333,6 +372,8 @@ PTO_INST RecordEvent TMATMUL_ACC(TileRes& cOutMatrix, TileRes& cInMatrix, TileLe
     b200::check_mad_valid<TileRes, TileLeft_, TileRight_>();
     if (&cOutMatrix != &cInMatrix) {
         cOutMatrix.products = cInMatrix.products;
+        cOutMatrix.bias = cInMatrix.bias;
+        cOutMatrix.one_row = cInMatrix.one_row;
     }
     cOutMatrix.products.push_back(b200::Product{aMatrix.view, bMatrix.view, {}, {}, false,
                                                 b200::dtype_of<typename TileLeft_::DType>::value,
@@ -347,6 +388,8 @@ PTO_INST RecordEvent TMATMUL_MX(TileRes& cMatrix, TileLeft_& aMatrix, TileLeftSc
 {
     b200::check_mad_mx_valid<TileRes, TileLeft_, TileRight_>();
     cMatrix.products.clear();
+    cMatrix.bias = b200::View{};
+    cMatrix.one_row = false;
     cMatrix.products.push_back(b200::Product{aMatrix.view, bMatrix.view, aScaleMatrix.view, bScaleMatrix.view, true,
                                              b200::dtype_of<typename TileLeft_::DType>::value,
                                              b200::dtype_of<typename TileRight_::DType>::value});
@@ -421,14 +464,30 @@ PTO_INST RecordEvent TSTORE(GlobalData& dst, TileAcc_& src)
     using OutT = typename GlobalData::DType;
     uint8_t* out = reinterpret_cast<uint8_t*>(dst.data());
     int rc;
+    if (first.mx && src.bias.bound()) {
+        b200::fail("TSTORE: the bias form of TMATMUL_MX needs a workspace; call pto_b200_gemm_mx_bias", 0);
+        return {};
+    }
     if (first.mx) {
         rc = pto_b200_gemm_mx_static(b200::current_stream(), out, a.ptr, b.ptr, sa.ptr, sb.ptr, m, n,
                                      static_cast<int>(k_total), a.row_stride, ldb, ldc, sa.row_stride,
                                      sb.col_stride != 1 ? sb.col_stride : sb.row_stride, first.a_dtype, first.b_dtype,
                                      b200::dtype_of<OutT>::value);
     } else {
-        rc = pto_b200_gemm(b200::current_stream(), out, a.ptr, b.ptr, m, n, static_cast<int>(k_total), a.row_stride, ldb,
-                           ldc, first.a_dtype, b200::dtype_of<OutT>::value, b_dn ? PTO_B200_B_DN : PTO_B200_B_ND);
+        rc = PTO_B200_EALIGN;
+        if (src.one_row && m == 1 && b_dn) {
+            rc = pto_b200_gemv(b200::current_stream(), out, a.ptr, b.ptr, src.bias.ptr, n, static_cast<int>(k_total), ldb,
+                               first.a_dtype, b200::dtype_of<OutT>::value);
+        }
+        if (rc == PTO_B200_EALIGN && src.bias.bound()) { // not a one-row chain, or its row is not 16-byte aligned
+            rc = pto_b200_gemm_bias(b200::current_stream(), out, a.ptr, b.ptr, src.bias.ptr, m, n,
+                                    static_cast<int>(k_total), a.row_stride, ldb, ldc, first.a_dtype,
+                                    b200::dtype_of<OutT>::value, b_dn ? PTO_B200_B_DN : PTO_B200_B_ND);
+        } else if (rc == PTO_B200_EALIGN) {
+            rc = pto_b200_gemm(b200::current_stream(), out, a.ptr, b.ptr, m, n, static_cast<int>(k_total), a.row_stride,
+                               ldb, ldc, first.a_dtype, b200::dtype_of<OutT>::value,
+                               b_dn ? PTO_B200_B_DN : PTO_B200_B_ND);
+        }
     }
     if (rc != PTO_B200_OK) {
         b200::fail("TSTORE: launch rejected", rc);

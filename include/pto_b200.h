@@ -94,6 +94,20 @@ int pto_b200_gemm_ws(void* stream, uint8_t* out, const uint8_t* src0, const uint
                      int launch_block_count, uint8_t* workspace, size_t workspace_bytes);
 
 /*
+ * pto_b200_gemm with a bias row: C[i][j] = (sum_k A[i][k] * B[k][j]) + bias[j], cast to out_dtype afterwards.
+ * Replaces: TMATMUL_BIAS(c, a, b, bias) as the first step of the K loop followed by TMATMUL_ACC
+ * (include/pto/common/pto_instr.hpp:1000-1015; arithmetic include/pto/cpu/TMatmul.hpp:219-230: the matmul result,
+ * then bias added per column in the accumulator's type, CheckBiasValid :159-167).
+ *   bias : n values of the accumulator type in device memory, 4-byte aligned: fp32 for F16 / BF16 inputs,
+ *          int32 for S8 inputs (out_dtype S32).
+ * The bias is added once to the finished accumulator: identical to the reference for int32; for fp32 the reference
+ * adds it after the first baseK chunk of the chain, one fp32 rounding apart (inside the dense tolerance).
+ */
+int pto_b200_gemm_bias(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, const uint8_t* bias,
+                       int m, int n, int k, long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype,
+                       int b_layout);
+
+/*
  * int8 x int8 -> int32 GEMM with the dequantising store fused:
  *   out[i][j] = bf16( (float(acc[i][j]) * s_col[j]) * s_row[i] ),  two separately rounded fp32 multiplies.
  * Replaces: TMATMUL/TMATMUL_ACC on int8 tiles + TSTORE_FP per-column dequant
@@ -125,6 +139,16 @@ int pto_b200_gemm_mx(void* stream, uint8_t* out, const uint8_t* src0, const uint
                      int b_dtype, int out_dtype);
 
 size_t pto_b200_gemm_mx_workspace_bytes(int m, int n, int k);
+
+/*
+ * pto_b200_gemm_mx with an fp32 bias row added to the finished accumulator: the six-operand TMATMUL_MX
+ * (c, a, a_scale, b, b_scale, bias), include/pto/common/pto_instr.hpp:918-942, include/pto/cpu/TMatmul.hpp:271-292.
+ * bias : n floats in device memory.
+ */
+int pto_b200_gemm_mx_bias(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, const uint8_t* src2,
+                          const uint8_t* src3, const uint8_t* bias, uint8_t* workspace, size_t workspace_bytes, int m,
+                          int n, int k, long long lda, long long ldb, long long ldc, long long ld_sfa,
+                          long long ld_sfb, int a_dtype, int b_dtype, int out_dtype);
 
 /*
  * pto_b200_gemm_mx without a workspace argument. No counterpart in the reference (its launchers never need
@@ -159,6 +183,33 @@ int pto_b200_gemm_mx_static(void* stream, uint8_t* out, const uint8_t* src0, con
  * reduced K-split partials (gemm_ar: reduced_output -> fp16/bf16 result, kernels/manual/a2a3/gemm_ar/README.md:33-46).
  */
 int pto_b200_cast_f32_to_bf16(void* stream, uint8_t* out, const uint8_t* in, long long count);
+
+/*
+ * One left row: out[j] = sum_k a[k] * B[k][j] (+ bias[j]).
+ * Replaces: TGEMV / TGEMV_BIAS (include/pto/common/pto_instr.hpp:1019-1060; include/pto/cpu/TMatmul.hpp:232-252,
+ * the TMATMUL arithmetic with a one-row left tile; reference cases tests/cpu/st/testcase/tmatmul case_gemm_*).
+ *   src0 : the left row, k elements, 16-byte aligned
+ *   src1 : B column-major (PTO_B200_B_DN), n runs of k elements, leading dimension ldb elements (rows 16-byte aligned)
+ *   bias : n values of the accumulator type (fp32, or int32 for S8 inputs), or null
+ *   in_dtype F16 / BF16 (out F32 / BF16 / F16) or S8 (out S32).
+ * Bandwidth-bound: B is streamed once with plain loads, no tensor-core tile. The fp32 sum is formed from 32 partial
+ * sums, not as the reference's single chain: within the dense tolerance; int32 is exact.
+ */
+int pto_b200_gemv(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, const uint8_t* bias, int n,
+                  int k, long long ldb, int in_dtype, int out_dtype);
+
+/*
+ * OCP MX quantisation of fp32 rows into e4m3 bytes and e8m0 block scales (one per 32 elements along k): the
+ * producer of pto_b200_gemm_mx's src0 / src2 (or src1 / src3) operands.
+ * Replaces: TQUANT<QuantType::MXFP8> with the OCP scale rule (include/pto/common/pto_instr.hpp:2981-3035;
+ * include/pto/cpu/TQuant.hpp:178-190 shared exponent, :226-237 scaling, :118-153 e4m3fn encoding, :461-494 grouping).
+ *   src    : rows x k floats, leading dimension ld_src elements (multiple of 4), 16-byte aligned, finite values
+ *   data   : rows x k bytes, leading dimension ld_data bytes (multiple of 4), 4-byte aligned
+ *   scales : rows x k/32 bytes, leading dimension ld_scales bytes
+ *   k % 32 == 0. Bit-identical to the reference for finite input.
+ */
+int pto_b200_mx_quantize_e4m3(void* stream, uint8_t* data, uint8_t* scales, const uint8_t* src, int rows, int k,
+                              long long ld_src, long long ld_data, long long ld_scales);
 
 /*
  * K-split reduction over peer memory: the reduce-scatter / all-gather half of the reference's GEMM + AllReduce

@@ -53,7 +53,11 @@ def _lib() -> ctypes.CDLL:
             build()
         lib = ctypes.CDLL(ORACLE_LIB)
         lib.pto_oracle_gemm_f32acc.argtypes = [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i]
+        lib.pto_oracle_gemm_f32acc_bias.argtypes = [_p, _p, _p, _i, _p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i]
         lib.pto_oracle_gemm_s8.argtypes = [_p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i]
+        lib.pto_oracle_gemm_s8_bias.argtypes = [_p, _p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _i]
+        lib.pto_oracle_gemm_mx_bias.argtypes = [_p, _p, _p, _p, _p, _i, _p, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _i, _i,
+                                                _i]
         lib.pto_oracle_gemm_mx.argtypes = [_p, _p, _p, _p, _p, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _i, _i, _i]
         lib.pto_oracle_store_cast.argtypes = [_p, _p, _ll, _i]
         lib.pto_oracle_dequant_bf16.argtypes = [_p, _p, _p, _p, _i, _i, _ll, _ll, _i]
@@ -85,8 +89,11 @@ def _ptr(a: np.ndarray) -> int:
 
 # ----------------------------------------------------------------------------- restatement
 
-def gemm_f32acc(a: np.ndarray, b: np.ndarray, in_dtype: int, b_layout: int = B_DN, threads: int = 0) -> np.ndarray:
-    """Sequential-k fmaf GEMM. a [m, k]; b [n, k] (B_DN) or [k, n] (B_ND). F16/BF16 arrays are uint16 bit patterns."""
+def gemm_f32acc(a: np.ndarray, b: np.ndarray, in_dtype: int, b_layout: int = B_DN, threads: int = 0,
+                bias: np.ndarray | None = None, bias_after_k: int = 0) -> np.ndarray:
+    """Sequential-k fmaf GEMM. a [m, k]; b [n, k] (B_DN) or [k, n] (B_ND). F16/BF16 arrays are uint16 bit patterns.
+    ``bias`` [n] float32 joins the chain after ``bias_after_k`` values of k (TMATMUL_BIAS on the first chunk;
+    0 = after the whole K)."""
     store = np.float32 if in_dtype == F32 else np.uint16
     a = _c(a, store)
     b = _c(b, store)
@@ -94,24 +101,35 @@ def gemm_f32acc(a: np.ndarray, b: np.ndarray, in_dtype: int, b_layout: int = B_D
     n = b.shape[0] if b_layout == B_DN else b.shape[1]
     assert (b.shape[1] if b_layout == B_DN else b.shape[0]) == k
     c = np.empty((m, n), dtype=np.float32)
+    if bias is not None:
+        bias = _c(bias, np.float32)
+        assert bias.shape == (n,)
+        _lib().pto_oracle_gemm_f32acc_bias(_ptr(a), _ptr(b), _ptr(bias), bias_after_k, _ptr(c), m, n, k, a.shape[1],
+                                           b.shape[1], n, in_dtype, b_layout, threads)
+        return c
     _lib().pto_oracle_gemm_f32acc(_ptr(a), _ptr(b), _ptr(c), m, n, k, a.shape[1], b.shape[1], n, in_dtype, b_layout,
                                   threads)
     return c
 
 
-def gemm_s8(a: np.ndarray, b_dn: np.ndarray, threads: int = 0) -> np.ndarray:
+def gemm_s8(a: np.ndarray, b_dn: np.ndarray, threads: int = 0, bias: np.ndarray | None = None) -> np.ndarray:
     a = _c(a, np.int8)
     b_dn = _c(b_dn, np.int8)
     m, k = a.shape
     n = b_dn.shape[0]
     assert b_dn.shape[1] == k
     c = np.empty((m, n), dtype=np.int32)
+    if bias is not None:
+        bias = _c(bias, np.int32)
+        assert bias.shape == (n,)
+        _lib().pto_oracle_gemm_s8_bias(_ptr(a), _ptr(b_dn), _ptr(bias), _ptr(c), m, n, k, k, k, n, threads)
+        return c
     _lib().pto_oracle_gemm_s8(_ptr(a), _ptr(b_dn), _ptr(c), m, n, k, k, k, n, threads)
     return c
 
 
 def gemm_mx(a: np.ndarray, b_dn: np.ndarray, sfa: np.ndarray, sfb: np.ndarray, a_fmt: int = E4M3, b_fmt: int = E4M3,
-            threads: int = 0) -> np.ndarray:
+            threads: int = 0, bias: np.ndarray | None = None, bias_after_k: int = 0) -> np.ndarray:
     a = _c(a, np.uint8)
     b_dn = _c(b_dn, np.uint8)
     sfa = _c(sfa, np.uint8)
@@ -120,6 +138,12 @@ def gemm_mx(a: np.ndarray, b_dn: np.ndarray, sfa: np.ndarray, sfb: np.ndarray, a
     n = b_dn.shape[0]
     assert b_dn.shape[1] == k and sfa.shape == (m, k // 32) and sfb.shape == (n, k // 32)
     c = np.empty((m, n), dtype=np.float32)
+    if bias is not None:
+        bias = _c(bias, np.float32)
+        assert bias.shape == (n,)
+        _lib().pto_oracle_gemm_mx_bias(_ptr(a), _ptr(b_dn), _ptr(sfa), _ptr(sfb), _ptr(bias), bias_after_k, _ptr(c), m,
+                                       n, k, k, k, n, k // 32, k // 32, a_fmt, b_fmt, threads)
+        return c
     _lib().pto_oracle_gemm_mx(_ptr(a), _ptr(b_dn), _ptr(sfa), _ptr(sfb), _ptr(c), m, n, k, k, k, n, k // 32, k // 32,
                               a_fmt, b_fmt, threads)
     return c
@@ -178,6 +202,10 @@ class Ref:
         lib.ref_tile_f32.argtypes = [_p, _p, _p, _i]
         lib.ref_tile_s8.argtypes = [_p, _p, _p, _i]
         lib.ref_tile_mx.argtypes = [_p, _p, _p, _p, _p, _i, _i, _i]
+        if hasattr(lib, "ref_tile_f16_bias"):  # absent from a shim built before the bias entry points existed
+            lib.ref_tile_f16_bias.argtypes = [_p, _p, _p, _p, _i]
+            lib.ref_tile_s8_bias.argtypes = [_p, _p, _p, _p, _i]
+            lib.ref_tile_mx_bias.argtypes = [_p, _p, _p, _p, _p, _p, _i]
         lib.ref_dequant_col.argtypes = [ctypes.c_int32, ctypes.c_float]
         lib.ref_dequant_col.restype = ctypes.c_float
         lib.ref_cast_bf16.argtypes = [ctypes.c_float]
@@ -218,6 +246,23 @@ class Ref:
     def tile_s8(self, a, b_dn):
         return self._tile(self.lib.ref_tile_s8, a, b_dn, np.int8, np.int32)
 
+    def tile_f16_bias(self, a, b_dn, bias):
+        """TMATMUL_BIAS on the first 64-deep chunk, TMATMUL_ACC on the rest; fp16 bit patterns, fp32 bias [256]."""
+        a, b_dn, bias = _c(a, np.uint16), _c(b_dn, np.uint16), _c(bias, np.float32)
+        assert a.shape[0] == self.TILE_M and b_dn.shape == (self.TILE_N, a.shape[1]) and bias.shape == (self.TILE_N,)
+        out = np.empty((self.TILE_M, self.TILE_N), dtype=np.float32)
+        if self.lib.ref_tile_f16_bias(_ptr(out), _ptr(a), _ptr(b_dn), _ptr(bias), a.shape[1]) != 0:
+            raise ValueError("K must be a positive multiple of 64")
+        return out
+
+    def tile_s8_bias(self, a, b_dn, bias):
+        a, b_dn, bias = _c(a, np.int8), _c(b_dn, np.int8), _c(bias, np.int32)
+        assert a.shape[0] == self.TILE_M and b_dn.shape == (self.TILE_N, a.shape[1]) and bias.shape == (self.TILE_N,)
+        out = np.empty((self.TILE_M, self.TILE_N), dtype=np.int32)
+        if self.lib.ref_tile_s8_bias(_ptr(out), _ptr(a), _ptr(b_dn), _ptr(bias), a.shape[1]) != 0:
+            raise ValueError("K must be a positive multiple of 64")
+        return out
+
     def tile_mx(self, a, b_dn, sfa, sfb, a_fmt=E4M3, b_fmt=E4M3):
         a = _c(a, np.uint8)
         b_dn = _c(b_dn, np.uint8)
@@ -230,6 +275,17 @@ class Ref:
         rc = self.lib.ref_tile_mx(_ptr(out), _ptr(a), _ptr(b_dn), _ptr(sfa), _ptr(sfb), k, a_fmt, b_fmt)
         if rc != 0:
             raise ValueError("unsupported K or format for ref_tile_mx")
+        return out
+
+    def tile_mx_bias(self, a, b_dn, sfa, sfb, bias):
+        """e4m3 x e4m3 tile, six-operand TMATMUL_MX (fp32 bias [256]) on the first 128-deep chunk."""
+        a, b_dn, sfa, sfb = _c(a, np.uint8), _c(b_dn, np.uint8), _c(sfa, np.uint8), _c(sfb, np.uint8)
+        bias = _c(bias, np.float32)
+        k = a.shape[1]
+        assert a.shape[0] == self.TILE_M and b_dn.shape == (self.TILE_N, k) and bias.shape == (self.TILE_N,)
+        out = np.empty((self.TILE_M, self.TILE_N), dtype=np.float32)
+        if self.lib.ref_tile_mx_bias(_ptr(out), _ptr(a), _ptr(b_dn), _ptr(sfa), _ptr(sfb), _ptr(bias), k) != 0:
+            raise ValueError("K must be a positive multiple of 128")
         return out
 
     def mx_quantize_e4m3(self, src):

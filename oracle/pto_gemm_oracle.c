@@ -203,6 +203,8 @@ typedef struct {
     float* c;
     int n, k;
     long long ldc;
+    const float* bias; /* per column, or NULL */
+    int bias_after_k;  /* the bias joins the chain after this many k (the first TMATMUL_BIAS chunk) */
 } dense_ctx;
 
 /* acc[j] = fmaf(a, b[j], acc[j]) for one k; fused, single rounding, like std::fma in TMatmulNzZn. */
@@ -248,10 +250,17 @@ static void dense_rows(void* vctx, int r0, int r1)
 #if defined(__x86_64__)
                 if (hw) {
                     fma_row_hw(acc, brow, arow[kk], jn);
-                    continue;
-                }
+                } else
 #endif
-                fma_row_sw(acc, brow, arow[kk], jn);
+                {
+                    fma_row_sw(acc, brow, arow[kk], jn);
+                }
+                if (x->bias && kk + 1 == x->bias_after_k) {
+                    /* TMATMUL_BIAS: the finished first chunk, then += bias per column (cpu/TMatmul.hpp:223-229) */
+                    for (int j = 0; j < jn; ++j) {
+                        acc[j] += x->bias[j0 + j];
+                    }
+                }
             }
             memcpy(x->c + (size_t)i * x->ldc + j0, acc, (size_t)jn * sizeof(float));
         }
@@ -273,8 +282,18 @@ static float load_as_float(const void* base, size_t idx, int dtype)
 void pto_oracle_gemm_f32acc(const void* a, const void* b, float* c, int m, int n, int k, long long lda,
                             long long ldb, long long ldc, int in_dtype, int b_layout, int threads)
 {
+    pto_oracle_gemm_f32acc_bias(a, b, NULL, 0, c, m, n, k, lda, ldb, ldc, in_dtype, b_layout, threads);
+}
+
+void pto_oracle_gemm_f32acc_bias(const void* a, const void* b, const float* bias, int bias_after_k, float* c, int m,
+                                 int n, int k, long long lda, long long ldb, long long ldc, int in_dtype,
+                                 int b_layout, int threads)
+{
     if (m <= 0 || n <= 0 || k <= 0) {
         return;
+    }
+    if (bias_after_k <= 0 || bias_after_k > k) {
+        bias_after_k = k;
     }
     float* af = (float*)malloc((size_t)m * k * sizeof(float));
     float* bt = (float*)malloc((size_t)k * n * sizeof(float));
@@ -302,7 +321,7 @@ void pto_oracle_gemm_f32acc(const void* a, const void* b, float* c, int m, int n
             }
         }
     }
-    dense_ctx x = {af, bt, c, n, k, ldc};
+    dense_ctx x = {af, bt, c, n, k, ldc, bias, bias_after_k};
     parallel_rows(dense_rows, &x, m, threads);
     free(af);
     free(bt);
@@ -316,6 +335,7 @@ typedef struct {
     int32_t* c;
     int n, k;
     long long lda, ldc;
+    const int32_t* bias; /* per column, or NULL; integer addition commutes, so its place in the chain is free */
 } s8_ctx;
 
 static void s8_rows(void* vctx, int r0, int r1)
@@ -334,6 +354,11 @@ static void s8_rows(void* vctx, int r0, int r1)
                     acc[j] += av * brow[j];
                 }
             }
+            if (x->bias) {
+                for (int j = 0; j < jn; ++j) {
+                    acc[j] = (int32_t)((uint32_t)acc[j] + (uint32_t)x->bias[j0 + j]);
+                }
+            }
             memcpy(x->c + (size_t)i * x->ldc + j0, acc, (size_t)jn * sizeof(int32_t));
         }
     }
@@ -341,6 +366,12 @@ static void s8_rows(void* vctx, int r0, int r1)
 
 void pto_oracle_gemm_s8(const int8_t* a, const int8_t* b, int32_t* c, int m, int n, int k, long long lda,
                         long long ldb, long long ldc, int threads)
+{
+    pto_oracle_gemm_s8_bias(a, b, NULL, c, m, n, k, lda, ldb, ldc, threads);
+}
+
+void pto_oracle_gemm_s8_bias(const int8_t* a, const int8_t* b, const int32_t* bias, int32_t* c, int m, int n, int k,
+                             long long lda, long long ldb, long long ldc, int threads)
 {
     if (m <= 0 || n <= 0 || k <= 0) {
         return;
@@ -354,7 +385,7 @@ void pto_oracle_gemm_s8(const int8_t* a, const int8_t* b, int32_t* c, int m, int
             bt[(size_t)kk * n + j] = b[(size_t)j * ldb + kk];
         }
     }
-    s8_ctx x = {a, bt, c, n, k, lda, ldc};
+    s8_ctx x = {a, bt, c, n, k, lda, ldc, bias};
     parallel_rows(s8_rows, &x, m, threads);
     free(bt);
 }
@@ -368,6 +399,8 @@ typedef struct {
     float* c;
     int n, k, a_fmt;
     long long lda, ldc, ld_sfa;
+    const float* bias; /* per column, or NULL */
+    int bias_after_k;
 } mx_ctx;
 
 static void mx_rows(void* vctx, int r0, int r1)
@@ -397,6 +430,12 @@ static void mx_rows(void* vctx, int r0, int r1)
                        double (8-bit significands times powers of two), so the grouping of its factors is free. */
                     acc[j] = (float)((double)acc[j] + av * brow[j]);
                 }
+                if (x->bias && kk + 1 == x->bias_after_k) {
+                    /* six-operand TMATMUL_MX: the finished first chunk, then += bias (cpu/TMatmul.hpp:285-291) */
+                    for (int j = 0; j < jn; ++j) {
+                        acc[j] += x->bias[j0 + j];
+                    }
+                }
             }
             memcpy(x->c + (size_t)i * x->ldc + j0, acc, (size_t)jn * sizeof(float));
         }
@@ -408,8 +447,19 @@ void pto_oracle_gemm_mx(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, 
                         int n, int k, long long lda, long long ldb, long long ldc, long long ld_sfa,
                         long long ld_sfb, int a_fmt, int b_fmt, int threads)
 {
+    pto_oracle_gemm_mx_bias(a, b, sfa, sfb, NULL, 0, c, m, n, k, lda, ldb, ldc, ld_sfa, ld_sfb, a_fmt, b_fmt, threads);
+}
+
+void pto_oracle_gemm_mx_bias(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, const uint8_t* sfb,
+                             const float* bias, int bias_after_k, float* c, int m, int n, int k, long long lda,
+                             long long ldb, long long ldc, long long ld_sfa, long long ld_sfb, int a_fmt, int b_fmt,
+                             int threads)
+{
     if (m <= 0 || n <= 0 || k <= 0) {
         return;
+    }
+    if (bias_after_k <= 0 || bias_after_k > k) {
+        bias_after_k = k;
     }
     double* bt = (double*)malloc((size_t)k * n * sizeof(double));
     if (!bt) {
@@ -421,7 +471,7 @@ void pto_oracle_gemm_mx(const uint8_t* a, const uint8_t* b, const uint8_t* sfa, 
                                      pto_oracle_e8m0_to_double(sfb[(size_t)j * ld_sfb + kk / 32]);
         }
     }
-    mx_ctx x = {a, sfa, bt, c, n, k, a_fmt, lda, ldc, ld_sfa};
+    mx_ctx x = {a, sfa, bt, c, n, k, a_fmt, lda, ldc, ld_sfa, bias, bias_after_k};
     parallel_rows(mx_rows, &x, m, threads);
     free(bt);
 }

@@ -51,7 +51,8 @@ void run_s8_tile(int32_t* out, const int8_t* a, const int8_t* b_dn)
 }
 
 template <typename AT, typename BT>
-void run_mx_tile(float* out, const uint8_t* a, const uint8_t* b_dn, const uint8_t* sfa, const uint8_t* sfb, int k)
+void run_mx_tile(float* out, const uint8_t* a, const uint8_t* b_dn, const uint8_t* sfa, const uint8_t* sfb, int k,
+                 const float* bias = nullptr)
 {
     constexpr int M = 128, N = 256, KC = 128, KS = KC / 32;
     NPU_MEMORY_INIT(NPUArch::A5);
@@ -70,6 +71,14 @@ void run_mx_tile(float* out, const uint8_t* a, const uint8_t* b_dn, const uint8_
     TASSIGN(saTile, GetScaleAddr(aTile.data()));
     TASSIGN(sbTile, GetScaleAddr(bTile.data()));
     TASSIGN(cTile, 0x0);
+    using BiasTile = Tile<TileType::Bias, float, 1, N, BLayout::RowMajor, 1, N>;
+    BiasTile biasTile;
+    TASSIGN(biasTile, 0x0);
+    if (bias != nullptr) {
+        for (int j = 0; j < N; ++j) {
+            biasTile.SetElement(0, j, bias[j]);
+        }
+    }
     const int kg = k / 32;
     for (int k0 = 0; k0 < k; k0 += KC) {
         for (int i = 0; i < M; ++i) {
@@ -88,7 +97,9 @@ void run_mx_tile(float* out, const uint8_t* a, const uint8_t* b_dn, const uint8_
                 sbTile.SetElement(g, j, float8_e8m0_t::FromRaw(sfb[static_cast<size_t>(j) * kg + k0 / 32 + g]));
             }
         }
-        if (k0 == 0) {
+        if (k0 == 0 && bias != nullptr) {
+            TMATMUL_MX(cTile, aTile, saTile, bTile, sbTile, biasTile);
+        } else if (k0 == 0) {
             TMATMUL_MX(cTile, aTile, saTile, bTile, sbTile);
         } else {
             TMATMUL_MX(cTile, cTile, aTile, saTile, bTile, sbTile);
@@ -101,9 +112,86 @@ void run_mx_tile(float* out, const uint8_t* a, const uint8_t* b_dn, const uint8_
     }
 }
 
+// One 128 x 256 tile through TMATMUL_BIAS on the first 64-deep K chunk and TMATMUL_ACC on the rest, the way a K loop
+// uses the bias form (tests/cpu/st/testcase/tmatmul/tmatmul_kernel.cpp:86-96 for the single-chunk case).
+template <typename AccT, typename InT, typename RawT>
+void run_bias_tile(AccT* out, const RawT* a, const RawT* b_dn, const AccT* bias, int k)
+{
+    constexpr int M = 128, N = 256, KC = 64;
+    using LeftTile = TileLeft<InT, M, KC, M, KC>;
+    using RightTile = TileRight<InT, KC, N, KC, N>;
+    using AccTile = TileAcc<AccT, M, N, M, N>;
+    using BiasTile = Tile<TileType::Bias, AccT, 1, N, BLayout::RowMajor, 1, N>;
+    LeftTile aTile;
+    RightTile bTile;
+    AccTile cTile;
+    BiasTile biasTile;
+    TASSIGN(aTile, 0x0);
+    TASSIGN(bTile, 0x0);
+    TASSIGN(cTile, 0x0);
+    TASSIGN(biasTile, 0x0);
+    for (int j = 0; j < N; ++j) {
+        biasTile.SetElement(0, j, bias[j]);
+    }
+    const InT* at = reinterpret_cast<const InT*>(a);
+    const InT* bt = reinterpret_cast<const InT*>(b_dn);
+    for (int k0 = 0; k0 < k; k0 += KC) {
+        for (int i = 0; i < M; ++i) {
+            for (int kk = 0; kk < KC; ++kk) {
+                aTile.SetElement(i, kk, at[static_cast<size_t>(i) * k + k0 + kk]);
+            }
+        }
+        for (int j = 0; j < N; ++j) {
+            for (int kk = 0; kk < KC; ++kk) {
+                bTile.SetElement(kk, j, bt[static_cast<size_t>(j) * k + k0 + kk]);
+            }
+        }
+        if (k0 == 0) {
+            TMATMUL_BIAS(cTile, aTile, bTile, biasTile);
+        } else {
+            TMATMUL_ACC(cTile, cTile, aTile, bTile);
+        }
+    }
+    for (int i = 0; i < M; ++i) {
+        for (int j = 0; j < N; ++j) {
+            out[static_cast<size_t>(i) * N + j] = cTile.GetElement(i, j);
+        }
+    }
+}
+
 } // namespace
 
 extern "C" {
+
+// 128 x 256 output tile, bias form: TMATMUL_BIAS on k in [0, 64), TMATMUL_ACC afterwards. k % 64 == 0.
+int ref_tile_f16_bias(float* out, const uint16_t* a, const uint16_t* b_dn, const float* bias, int k)
+{
+    if (k <= 0 || k % 64 != 0) {
+        return -1;
+    }
+    run_bias_tile<float, half, uint16_t>(out, a, b_dn, bias, k);
+    return 0;
+}
+
+// e4m3 x e4m3 MX tile with the six-operand TMATMUL_MX (bias) on the first 128-deep chunk. k % 128 == 0.
+int ref_tile_mx_bias(float* out, const uint8_t* a, const uint8_t* b_dn, const uint8_t* sfa, const uint8_t* sfb,
+                     const float* bias, int k)
+{
+    if (k <= 0 || k % 128 != 0 || bias == nullptr) {
+        return -1;
+    }
+    run_mx_tile<float8_e4m3_t, float8_e4m3_t>(out, a, b_dn, sfa, sfb, k, bias);
+    return 0;
+}
+
+int ref_tile_s8_bias(int32_t* out, const int8_t* a, const int8_t* b_dn, const int32_t* bias, int k)
+{
+    if (k <= 0 || k % 64 != 0) {
+        return -1;
+    }
+    run_bias_tile<int32_t, int8_t, int8_t>(out, a, b_dn, bias, k);
+    return 0;
+}
 
 // 1 if this build has the simulator's real bfloat16_t (std::bfloat16_t), 0 if it is the _Float16 placeholder.
 int ref_has_real_bf16()

@@ -2,7 +2,8 @@
 
 Host-side mirror of the reference's GEMM entry points over the C ABI in ``include/pto_b200.h``:
 ``gemm`` (TLOAD -> TMATMUL/TMATMUL_ACC -> TSTORE), ``gemm_s8_dequant`` (int8 + fixpipe dequant),
-``gemm_mx`` (TMATMUL_MX, e8m0 block scales), ``pto_gemm_basic`` (the torch op of demos/baseline/gemm_basic)
+``gemm_mx`` (TMATMUL_MX, e8m0 block scales), ``gemv`` (TGEMV), ``mx_quantize_e4m3`` (TQUANT, MXFP8),
+``pto_gemm_basic`` (the torch op of demos/baseline/gemm_basic)
 and the K-split GEMM + allreduce (``ksplit``). PyTorch is used for device memory, streams and
 torch.distributed only; all arithmetic runs in the CUDA library.
 """
@@ -15,12 +16,15 @@ from .gemm import (
     gemm_mx,
     gemm_mx_workspace_bytes,
     gemm_s8_dequant,
+    gemv,
     launch_count,
+    mx_quantize_e4m3,
     pto_gemm_basic,
 )
 
 __all__ = [
-    "gemm", "gemm_s8_dequant", "gemm_mx", "gemm_mx_workspace_bytes", "cast_f32_to_bf16", "pto_gemm_basic",
+    "gemm", "gemm_s8_dequant", "gemm_mx", "gemm_mx_workspace_bytes", "gemv", "mx_quantize_e4m3", "cast_f32_to_bf16",
+    "pto_gemm_basic",
     "device_status", "launch_count", "PtoB200Error",
     "F16", "BF16", "F32", "S8", "S32", "E4M3", "E5M2", "B_DN", "B_ND",
 ]

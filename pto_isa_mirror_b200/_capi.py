@@ -31,6 +31,10 @@ SYMBOLS = {
         _i,
         [ctypes.c_void_p, _u8p, _u8p, _u8p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i, _i, _u8p, ctypes.c_size_t],
     ),
+    "pto_b200_gemm_bias": (
+        _i,
+        [ctypes.c_void_p, _u8p, _u8p, _u8p, _u8p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i],
+    ),
     "pto_b200_gemm_s8_dequant": (
         _i,
         [ctypes.c_void_p, _u8p, _u8p, _u8p, ctypes.c_void_p, ctypes.c_void_p, _i, _i, _i, _ll, _ll, _ll],
@@ -40,7 +44,14 @@ SYMBOLS = {
         [ctypes.c_void_p, _u8p, _u8p, _u8p, _u8p, _u8p, _u8p, ctypes.c_size_t, _i, _i, _i, _ll, _ll, _ll, _ll, _ll,
          _i, _i, _i],
     ),
+    "pto_b200_gemm_mx_bias": (
+        _i,
+        [ctypes.c_void_p, _u8p, _u8p, _u8p, _u8p, _u8p, _u8p, _u8p, ctypes.c_size_t, _i, _i, _i, _ll, _ll, _ll, _ll,
+         _ll, _i, _i, _i],
+    ),
     "pto_b200_gemm_mx_workspace_bytes": (ctypes.c_size_t, [_i, _i, _i]),
+    "pto_b200_gemv": (_i, [ctypes.c_void_p, _u8p, _u8p, _u8p, _u8p, _i, _i, _ll, _i, _i]),
+    "pto_b200_mx_quantize_e4m3": (_i, [ctypes.c_void_p, _u8p, _u8p, _u8p, _i, _i, _ll, _ll, _ll]),
     "pto_b200_gemm_mx_static": (
         _i,
         [ctypes.c_void_p, _u8p, _u8p, _u8p, _u8p, _u8p, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _i, _i, _i],

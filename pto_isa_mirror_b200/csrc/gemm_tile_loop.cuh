@@ -45,6 +45,7 @@ struct GemmParams {
     const float* s_col;
     const uint8_t* sfa; // scale factors re-tiled to 512-byte atoms, index (k_block, m_block)
     const uint8_t* sfb; // same, index (k_block, n_block)
+    const void* bias;   // TMATMUL_BIAS: one value per output column in the accumulator's type (fp32 / int32), or null
     int* status;
     // CTA-pair kernels, last partly filled wave: each leftover tile is cut in two K halves that run on two pairs at
     // once; the first half parks its fp32 / int32 accumulators in the workspace, the second half adds them and stores.
@@ -124,12 +125,9 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& mi,
 }
 
 template <int EPI>
-__device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], const GemmParams& p, int row, int col0,
-                                            bool vec_ok, float s_row)
+__device__ __forceinline__ void store_chunk_nobias(const uint32_t (&v)[32], const GemmParams& p, int row, int col0,
+                                                   bool vec_ok, float s_row)
 {
-    if (row >= p.m) {
-        return;
-    }
     const int n_left = p.n - col0;
     if constexpr (EPI == EPI_F32 || EPI == EPI_S32) {
         uint32_t* dst = reinterpret_cast<uint32_t*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
@@ -195,6 +193,35 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], const GemmP
             }
         }
     }
+}
+
+// One 32-column chunk of one accumulator row: optional bias, then cast / dequantise and store. The bias is added to
+// the finished accumulator in the accumulator's own type, once per output element (TMATMUL_BIAS adds it after the
+// first matmul of the K loop, include/pto/cpu/TMatmul.hpp:219-230: exact for int32, one fp32 rounding apart otherwise).
+template <int EPI>
+__device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], const GemmParams& p, int row, int col0,
+                                            bool vec_ok, float s_row)
+{
+    if (row >= p.m) {
+        return;
+    }
+    if (p.bias == nullptr) {
+        store_chunk_nobias<EPI>(v, p, row, col0, vec_ok, s_row);
+        return;
+    }
+    const int n_left = p.n - col0;
+    uint32_t w[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        if constexpr (EPI == EPI_S32 || EPI == EPI_DEQ_BF16) {
+            const uint32_t b = (i < n_left) ? __ldg(static_cast<const uint32_t*>(p.bias) + col0 + i) : 0u;
+            w[i] = v[i] + b; // two's complement: the int32 sum
+        } else {
+            const float b = (i < n_left) ? __ldg(static_cast<const float*>(p.bias) + col0 + i) : 0.0f;
+            w[i] = __float_as_uint(__fadd_rn(__uint_as_float(v[i]), b));
+        }
+    }
+    store_chunk_nobias<EPI>(w, p, row, col0, vec_ok, s_row);
 }
 
 template <int KIND, int BLOCK_N, int STAGES, int EPI, bool B_MN_MAJOR>

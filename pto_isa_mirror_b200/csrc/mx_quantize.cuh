@@ -1,0 +1,76 @@
+// OCP MX quantisation on the device: fp32 [rows][k] -> e4m3fn bytes [rows][k] + one e8m0 scale per 32 elements of K.
+//
+// Follows TQUANT<QuantType::MXFP8> with the OCP scale rule (include/pto/cpu/TQuant.hpp: group maximum and shared
+// exponent ComputeSharedExponent :178-190, scaling factor ComputeMxScalingFromExponent :226-237, element encoding
+// EncodeE4M3Fn :118-153, grouping of 32 along the row QuantizeMxTile :461-494; MX_BLOCK_SIZE = 32,
+// include/pto/common/constants.hpp:42):
+//   e8m0    = max(biased_exponent(absmax of the 32 values) - 8, 0)
+//   scaling = 2^(127 - e8m0)
+//   byte    = nearest e4m3fn code of clamp(x * scaling, +-448), ties to the even code; a result that rounds to zero
+//             is stored as +0 (0x00) whatever its sign.
+// Inputs must be finite (a NaN or infinity in a block is outside the supported domain).
+//
+// HBM-bound: 4 bytes read and 1 + 1/32 bytes written per element. Eight consecutive lanes own one block of 32
+// values (one 16-byte load each), share the maximum with three shuffles and store 4 bytes each, so a warp reads 512
+// contiguous bytes and writes 128.
+#pragma once
+#include <cuda_fp8.h>
+
+#include <cstdint>
+
+namespace pto_b200 {
+
+constexpr int kQuantThreads = 256;
+
+// Two floats -> two e4m3fn codes (low byte = first value), round to nearest even, saturating at +-448.
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi)
+{
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t drop_negative_zero(uint32_t four_codes)
+{
+    // a byte that is exactly 0x80 (negative zero) becomes 0x00; other bytes stay
+    const uint32_t magnitude = four_codes & 0x7F7F7F7Fu;
+    const uint32_t nonzero = ((magnitude + 0x7F7F7F7Fu) | magnitude) & 0x80808080u; // 0x80 per byte with magnitude != 0
+    return magnitude | (four_codes & nonzero);
+}
+
+// src: [rows][ld_src] floats (16-byte aligned rows); data: [rows][ld_data] bytes (4-byte aligned rows);
+// scales: [rows][ld_scales] bytes. k % 32 == 0.
+__global__ void __launch_bounds__(kQuantThreads) mx_quantize_e4m3_kernel(const float* __restrict__ src,
+                                                                          uint8_t* __restrict__ data,
+                                                                          uint8_t* __restrict__ scales, int rows, int k,
+                                                                          long long ld_src, long long ld_data,
+                                                                          long long ld_scales)
+{
+    const int k4 = k / 4;
+    const long long total = static_cast<long long>(rows) * k4; // 16-byte items; a multiple of 8 per row
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    // every lane of a warp runs the same number of iterations (total and stride are multiples of 8, and the
+    // shuffles below stay inside aligned groups of 8 lanes whose items are all in range or all out of range)
+    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += stride) {
+        const long long row = i / k4;
+        const int c4 = static_cast<int>(i - row * k4);
+        const float4 v = __ldcs(reinterpret_cast<const float4*>(src + row * ld_src) + c4);
+        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        const unsigned group_mask = 0xFFu << (threadIdx.x & 24u);
+        amax = fmaxf(amax, __shfl_xor_sync(group_mask, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(group_mask, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(group_mask, amax, 4));
+        const uint32_t exponent = (__float_as_uint(amax) & 0x7F800000u) >> 23;
+        const uint32_t e8m0 = exponent <= 8u ? 0u : exponent - 8u;
+        const float scaling = __uint_as_float((254u - e8m0) << 23); // e8m0 <= 246 for finite input: never zero
+        const uint32_t lo = cvt_e4m3x2(__fmul_rn(v.x, scaling), __fmul_rn(v.y, scaling));
+        const uint32_t hi = cvt_e4m3x2(__fmul_rn(v.z, scaling), __fmul_rn(v.w, scaling));
+        const uint32_t packed = drop_negative_zero(lo | (hi << 16));
+        *reinterpret_cast<uint32_t*>(data + row * ld_data + static_cast<long long>(c4) * 4) = packed;
+        if ((c4 & 7) == 0) {
+            scales[row * ld_scales + (c4 >> 3)] = static_cast<uint8_t>(e8m0);
+        }
+    }
+}
+
+} // namespace pto_b200

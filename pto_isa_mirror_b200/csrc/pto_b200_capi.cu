@@ -13,7 +13,9 @@
 
 #include "gemm_tile_loop.cuh"
 #include "gemm_tile_loop_2cta.cuh"
+#include "gemv.cuh"
 #include "ksplit_reduce.cuh"
+#include "mx_quantize.cuh"
 
 #if !defined(__CUDA_ARCH_LIST__)
 #error "pto_b200 is built with nvcc for sm_100a only"
@@ -351,12 +353,15 @@ extern "C" int pto_b200_gemm_ex(void* stream, uint8_t* out, const uint8_t* src0,
 
 extern "C" size_t pto_b200_gemm_workspace_bytes(void) { return kGemmWorkspaceBytes; }
 
-extern "C" int pto_b200_gemm_ws(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, int m, int n,
-                                int k, long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype,
-                                int b_layout, int launch_block_count, uint8_t* workspace, size_t workspace_bytes)
+static int gemm_dense_impl(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, int m, int n, int k,
+                           long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype, int b_layout,
+                           int launch_block_count, uint8_t* workspace, size_t workspace_bytes, const void* bias)
 {
     if (launch_block_count < 0) {
         return PTO_B200_EINVAL;
+    }
+    if (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 3u)) {
+        return PTO_B200_EALIGN;
     }
     if (workspace != nullptr && ((reinterpret_cast<uintptr_t>(workspace) & 15u) || workspace_bytes < kGemmWorkspaceBytes)) {
         return PTO_B200_EWORKSPACE;
@@ -389,6 +394,7 @@ extern "C" int pto_b200_gemm_ws(void* stream, uint8_t* out, const uint8_t* src0,
     const int kelems = kBlockKBytes / es;
     GemmParams p;
     fill_params(p, out, q, block_n, kelems, dev->status_ptr);
+    p.bias = bias;
     CUtensorMap ta, tb;
     if (int rc = make_tensor_map(&ta, in_dtype, src0, m, k, lda, kelems, kBlockM)) {
         return rc;
@@ -458,6 +464,25 @@ extern "C" int pto_b200_gemm_ws(void* stream, uint8_t* out, const uint8_t* src0,
     }
 }
 
+extern "C" int pto_b200_gemm_ws(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, int m, int n,
+                                int k, long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype,
+                                int b_layout, int launch_block_count, uint8_t* workspace, size_t workspace_bytes)
+{
+    return gemm_dense_impl(stream, out, src0, src1, m, n, k, lda, ldb, ldc, in_dtype, out_dtype, b_layout,
+                           launch_block_count, workspace, workspace_bytes, nullptr);
+}
+
+extern "C" int pto_b200_gemm_bias(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1,
+                                  const uint8_t* bias, int m, int n, int k, long long lda, long long ldb,
+                                  long long ldc, int in_dtype, int out_dtype, int b_layout)
+{
+    if (bias == nullptr) {
+        return PTO_B200_EINVAL;
+    }
+    return gemm_dense_impl(stream, out, src0, src1, m, n, k, lda, ldb, ldc, in_dtype, out_dtype, b_layout, 0, nullptr,
+                           0, bias);
+}
+
 extern "C" int pto_b200_gemm_s8_dequant(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1,
                                         const float* s_row, const float* s_col, int m, int n, int k, long long lda,
                                         long long ldb, long long ldc)
@@ -514,11 +539,14 @@ extern "C" size_t pto_b200_gemm_mx_workspace_bytes(int m, int n, int k)
     return k_blocks * (m_blocks + n_blocks) * 512;
 }
 
-extern "C" int pto_b200_gemm_mx(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1,
-                                const uint8_t* src2, const uint8_t* src3, uint8_t* workspace, size_t workspace_bytes,
-                                int m, int n, int k, long long lda, long long ldb, long long ldc, long long ld_sfa,
-                                long long ld_sfb, int a_dtype, int b_dtype, int out_dtype)
+static int gemm_mx_impl(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, const uint8_t* src2,
+                        const uint8_t* src3, uint8_t* workspace, size_t workspace_bytes, int m, int n, int k,
+                        long long lda, long long ldb, long long ldc, long long ld_sfa, long long ld_sfb, int a_dtype,
+                        int b_dtype, int out_dtype, const void* bias)
 {
+    if (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 3u)) {
+        return PTO_B200_EALIGN;
+    }
     const bool a_ok = (a_dtype == PTO_B200_E4M3 || a_dtype == PTO_B200_E5M2);
     const bool b_ok = (b_dtype == PTO_B200_E4M3 || b_dtype == PTO_B200_E5M2);
     if (!a_ok || !b_ok || !(out_dtype == PTO_B200_BF16 || out_dtype == PTO_B200_F32)) {
@@ -560,6 +588,7 @@ extern "C" int pto_b200_gemm_mx(void* stream, uint8_t* out, const uint8_t* src0,
         }
         uint8_t* sfa_ws = workspace;
         uint8_t* sfb_ws = workspace + static_cast<size_t>(p.k_blocks) * a_blocks * 512;
+        p.bias = bias;
         p.sfa = sfa_ws;
         p.sfb = sfb_ws;
         CUtensorMap ta, tb, tsa, tsb;
@@ -615,6 +644,28 @@ extern "C" int pto_b200_gemm_mx(void* stream, uint8_t* out, const uint8_t* src0,
     return run(false, pick_block_n(m, n, dev->sm_count));
 }
 
+extern "C" int pto_b200_gemm_mx(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1,
+                                const uint8_t* src2, const uint8_t* src3, uint8_t* workspace, size_t workspace_bytes,
+                                int m, int n, int k, long long lda, long long ldb, long long ldc, long long ld_sfa,
+                                long long ld_sfb, int a_dtype, int b_dtype, int out_dtype)
+{
+    return gemm_mx_impl(stream, out, src0, src1, src2, src3, workspace, workspace_bytes, m, n, k, lda, ldb, ldc, ld_sfa,
+                        ld_sfb, a_dtype, b_dtype, out_dtype, nullptr);
+}
+
+extern "C" int pto_b200_gemm_mx_bias(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1,
+                                     const uint8_t* src2, const uint8_t* src3, const uint8_t* bias, uint8_t* workspace,
+                                     size_t workspace_bytes, int m, int n, int k, long long lda, long long ldb,
+                                     long long ldc, long long ld_sfa, long long ld_sfb, int a_dtype, int b_dtype,
+                                     int out_dtype)
+{
+    if (bias == nullptr) {
+        return PTO_B200_EINVAL;
+    }
+    return gemm_mx_impl(stream, out, src0, src1, src2, src3, workspace, workspace_bytes, m, n, k, lda, ldb, ldc, ld_sfa,
+                        ld_sfb, a_dtype, b_dtype, out_dtype, bias);
+}
+
 extern "C" int pto_b200_cast_f32_to_bf16(void* stream, uint8_t* out, const uint8_t* in, long long count)
 {
     if (out == nullptr || in == nullptr || count < 0) {
@@ -637,6 +688,98 @@ extern "C" int pto_b200_cast_f32_to_bf16(void* stream, uint8_t* out, const uint8
         reinterpret_cast<const float*>(in), reinterpret_cast<__nv_bfloat16*>(out), count);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return note_cuda(cudaGetLastError(), "cast_f32_bf16 launch");
+}
+
+// ---------------------------------------------------------------- TGEMV (one left row) and the MX quantiser
+
+template <int IN>
+static int launch_gemv(cudaStream_t s, int grid, int out_dtype, const void* a, const void* b, const void* bias,
+                       void* out, int n, int k, long long ldb)
+{
+    if constexpr (IN == GEMV_S8) {
+        gemv_kernel<GEMV_S8, GEMV_OUT_S32><<<grid, kGemvThreads, 0, s>>>(a, b, bias, out, n, k, ldb);
+    } else {
+        switch (out_dtype) {
+            case PTO_B200_F32:
+                gemv_kernel<IN, GEMV_OUT_F32><<<grid, kGemvThreads, 0, s>>>(a, b, bias, out, n, k, ldb);
+                break;
+            case PTO_B200_BF16:
+                gemv_kernel<IN, GEMV_OUT_BF16><<<grid, kGemvThreads, 0, s>>>(a, b, bias, out, n, k, ldb);
+                break;
+            default:
+                gemv_kernel<IN, GEMV_OUT_F16><<<grid, kGemvThreads, 0, s>>>(a, b, bias, out, n, k, ldb);
+                break;
+        }
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return note_cuda(cudaGetLastError(), "gemv launch");
+}
+
+extern "C" int pto_b200_gemv(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1,
+                             const uint8_t* bias, int n, int k, long long ldb, int in_dtype, int out_dtype)
+{
+    const bool is16 = (in_dtype == PTO_B200_F16 || in_dtype == PTO_B200_BF16);
+    const bool is8 = (in_dtype == PTO_B200_S8);
+    if (!is16 && !is8) {
+        return PTO_B200_EDTYPE;
+    }
+    if (is16 && !(out_dtype == PTO_B200_F32 || out_dtype == PTO_B200_BF16 || out_dtype == PTO_B200_F16)) {
+        return PTO_B200_EDTYPE;
+    }
+    if (is8 && out_dtype != PTO_B200_S32) {
+        return PTO_B200_EDTYPE;
+    }
+    if (out == nullptr || src0 == nullptr || src1 == nullptr || n <= 0 || k <= 0 || ldb < k) {
+        return PTO_B200_EINVAL;
+    }
+    const int es = is8 ? 1 : 2;
+    const int out_es = (out_dtype == PTO_B200_F32 || out_dtype == PTO_B200_S32) ? 4 : 2;
+    if ((reinterpret_cast<uintptr_t>(src0) & 15u) || (reinterpret_cast<uintptr_t>(src1) & 15u) ||
+        ((ldb * es) & 15) != 0 || (reinterpret_cast<uintptr_t>(out) & static_cast<uintptr_t>(out_es - 1)) ||
+        (reinterpret_cast<uintptr_t>(bias) & 3u)) {
+        return PTO_B200_EALIGN;
+    }
+    DeviceInfo* dev = nullptr;
+    if (int rc = device_info(&dev)) {
+        return rc;
+    }
+    const int warps_per_block = kGemvThreads / 32;
+    const long long want = (static_cast<long long>(n) + warps_per_block - 1) / warps_per_block;
+    const long long cap = static_cast<long long>(dev->sm_count) * 8; // 8 x 256 threads fill an SM
+    const int grid = static_cast<int>(want < cap ? want : cap);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (is8) {
+        return launch_gemv<GEMV_S8>(s, grid, out_dtype, src0, src1, bias, out, n, k, ldb);
+    }
+    if (in_dtype == PTO_B200_BF16) {
+        return launch_gemv<GEMV_BF16>(s, grid, out_dtype, src0, src1, bias, out, n, k, ldb);
+    }
+    return launch_gemv<GEMV_F16>(s, grid, out_dtype, src0, src1, bias, out, n, k, ldb);
+}
+
+extern "C" int pto_b200_mx_quantize_e4m3(void* stream, uint8_t* data, uint8_t* scales, const uint8_t* src, int rows,
+                                         int k, long long ld_src, long long ld_data, long long ld_scales)
+{
+    if (data == nullptr || scales == nullptr || src == nullptr || rows <= 0 || k <= 0 || k % 32 != 0 || ld_src < k ||
+        ld_data < k || ld_scales < k / 32) {
+        return PTO_B200_EINVAL;
+    }
+    if ((reinterpret_cast<uintptr_t>(src) & 15u) || (ld_src & 3) != 0 || (reinterpret_cast<uintptr_t>(data) & 3u) ||
+        (ld_data & 3) != 0) {
+        return PTO_B200_EALIGN;
+    }
+    DeviceInfo* dev = nullptr;
+    if (int rc = device_info(&dev)) {
+        return rc;
+    }
+    const long long items = static_cast<long long>(rows) * (k / 4);
+    const long long want = (items + kQuantThreads - 1) / kQuantThreads;
+    const long long cap = static_cast<long long>(dev->sm_count) * 8;
+    const int grid = static_cast<int>(want < cap ? want : cap);
+    mx_quantize_e4m3_kernel<<<grid, kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float*>(src), data, scales, rows, k, ld_src, ld_data, ld_scales);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return note_cuda(cudaGetLastError(), "mx_quantize launch");
 }
 
 // ---------------------------------------------------------------- K-split reduction over peer memory

@@ -57,8 +57,11 @@ def gemm_workspace(device: torch.device, stream_ptr: int) -> torch.Tensor:
 
 def gemm(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype = torch.float32, b_layout: int = B_DN,
          out: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None,
-         launch_block_count: int = 0, workspace=None) -> torch.Tensor:
+         launch_block_count: int = 0, workspace=None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """C = A @ B with fp32 (int32 for int8 inputs) accumulation over the whole K.
+
+    ``bias``: n values of the accumulator type (float32, or int32 for int8 inputs) added per output column before the
+    store cast (TMATMUL_BIAS); not combined with ``launch_block_count`` / ``workspace``.
 
     ``launch_block_count`` caps the thread blocks (SMs) the GEMM occupies, 0 = all of them: the knob the reference's
     launchGemmCompute has for leaving cores to the communication kernel that runs beside it.
@@ -91,6 +94,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype = torch.float3
             raise ValueError("out has the wrong shape")
         out_dtype = out.dtype
     sp = _stream_ptr(stream)
+    if bias is not None:
+        if launch_block_count != 0 or workspace is not None:
+            raise ValueError("bias cannot be combined with launch_block_count or workspace")
+        want = torch.int32 if a.dtype == torch.int8 else torch.float32
+        if bias.dtype != want or not bias.is_cuda or bias.numel() != n or not bias.is_contiguous():
+            raise ValueError(f"bias must be a contiguous CUDA {want} tensor with {n} elements")
+        rc = lib.pto_b200_gemm_bias(sp, out.data_ptr(), a.data_ptr(), b.data_ptr(), bias.data_ptr(), m, n, k,
+                                    a.stride(0), b.stride(0), out.stride(0), _TORCH_TO_PTO[a.dtype],
+                                    _TORCH_TO_PTO[out_dtype], b_layout)
+        _capi.check(rc, "pto_b200_gemm_bias")
+        return out
     if isinstance(workspace, str):
         workspace = gemm_workspace(a.device, sp)
     ws_ptr, ws_bytes = (workspace.data_ptr(), workspace.numel()) if workspace is not None else (None, 0)
@@ -132,10 +146,11 @@ def gemm_mx_workspace_bytes(m: int, n: int, k: int) -> int:
 def gemm_mx(a: torch.Tensor, b_dn: torch.Tensor, sfa: torch.Tensor, sfb: torch.Tensor,
             out_dtype: torch.dtype = torch.bfloat16, a_fmt: int = E4M3, b_fmt: int = E4M3,
             workspace: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-            stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+            stream: Optional[torch.cuda.Stream] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """MX block-scaled fp8 GEMM (TMATMUL_MX): a [M, K] and b_dn [N, K] fp8 bytes (uint8 or torch fp8 dtypes),
     sfa [M, K/32] and sfb [N, K/32] e8m0 bytes (uint8). ``workspace`` is a uint8 CUDA tensor of at least
-    ``gemm_mx_workspace_bytes(m, n, k)`` bytes; one is allocated through torch when omitted."""
+    ``gemm_mx_workspace_bytes(m, n, k)`` bytes; one is allocated through torch when omitted. ``bias``: n float32
+    values added per column to the finished accumulator (the six-operand TMATMUL_MX)."""
     lib = _capi.load()
     for t, name in ((a, "a"), (b_dn, "b_dn"), (sfa, "sfa"), (sfb, "sfb")):
         _require_cuda_2d(t, name)
@@ -152,12 +167,69 @@ def gemm_mx(a: torch.Tensor, b_dn: torch.Tensor, sfa: torch.Tensor, sfb: torch.T
         workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
     if out is None:
         out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    if bias is not None:
+        if bias.dtype != torch.float32 or not bias.is_cuda or bias.numel() != n or not bias.is_contiguous():
+            raise ValueError(f"bias must be a contiguous CUDA float32 tensor with {n} elements")
+        rc = lib.pto_b200_gemm_mx_bias(_stream_ptr(stream), out.data_ptr(), a.data_ptr(), b_dn.data_ptr(),
+                                       sfa.data_ptr(), sfb.data_ptr(), bias.data_ptr(), workspace.data_ptr(),
+                                       workspace.numel(), m, n, k, a.stride(0), b_dn.stride(0), out.stride(0),
+                                       sfa.stride(0), sfb.stride(0), a_fmt, b_fmt, _TORCH_TO_PTO[out.dtype])
+        _capi.check(rc, "pto_b200_gemm_mx_bias")
+        return out
     rc = lib.pto_b200_gemm_mx(_stream_ptr(stream), out.data_ptr(), a.data_ptr(), b_dn.data_ptr(), sfa.data_ptr(),
                               sfb.data_ptr(), workspace.data_ptr(), workspace.numel(), m, n, k, a.stride(0),
                               b_dn.stride(0), out.stride(0), sfa.stride(0), sfb.stride(0), a_fmt, b_fmt,
                               _TORCH_TO_PTO[out.dtype])
     _capi.check(rc, "pto_b200_gemm_mx")
     return out
+
+
+def gemv(x: torch.Tensor, b_dn: torch.Tensor, out_dtype: torch.dtype = torch.float32,
+         bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+         stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """TGEMV: out[j] = sum_k x[k] * b_dn[j, k] (+ bias[j]) for one left row x [K] (or [1, K]) and column-major
+    b_dn [N, K]. float16 / bfloat16 inputs give float32 / bfloat16 / float16; int8 inputs give int32. Returns [N]."""
+    lib = _capi.load()
+    _require_cuda_2d(b_dn, "b_dn")
+    if not x.is_cuda or x.dtype != b_dn.dtype or x.numel() != b_dn.shape[1] or not x.is_contiguous():
+        raise ValueError("x must be a contiguous CUDA tensor of b_dn's dtype with K elements")
+    if x.dtype not in (torch.float16, torch.bfloat16, torch.int8):
+        raise ValueError("inputs must be float16, bfloat16 or int8")
+    n, k = b_dn.shape
+    if x.dtype == torch.int8:
+        out_dtype = torch.int32
+    if out is None:
+        out = torch.empty((n,), dtype=out_dtype, device=x.device)
+    elif out.numel() != n or not out.is_contiguous() or not out.is_cuda:
+        raise ValueError("out must be a contiguous CUDA tensor with N elements")
+    bias_ptr = None
+    if bias is not None:
+        want = torch.int32 if x.dtype == torch.int8 else torch.float32
+        if bias.dtype != want or not bias.is_cuda or bias.numel() != n or not bias.is_contiguous():
+            raise ValueError(f"bias must be a contiguous CUDA {want} tensor with {n} elements")
+        bias_ptr = bias.data_ptr()
+    rc = lib.pto_b200_gemv(_stream_ptr(stream), out.data_ptr(), x.data_ptr(), b_dn.data_ptr(), bias_ptr, n, k,
+                           b_dn.stride(0), _TORCH_TO_PTO[x.dtype], _TORCH_TO_PTO[out.dtype])
+    _capi.check(rc, "pto_b200_gemv")
+    return out
+
+
+def mx_quantize_e4m3(src: torch.Tensor, stream: Optional[torch.cuda.Stream] = None):
+    """OCP MX quantisation (TQUANT, MXFP8): float32 src [rows, K] -> (e4m3 bytes [rows, K] uint8, e8m0 scales
+    [rows, K/32] uint8), one scale per 32 elements along K. Finite input only."""
+    lib = _capi.load()
+    _require_cuda_2d(src, "src")
+    if src.dtype != torch.float32:
+        raise ValueError("src must be float32")
+    rows, k = src.shape
+    if k % 32 != 0:
+        raise ValueError("K must be a multiple of 32")
+    data = torch.empty((rows, k), dtype=torch.uint8, device=src.device)
+    scales = torch.empty((rows, k // 32), dtype=torch.uint8, device=src.device)
+    rc = lib.pto_b200_mx_quantize_e4m3(_stream_ptr(stream), data.data_ptr(), scales.data_ptr(), src.data_ptr(), rows,
+                                       k, src.stride(0), data.stride(0), scales.stride(0))
+    _capi.check(rc, "pto_b200_mx_quantize_e4m3")
+    return data, scales
 
 
 def cast_f32_to_bf16(src: torch.Tensor, out: Optional[torch.Tensor] = None,

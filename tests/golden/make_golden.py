@@ -1,6 +1,7 @@
 """Generate the golden fixtures under tests/golden/ by running the REFERENCE CPU simulator (oracle/_ref).
 
-Run where the reference tree is mounted:  make -C oracle && python tests/golden/make_golden.py
+Run where the reference tree is mounted:  make -C oracle && python tests/golden/make_golden.py [name fragment ...]
+(with fragments only the fixtures whose file name contains one of them are rewritten).
 Inputs are not stored: they are regenerated from pto_isa_mirror_b200.gen_data with the seeds below, and each
 fixture carries the SHA-256 of its input bytes so a drifting generator is caught. Outputs are the reference's.
 """
@@ -25,7 +26,16 @@ def sha(*arrays) -> str:
     return h.hexdigest()
 
 
+ONLY = sys.argv[1:]  # name fragments; empty = every fixture
+
+
+def wanted(name) -> bool:
+    return not ONLY or any(frag in name for frag in ONLY)
+
+
 def save(name, **kw):
+    if not wanted(name):
+        return
     np.savez_compressed(os.path.join(HERE, name + ".npz"), **kw)
     print("wrote", name, {k: getattr(v, "shape", v) for k, v in kw.items()})
 
@@ -80,6 +90,19 @@ def main():
     sfb = gd.randint((256, 8), 127, 129, 19, 5).astype(np.uint8)
     save("mx_randint_e4m3_e5m2_k256", out=ref.tile_mx(a8, b8, sfa, sfb, oracle.E4M3, oracle.E5M2), a=a8, b=b8, sfa=sfa,
          sfb=sfb)
+
+    # bias forms: TMATMUL_BIAS on the first chunk then TMATMUL_ACC (fp16 and int8), six-operand TMATMUL_MX
+    if wanted("bias"):
+        a, b = gd.dense_inputs(128, 256, 256, "f16", 7, "uniform")
+        bias = (gd.normal((256,), 8) * np.float32(3.0)).astype(np.float32)
+        save("f16_bias_k256", out=ref.tile_f16_bias(a, b, bias), bias=bias, input_sha=sha(a, b), seed=7)
+        a, b, _, _ = gd.s8_inputs(128, 256, 1024, 2)
+        bias_i = gd.randint((256,), -100000, 100000, 9, 0).astype(np.int32)
+        save("s8_bias_k1024", out=ref.tile_s8_bias(a, b, bias_i), bias=bias_i, input_sha=sha(a, b), seed=2)
+        a, sfa = ref.mx_quantize_e4m3(gd.normal((128, 256), 3, 0))
+        b, sfb = ref.mx_quantize_e4m3(gd.normal((256, 256), 3, 1))
+        save("mx_bias_k256", out=ref.tile_mx_bias(a, b, sfa, sfb, bias), bias=bias, a_sha=sha(a, sfa),
+             b_sha=sha(b, sfb), seed=3)
 
     # scalar tables: store casts, fp8 / e8m0 decode, quantiser
     x = np.concatenate([gd.normal((4096,), 5) * np.float32(3.0),

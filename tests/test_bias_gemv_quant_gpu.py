@@ -1,0 +1,223 @@
+"""Parity of the bias forms (TMATMUL_BIAS, six-operand TMATMUL_MX), TGEMV and the MX quantiser (TQUANT) with the
+oracle and the reference-generated fixtures, through the C ABI.
+
+Integer-valued cases (the reference tests' own style, tests/cpu/st/testcase/tmatmul/gen_data.py:40-61) must be exact;
+int32 accumulators and quantised bytes are bit-exact; fp32 results are held to the dense / MX tolerances."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import pto_isa_mirror_b200 as pto
+from conftest import golden
+from parity import max_rel_err, result_cmp
+from pto_isa_mirror_b200 import gen_data as gd
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DENSE_TOL = 1e-3
+MX_TOL = 1e-2
+
+
+def dev16(bits, dtype):
+    return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).to(DEV).view(dtype)
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(DEV)
+
+
+def host(t):
+    torch.cuda.synchronize()
+    if t.dtype in (torch.bfloat16, torch.float16):
+        return t.view(torch.int16).cpu().numpy().view(np.uint16)
+    return t.cpu().numpy()
+
+
+def padded(x, mult):
+    rows, cols = x.shape
+    pitch = (cols + mult - 1) // mult * mult
+    buf = torch.zeros((rows, pitch), dtype=x.dtype, device=DEV)
+    buf[:, :cols] = x
+    return buf[:, :cols]
+
+
+@pytest.fixture(autouse=True)
+def status_word_stays_clear():
+    yield
+    assert pto.device_status() == 0, "a kernel gave up on a bounded wait"
+
+
+# ------------------------------------------------------------------ bias
+
+def test_bias_golden_tiles():
+    g = golden("f16_bias_k256")
+    a, b = gd.dense_inputs(128, 256, 256, "f16", 7, "uniform")
+    out = host(pto.gemm(dev16(a, torch.float16), dev16(b, torch.float16), torch.float32, bias=dev(g["bias"])))
+    assert max_rel_err(out, g["out"]) <= DENSE_TOL
+    assert result_cmp(g["out"], out, DENSE_TOL)
+    out16 = host(pto.gemm(dev16(a, torch.float16), dev16(b, torch.float16), torch.bfloat16, bias=dev(g["bias"])))
+    assert np.array_equal(out16, gd.f32_to_bf16_bits(out))      # the bias joins before the store cast
+
+    g = golden("s8_bias_k1024")
+    a8, b8, _, _ = gd.s8_inputs(128, 256, 1024, 2)
+    assert np.array_equal(host(pto.gemm(dev(a8), dev(b8), torch.int32, bias=dev(g["bias"]))), g["out"])
+
+    g = golden("mx_bias_k256")
+    am, sfa = gd.mx_quantize_e4m3(gd.normal((128, 256), 3, 0))
+    bm, sfb = gd.mx_quantize_e4m3(gd.normal((256, 256), 3, 1))
+    outm = host(pto.gemm_mx(dev(am), dev(bm), dev(sfa), dev(sfb), torch.float32, bias=dev(g["bias"])))
+    assert max_rel_err(outm, g["out"]) <= MX_TOL
+
+
+# bias cases of tests/cpu/st/testcase/tmatmul/gen_data.py:108-111,118 (m, k, n there; m, n, k here)
+@pytest.mark.parametrize("kind,m,n,k", [("s8", 8, 6, 7), ("f16", 16, 16, 15), ("f16", 1, 50, 110), ("bf16", 16, 16, 15),
+                                        ("f16", 127, 63, 128)])
+def test_reference_bias_cases_exact(kind, m, n, k):
+    ai = gd.randint((m, k), 1, 5, 29, 0)
+    bi = gd.randint((n, k), 1, 5, 29, 1)
+    bias = gd.randint((n,), 1, 10, 29, 2)
+    exact = ai @ bi.T + bias[None, :]
+    if kind == "s8":
+        a = padded(dev(ai.astype(np.int8)), 16)
+        b = padded(dev(bi.astype(np.int8)), 16)
+        out = host(pto.gemm(a, b, torch.int32, bias=dev(bias.astype(np.int32))))
+        assert np.array_equal(out, exact)
+        assert np.array_equal(oracle.gemm_s8(ai.astype(np.int8), bi.astype(np.int8), bias=bias.astype(np.int32)), exact)
+        return
+    dt = torch.float16 if kind == "f16" else torch.bfloat16
+    a = padded(dev(ai.astype(np.float32)).to(dt), 8)
+    b = padded(dev(bi.astype(np.float32)).to(dt), 8)
+    out = host(pto.gemm(a, b, torch.float32, bias=dev(bias.astype(np.float32))))
+    assert np.array_equal(out.astype(np.int64), exact)
+    b_nd = padded(dev(np.ascontiguousarray(bi.T).astype(np.float32)).to(dt), 8)
+    out_nd = host(pto.gemm(a, b_nd, torch.float32, pto.B_ND, bias=dev(bias.astype(np.float32))))
+    assert np.array_equal(out_nd.astype(np.int64), exact)
+
+
+@pytest.mark.parametrize("kind", ["f16", "s8"])
+def test_bias_on_the_pair_kernel_exact(kind):
+    """Enough 256 x 256 tiles for the CTA-pair kernel (9 x 9 = 81 >= 74 pairs), ragged edges, integer values."""
+    m, n, k = 2200, 2290, 192
+    ai = gd.randint((m, k), -4, 4, 31, 0)
+    bi = gd.randint((n, k), -4, 4, 31, 1)
+    bias = gd.randint((n,), -1000, 1000, 31, 2)
+    exact = ai @ bi.T + bias[None, :]
+    if kind == "s8":
+        out = host(pto.gemm(dev(ai.astype(np.int8)), dev(bi.astype(np.int8)), torch.int32,
+                            bias=dev(bias.astype(np.int32))))
+        assert np.array_equal(out, exact)
+        rows = slice(1000, 1064)
+        assert np.array_equal(oracle.gemm_s8(ai[rows].astype(np.int8), bi.astype(np.int8), bias=bias.astype(np.int32)),
+                              exact[rows])
+    else:
+        a = dev(ai.astype(np.float32)).to(torch.float16)
+        b = dev(bi.astype(np.float32)).to(torch.float16)
+        out = host(pto.gemm(a, b, torch.float32, bias=dev(bias.astype(np.float32))))
+        assert np.array_equal(out.astype(np.int64), exact)
+        out16 = host(pto.gemm(a, b, torch.bfloat16, bias=dev(bias.astype(np.float32))))
+        assert np.array_equal(out16, oracle.store_cast(exact.astype(np.float32), oracle.BF16))
+
+
+def test_mx_bias_on_the_pair_kernel():
+    m, n, k = 2304, 2304, 256
+    am, sfa = gd.mx_quantize_e4m3(gd.normal((m, k), 33, 0))
+    bm, sfb = gd.mx_quantize_e4m3(gd.normal((n, k), 33, 1))
+    bias = (gd.normal((n,), 33, 2) * np.float32(4.0)).astype(np.float32)
+    out = host(pto.gemm_mx(dev(am), dev(bm), dev(sfa), dev(sfb), torch.float32, bias=dev(bias)))
+    rows = slice(1200, 1264)
+    ref = oracle.gemm_mx(am[rows], bm, sfa[rows], sfb, bias=bias, bias_after_k=128)
+    assert max_rel_err(out[rows], ref) <= MX_TOL
+    plain = host(pto.gemm_mx(dev(am), dev(bm), dev(sfa), dev(sfb), torch.float32))
+    assert np.array_equal(out, plain + bias[None, :])           # one fp32 add of the same accumulator
+
+
+# ------------------------------------------------------------------ TGEMV
+
+# m = 1 cases of tests/cpu/st/testcase/tmatmul/gen_data.py:106,111 plus ragged K tails and an int8 row
+@pytest.mark.parametrize("kind,n,k", [("f16", 50, 110), ("bf16", 64, 128), ("f16", 513, 1000), ("s8", 90, 89),
+                                      ("s8", 300, 4112)])
+def test_gemv_integer_cases_exact(kind, n, k):
+    xi = gd.randint((1, k), 1, 5, 37, 0)
+    bi = gd.randint((n, k), 1, 5, 37, 1)
+    bias = gd.randint((n,), 1, 10, 37, 2)
+    exact = (xi @ bi.T)[0]
+    if kind == "s8":
+        x = dev(xi[0].astype(np.int8))
+        b = padded(dev(bi.astype(np.int8)), 16)
+        assert np.array_equal(host(pto.gemv(x, b)), exact)
+        assert np.array_equal(host(pto.gemv(x, b, bias=dev(bias.astype(np.int32)))), exact + bias)
+        assert np.array_equal(oracle.gemm_s8(xi.astype(np.int8), bi.astype(np.int8))[0], exact)
+        return
+    dt = torch.float16 if kind == "f16" else torch.bfloat16
+    x = dev(xi[0].astype(np.float32)).to(dt)
+    b = padded(dev(bi.astype(np.float32)).to(dt), 8)
+    assert np.array_equal(host(pto.gemv(x, b, torch.float32)).astype(np.int64), exact)
+    assert np.array_equal(host(pto.gemv(x, b, torch.float32, bias=dev(bias.astype(np.float32)))).astype(np.int64),
+                          exact + bias)
+    got16 = host(pto.gemv(x, b, torch.bfloat16))
+    assert np.array_equal(got16, oracle.store_cast(exact.astype(np.float32), oracle.BF16))
+    # the tile loop with a one-row left operand computes the same thing
+    assert np.array_equal(host(pto.gemm(padded(x.view(1, k), 8), b, torch.float32))[0].astype(np.int64), exact)
+
+
+def test_gemv_bf16_against_the_oracle():
+    n, k = 4096, 8192
+    a, b = gd.dense_inputs(1, n, k, "bf16", 41)
+    out = host(pto.gemv(dev16(a, torch.bfloat16).view(-1), dev16(b, torch.bfloat16), torch.float32))
+    ref = oracle.gemm_f32acc(a, b, oracle.BF16)[0]
+    assert max_rel_err(out, ref) <= DENSE_TOL
+    assert result_cmp(ref, out, DENSE_TOL)
+
+
+def test_gemv_rejects_bad_arguments():
+    b = torch.zeros((8, 64), dtype=torch.float16, device=DEV)
+    with pytest.raises(ValueError):
+        pto.gemv(torch.zeros(32, dtype=torch.float16, device=DEV), b)
+    with pytest.raises(ValueError):
+        pto.gemv(torch.zeros(64, dtype=torch.bfloat16, device=DEV), b)
+    with pytest.raises(pto.PtoB200Error):
+        pto.gemv(torch.zeros(72, dtype=torch.float16, device=DEV)[8:], torch.zeros((8, 72), dtype=torch.float16,
+                                                                                    device=DEV)[:, 4:68])
+
+
+# ------------------------------------------------------------------ MX quantiser
+
+def test_mx_quantiser_bit_exact():
+    g = golden("mx_quantize")                                   # zeros, 1e-30 and 1e30 blocks, a lone negative tiny value
+    d, s = pto.mx_quantize_e4m3(dev(g["src"]))
+    assert np.array_equal(host(d), g["data"]) and np.array_equal(host(s), g["scales"])
+
+    src = gd.normal((300, 4096), 43)
+    src[5] *= np.float32(1e-20)
+    src[6] *= np.float32(1e20)
+    src[7, ::3] = 0
+    src[8] = -np.abs(src[8]) * np.float32(1e-4)
+    src[9, :64] = np.float32(2.0) ** np.arange(-32, 32, dtype=np.float32)      # exact powers of two
+    src[10, :32] = np.float32(448.0) * np.float32(2.0) ** -np.arange(32, dtype=np.float32)
+    # ties between neighbouring e4m3 codes: the block maximum 1.9375 gives a scaling of 2^8, so 1 + (2 i + 1) / 16
+    # lands midway between two normal codes and j / 2 * 2^-17 midway between two subnormal codes (or zero)
+    sub = np.array([0.5, 1.5, 2.5, 3.5, 6.5, 7.5, 8.5, -0.5, -1.5, -2.5, -7.5, 0.25, -0.25, 0.75]) * 2.0 ** -17
+    src[11, :32] = np.concatenate([[1.9375], 1.0 + (2 * np.arange(7) + 1) / 16.0, sub, np.zeros(10)])
+    d, s = pto.mx_quantize_e4m3(dev(src))
+    rd, rs = oracle.mx_quantize_e4m3(src)
+    assert np.array_equal(host(s), rs)
+    assert np.array_equal(host(d), rd)
+
+    # a strided view (row pitch larger than K)
+    wide = torch.zeros((64, 512 + 64), dtype=torch.float32, device=DEV)
+    wide[:, :512] = dev(src[:64, :512])
+    d2, s2 = pto.mx_quantize_e4m3(wide[:, :512])
+    assert np.array_equal(host(d2), rd[:64, :512]) and np.array_equal(host(s2), rs[:64, :16])
+
+
+def test_quantise_then_multiply_matches_the_oracle_pipeline():
+    m, n, k = 128, 256, 512
+    xa, xb = gd.normal((m, k), 47, 0), gd.normal((n, k), 47, 1)
+    a, sfa = pto.mx_quantize_e4m3(dev(xa))
+    b, sfb = pto.mx_quantize_e4m3(dev(xb))
+    out = host(pto.gemm_mx(a, b, sfa, sfb, torch.float32))
+    ra, rsa = oracle.mx_quantize_e4m3(xa)
+    rb, rsb = oracle.mx_quantize_e4m3(xb)
+    assert np.array_equal(host(a), ra) and np.array_equal(host(sfb), rsb)
+    assert max_rel_err(out, oracle.gemm_mx(ra, rb, rsa, rsb)) <= MX_TOL

@@ -64,6 +64,26 @@ def test_argument_errors_come_before_any_launch(lib):
     assert mx(None, p, p, p, p, p, p, 1 << 20, 16, 16, 64, 64, 64, 16, 2, 2, E4M3, E5M2, F16 + 0) == _capi.EDTYPE
     assert mx(None, p, p, p, p, p, None, 0, 16, 16, 64, 64, 64, 16, 2, 2, E4M3, E4M3, BF16) == _capi.EWORKSPACE
     assert mx(None, p, p, p, p, p, p, 16, 16, 16, 64, 64, 64, 16, 2, 2, E4M3, E4M3, BF16) == _capi.EWORKSPACE   # too small
+    gb = lib.pto_b200_gemm_bias
+    assert gb(None, p, p, p, None, 16, 16, 16, 16, 16, 16, F16, F32, 0) == _capi.EINVAL        # bias missing
+    assert gb(None, p, p, p, p + 2, 16, 16, 16, 16, 16, 16, F16, F32, 0) == _capi.EALIGN       # bias not 4-byte aligned
+    assert gb(None, p, p, p, p, 16, 16, 16, 16, 16, 16, S8, F32, 0) == _capi.EDTYPE
+    mxb = lib.pto_b200_gemm_mx_bias
+    assert mxb(None, p, p, p, p, p, None, p, 1 << 20, 16, 16, 64, 64, 64, 16, 2, 2, E4M3, E4M3, BF16) == _capi.EINVAL
+    gv = lib.pto_b200_gemv
+    assert gv(None, None, p, p, None, 16, 16, 16, F16, F32) == _capi.EINVAL
+    assert gv(None, p, p, p, None, 16, 16, 8, F16, F32) == _capi.EINVAL                         # ldb < k
+    assert gv(None, p, p, p, None, 16, 0, 16, F16, F32) == _capi.EINVAL                         # empty K
+    assert gv(None, p, p + 2, p, None, 16, 16, 16, F16, F32) == _capi.EALIGN                    # row not 16-byte aligned
+    assert gv(None, p, p, p, None, 16, 12, 12, BF16, F32) == _capi.EALIGN                       # 24-byte column pitch
+    assert gv(None, p, p, p, None, 16, 16, 16, S8, F32) == _capi.EDTYPE                         # int8 -> float
+    assert gv(None, p, p, p, None, 16, 16, 16, F32, F32) == _capi.EDTYPE
+    q = lib.pto_b200_mx_quantize_e4m3
+    assert q(None, p, p, None, 4, 64, 64, 64, 2) == _capi.EINVAL
+    assert q(None, p, p, p, 4, 48, 48, 48, 2) == _capi.EINVAL                                   # k % 32
+    assert q(None, p, p, p, 4, 64, 64, 64, 1) == _capi.EINVAL                                   # ld_scales < k / 32
+    assert q(None, p, p, p + 4, 4, 64, 64, 64, 2) == _capi.EALIGN                               # src not 16-byte aligned
+    assert q(None, p, p, p, 4, 64, 66, 64, 2) == _capi.EALIGN                                   # ld_src % 4
     assert lib.pto_b200_cast_f32_to_bf16(None, None, p, 4) == _capi.EINVAL
     assert lib.pto_b200_cast_f32_to_bf16(None, p, p, 0) == _capi.OK
     assert lib.pto_b200_launch_count() == before
