@@ -260,6 +260,53 @@ def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=4, 
     raise ValueError(kind)
 
 
+# The shapes of the reference's own published table (fp16 in, fp32 out, m = n = k), timed briefly under "all_configs".
+REF_TABLE_SHAPES = (1536, 3072, 6144, 7680)
+
+
+def aux_configs(dev, peaks):
+    """Brief timings of the neighbours of the GEMM path: the reference table's fp16 -> fp32 cubes (tensor-bound), the
+    one-row TGEMV and the MX quantiser (both HBM-bound: GB/s of algorithmic bytes against the measured copy peak)."""
+    import torch
+
+    import pto_isa_mirror_b200 as pto
+
+    out = {}
+    gen = torch.Generator(device=dev).manual_seed(11)
+    peak_tf = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    peak_gbs = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+    for size in REF_TABLE_SHAPES:
+        step, flops, _, _ = make_step(f"f16_f32_{size}", dict(kind="dense", m=size, n=size, k=size, dtype="f16", out="f32"),
+                                      dev, seed=3)
+        ms = time_steps(step, 20, 3, dev, 1) / 20
+        out[f"f16_f32_{size}cubed"] = {"tflops": flops / (ms * 1e-3) / 1e12, "ms": ms,
+                                       "frac_of_peak": flops / (ms * 1e-3) / 1e12 / peak_tf, "peak": peak_tf}
+        del step
+        torch.cuda.empty_cache()
+    # TGEMV: bf16 8192 x 8192 B per launch, 4 rotating matrices (512 MiB > L2)
+    n = k = 8192
+    mats = [_randn_scaled((n, k), k, torch.bfloat16, gen, dev) for _ in range(4)]
+    x = _randn_scaled((k,), k, torch.bfloat16, gen, dev)
+    y = torch.empty((n,), dtype=torch.float32, device=dev)
+    ms = time_steps(lambda i: pto.gemv(x, mats[i % 4], out=y), 40, 5, dev, 1) / 40
+    gbytes = (n * k * 2 + k * 2 + n * 4) / 1e9
+    out["gemv_bf16_8192x8192"] = {"gbs": gbytes / (ms * 1e-3), "ms": ms, "bytes": int(gbytes * 1e9),
+                                  "frac_of_hbm_peak": gbytes / (ms * 1e-3) / peak_gbs, "peak_gbs": peak_gbs}
+    del mats
+    torch.cuda.empty_cache()
+    # MX quantiser: fp32 8192 x 8192 per launch (256 MiB read + 66 MiB written), 2 rotating sources
+    rows = kq = 8192
+    srcs = [torch.randn((rows, kq), generator=gen, device=dev) for _ in range(2)]
+    ms = time_steps(lambda i: pto.mx_quantize_e4m3(srcs[i % 2]), 20, 3, dev, 1) / 20
+    gbytes = rows * kq * (4 + 1 + 1 / 32) / 1e9
+    out["mx_quantize_8192x8192"] = {"gbs": gbytes / (ms * 1e-3), "ms": ms, "bytes": int(gbytes * 1e9),
+                                    "frac_of_hbm_peak": gbytes / (ms * 1e-3) / peak_gbs, "peak_gbs": peak_gbs,
+                                    "note": "includes the two output allocations of the wrapper"}
+    del srcs
+    torch.cuda.empty_cache()
+    return out
+
+
 # --------------------------------------------------------------------------------------- timing
 
 def time_steps(step, steps, warmup, dev, world):
@@ -525,6 +572,10 @@ def main():
                 torch.cuda.empty_cache()
             except Exception as e:  # noqa: BLE001
                 others[oname] = {"error": repr(e)}
+        try:
+            others.update(aux_configs(dev, peaks))
+        except Exception as e:  # noqa: BLE001
+            others["aux"] = {"error": repr(e)}
         line["all_configs"] = others
         try:
             v, info = cpu_reference_sample("dense", spec["k"] if spec["k"] <= 8192 else 8192, args.cpu_budget)

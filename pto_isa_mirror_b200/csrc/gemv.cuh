@@ -55,8 +55,10 @@ __device__ __forceinline__ float scalar_to_float(const void* base, long long idx
 
 // a: [k] elements, 16-byte aligned. b: [n][ldb] elements (column-major K x N), rows 16-byte aligned.
 // bias: n values of the accumulator type or null. out: [n] of the OUT type.
+// At most 32 registers per thread: eight 256-thread blocks per SM, so that 8192 columns (1024 blocks) are all
+// resident at once on 148 SMs instead of running as one full wave and a 38 % wave.
 template <int IN, int OUT>
-__global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const void* __restrict__ a, const void* __restrict__ b,
+__global__ void __launch_bounds__(kGemvThreads, 8) gemv_kernel(const void* __restrict__ a, const void* __restrict__ b,
                                                              const void* __restrict__ bias, void* __restrict__ out,
                                                              int n, int k, long long ldb)
 {
@@ -72,7 +74,7 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const void* __restri
         const uint4* brow = reinterpret_cast<const uint4*>(brow_bytes);
         if constexpr (IN == GEMV_S8) {
             int acc0 = 0, acc1 = 0;
-#pragma unroll 4
+#pragma unroll 2
             for (int i = lane; i < kv; i += 32) {
                 const uint4 bv = ld_stream_u4(brow + i);
                 const uint4 xv = __ldg(av + i);
@@ -99,7 +101,7 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const void* __restri
             }
         } else {
             float acc0 = 0.0f, acc1 = 0.0f;
-#pragma unroll 4
+#pragma unroll 2
             for (int i = lane; i < kv; i += 32) {
                 const uint4 bv = ld_stream_u4(brow + i);
                 const uint4 xv = __ldg(av + i);

@@ -38,6 +38,8 @@ __device__ __forceinline__ uint32_t drop_negative_zero(uint32_t four_codes)
     return magnitude | (four_codes & nonzero);
 }
 
+constexpr int kQuantItems = 4; // 16-byte loads in flight per thread
+
 // src: [rows][ld_src] floats (16-byte aligned rows); data: [rows][ld_data] bytes (4-byte aligned rows);
 // scales: [rows][ld_scales] bytes. k % 32 == 0.
 __global__ void __launch_bounds__(kQuantThreads) mx_quantize_e4m3_kernel(const float* __restrict__ src,
@@ -49,26 +51,43 @@ __global__ void __launch_bounds__(kQuantThreads) mx_quantize_e4m3_kernel(const f
     const int k4 = k / 4;
     const long long total = static_cast<long long>(rows) * k4; // 16-byte items; a multiple of 8 per row
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-    // every lane of a warp runs the same number of iterations (total and stride are multiples of 8, and the
-    // shuffles below stay inside aligned groups of 8 lanes whose items are all in range or all out of range)
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total; i += stride) {
-        const long long row = i / k4;
-        const int c4 = static_cast<int>(i - row * k4);
-        const float4 v = __ldcs(reinterpret_cast<const float4*>(src + row * ld_src) + c4);
-        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-        const unsigned group_mask = 0xFFu << (threadIdx.x & 24u);
-        amax = fmaxf(amax, __shfl_xor_sync(group_mask, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(group_mask, amax, 2));
-        amax = fmaxf(amax, __shfl_xor_sync(group_mask, amax, 4));
-        const uint32_t exponent = (__float_as_uint(amax) & 0x7F800000u) >> 23;
-        const uint32_t e8m0 = exponent <= 8u ? 0u : exponent - 8u;
-        const float scaling = __uint_as_float((254u - e8m0) << 23); // e8m0 <= 246 for finite input: never zero
-        const uint32_t lo = cvt_e4m3x2(__fmul_rn(v.x, scaling), __fmul_rn(v.y, scaling));
-        const uint32_t hi = cvt_e4m3x2(__fmul_rn(v.z, scaling), __fmul_rn(v.w, scaling));
-        const uint32_t packed = drop_negative_zero(lo | (hi << 16));
-        *reinterpret_cast<uint32_t*>(data + row * ld_data + static_cast<long long>(c4) * 4) = packed;
-        if ((c4 & 7) == 0) {
-            scales[row * ld_scales + (c4 >> 3)] = static_cast<uint8_t>(e8m0);
+    const unsigned group_mask = 0xFFu << (threadIdx.x & 24u);
+    // total and stride are multiples of 8, so the eight lanes of a group hold items of one 32-value block that are
+    // all in range or all out of range: the group's shuffles below are executed by all eight lanes or by none
+    for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < total;
+         i0 += stride * kQuantItems) {
+        float4 v[kQuantItems];
+        long long row[kQuantItems];
+        int c4[kQuantItems];
+#pragma unroll
+        for (int u = 0; u < kQuantItems; ++u) {
+            const long long i = i0 + u * stride;
+            row[u] = -1;
+            if (i < total) {
+                row[u] = i / k4;
+                c4[u] = static_cast<int>(i - row[u] * k4);
+                v[u] = __ldcs(reinterpret_cast<const float4*>(src + row[u] * ld_src) + c4[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kQuantItems; ++u) {
+            if (row[u] < 0) {
+                continue;
+            }
+            float amax = fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w)));
+            amax = fmaxf(amax, __shfl_xor_sync(group_mask, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(group_mask, amax, 2));
+            amax = fmaxf(amax, __shfl_xor_sync(group_mask, amax, 4));
+            const uint32_t exponent = (__float_as_uint(amax) & 0x7F800000u) >> 23;
+            const uint32_t e8m0 = exponent <= 8u ? 0u : exponent - 8u;
+            const float scaling = __uint_as_float((254u - e8m0) << 23); // e8m0 <= 246 for finite input: never zero
+            const uint32_t lo = cvt_e4m3x2(__fmul_rn(v[u].x, scaling), __fmul_rn(v[u].y, scaling));
+            const uint32_t hi = cvt_e4m3x2(__fmul_rn(v[u].z, scaling), __fmul_rn(v[u].w, scaling));
+            const uint32_t packed = drop_negative_zero(lo | (hi << 16));
+            *reinterpret_cast<uint32_t*>(data + row[u] * ld_data + static_cast<long long>(c4[u]) * 4) = packed;
+            if ((c4[u] & 7) == 0) {
+                scales[row[u] * ld_scales + (c4[u] >> 3)] = static_cast<uint8_t>(e8m0);
+            }
         }
     }
 }

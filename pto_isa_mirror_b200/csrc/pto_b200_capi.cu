@@ -772,9 +772,16 @@ extern "C" int pto_b200_mx_quantize_e4m3(void* stream, uint8_t* data, uint8_t* s
     if (int rc = device_info(&dev)) {
         return rc;
     }
+    // one resident wave of blocks walking the matrix with a grid stride: no partly filled second wave
+    int blocks_per_sm = 0;
+    if (int rc = note_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, mx_quantize_e4m3_kernel,
+                                                                         kQuantThreads, 0),
+                           "mx_quantize occupancy")) {
+        return rc;
+    }
     const long long items = static_cast<long long>(rows) * (k / 4);
     const long long want = (items + kQuantThreads - 1) / kQuantThreads;
-    const long long cap = static_cast<long long>(dev->sm_count) * 8;
+    const long long cap = static_cast<long long>(dev->sm_count) * (blocks_per_sm > 0 ? blocks_per_sm : 1);
     const int grid = static_cast<int>(want < cap ? want : cap);
     mx_quantize_e4m3_kernel<<<grid, kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const float*>(src), data, scales, rows, k, ld_src, ld_data, ld_scales);
