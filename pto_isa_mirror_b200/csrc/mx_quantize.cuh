@@ -52,21 +52,32 @@ __global__ void __launch_bounds__(kQuantThreads) mx_quantize_e4m3_kernel(const f
     const long long total = static_cast<long long>(rows) * k4; // 16-byte items; a multiple of 8 per row
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     const unsigned group_mask = 0xFFu << (threadIdx.x & 24u);
+    // (row, column) of the running item index, advanced by one stride per item: one division per thread, none per item
+    const long long row_step = stride / k4;
+    const int col_step = static_cast<int>(stride - row_step * k4);
+    long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    long long cur_row = i / k4;
+    int cur_c4 = static_cast<int>(i - cur_row * k4);
     // total and stride are multiples of 8, so the eight lanes of a group hold items of one 32-value block that are
     // all in range or all out of range: the group's shuffles below are executed by all eight lanes or by none
-    for (long long i0 = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i0 < total;
-         i0 += stride * kQuantItems) {
+    while (i < total) {
         float4 v[kQuantItems];
         long long row[kQuantItems];
         int c4[kQuantItems];
 #pragma unroll
         for (int u = 0; u < kQuantItems; ++u) {
-            const long long i = i0 + u * stride;
             row[u] = -1;
             if (i < total) {
-                row[u] = i / k4;
-                c4[u] = static_cast<int>(i - row[u] * k4);
-                v[u] = __ldcs(reinterpret_cast<const float4*>(src + row[u] * ld_src) + c4[u]);
+                row[u] = cur_row;
+                c4[u] = cur_c4;
+                v[u] = __ldcs(reinterpret_cast<const float4*>(src + cur_row * ld_src) + cur_c4);
+            }
+            i += stride;
+            cur_row += row_step;
+            cur_c4 += col_step;
+            if (cur_c4 >= k4) {
+                cur_c4 -= k4;
+                cur_row += 1;
             }
         }
 #pragma unroll
