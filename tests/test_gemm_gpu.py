@@ -334,3 +334,32 @@ def test_launch_is_asynchronous_on_the_given_stream():
     out = pto.gemm(ta, tb, torch.float32, stream=s)
     s.synchronize()
     assert max_rel_err(out.cpu().numpy(), oracle.gemm_f32acc(a, b, oracle.BF16)) <= DENSE_TOL
+
+
+def test_host_pipeline_matches_one_product_at_a_time():
+    """HostGemmPipeline (copies of neighbouring products overlapped with the GEMM) returns the bits of HostGemm.run."""
+    from pto_isa_mirror_b200.host_api import HostGemm, HostGemmPipeline
+
+    m, n, k = 256, 512, 320
+    pairs = []
+    for i in range(7):
+        a, b = gd.dense_inputs(m, n, k, "bf16", 50 + i)
+        pairs.append((torch.from_numpy(a.view(np.int16)).view(torch.bfloat16).pin_memory(),
+                      torch.from_numpy(b.view(np.int16)).view(torch.bfloat16).pin_memory()))
+    one = HostGemm(m, n, k, torch.bfloat16, torch.float32)
+    want = [one.run(a, b).clone() for a, b in pairs]
+    pipe = HostGemmPipeline(m, n, k, torch.bfloat16, torch.float32, depth=3)
+    got = {}
+    for i, (a, b) in enumerate(pairs):
+        t = pipe.submit(a, b)
+        assert t == i
+        if t >= 2:
+            got[t - 2] = pipe.result(t - 2).clone()
+    for t in range(len(pairs) - 2, len(pairs)):
+        got[t] = pipe.result(t).clone()
+    for i in range(len(pairs)):
+        assert torch.equal(got[i], want[i]), i
+    ref = oracle.gemm_f32acc(gd.dense_inputs(m, n, k, "bf16", 50)[0], gd.dense_inputs(m, n, k, "bf16", 50)[1], oracle.BF16)
+    assert max_rel_err(got[0].numpy(), ref) <= DENSE_TOL
+    with pytest.raises(ValueError):
+        pipe.result(0)                                              # overwritten four submissions ago
