@@ -357,6 +357,7 @@ PTO_INST RecordEvent TGEMV(TileRes& cMatrix, TileLeft_& aMatrix, TileRight_& bMa
     return {};
 }
 
+// The accumulating forms are declared after TMATMUL_ACC below.
 template <AccPhase Phase = AccPhase::Unspecified, typename TileRes, typename TileLeft_, typename TileRight_,
           typename TileBias_>
 PTO_INST RecordEvent TGEMV_BIAS(TileRes& cMatrix, TileLeft_& aMatrix, TileRight_& bMatrix, TileBias_& biasData)
@@ -379,6 +380,13 @@ PTO_INST RecordEvent TMATMUL_ACC(TileRes& cOutMatrix, TileRes& cInMatrix, TileLe
                                                 b200::dtype_of<typename TileLeft_::DType>::value,
                                                 b200::dtype_of<typename TileRight_::DType>::value});
     return {};
+}
+
+// TGEMV_ACC (cpu/TMatmul.hpp:239-244): the next K slice of a one-row chain.
+template <AccPhase Phase = AccPhase::Unspecified, typename TileRes, typename TileLeft_, typename TileRight_>
+PTO_INST RecordEvent TGEMV_ACC(TileRes& cOutMatrix, TileRes& cInMatrix, TileLeft_& aMatrix, TileRight_& bMatrix)
+{
+    return TMATMUL_ACC<Phase>(cOutMatrix, cInMatrix, aMatrix, bMatrix);
 }
 
 template <AccPhase Phase = AccPhase::Unspecified, typename TileRes, typename TileLeft_, typename TileLeftScale_,

@@ -39,6 +39,25 @@ def test_illegal_dtype_combination_is_a_compile_error(tmp_path):
     assert proc.returncode != 0 and "Not supported data type" in proc.stderr
 
 
+def test_one_row_and_bias_forms_compile(tmp_path):
+    """TGEMV / TGEMV_ACC / TGEMV_BIAS / TMATMUL_BIAS exist with the reference's argument order, and a bias tile of the
+    wrong type is a compile error (CheckBiasValid, include/pto/cpu/TMatmul.hpp:159-167)."""
+    good = tmp_path / "good.cpp"
+    good.write_text('#include "pto/pto-inst.hpp"\nusing namespace pto;\nint main() {\n'
+                    "  TileLeft<half, 1, 64> a; TileRight<half, 64, 256> b; TileAcc<float, 1, 256> c;\n"
+                    "  Tile<TileType::Bias, float, 1, 256, BLayout::RowMajor, 1, 256> bias;\n"
+                    "  if (false) { TGEMV(c, a, b); TGEMV_ACC(c, c, a, b); TGEMV_BIAS(c, a, b, bias); "
+                    "TMATMUL_BIAS(c, a, b, bias); }\n  return 0;\n}\n")
+    inc = ["-I", os.path.join(ROOT, "include"), "-I", os.path.join(CUDA, "include")]
+    proc = subprocess.run(["g++", "-std=c++17", "-Wall", "-Werror", "-fsyntax-only", *inc, str(good)],
+                          capture_output=True, text=True)
+    assert proc.returncode == 0, proc.stderr
+    bad = tmp_path / "bad_bias.cpp"
+    bad.write_text(good.read_text().replace("Tile<TileType::Bias, float,", "Tile<TileType::Bias, int32_t,"))
+    proc = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", *inc, str(bad)], capture_output=True, text=True)
+    assert proc.returncode != 0 and "No supported bias data type" in proc.stderr
+
+
 @pytest.mark.gpu
 def test_reference_tile_programs_run_exactly_on_gpu():
     exe = compile_example()
