@@ -385,9 +385,9 @@ def cpu_tile_runner(kind: str, k: int, single_thread=False):
     return run, {"kind": "reference" if use_ref else "port", "cores": cores, "what": what}
 
 
-def cpu_reference_sample(kind: str, k: int, budget_s: float):
+def cpu_reference_sample(kind: str, k: int, budget_s: float, single_thread: bool = False):
     """Times output tiles of the workload on the host cores until `budget_s` has elapsed."""
-    run, info = cpu_tile_runner(kind, k)
+    run, info = cpu_tile_runner(kind, k, single_thread)
     flops = 2.0 * 128 * 256 * k
     run()
     n, t0 = 0, time.perf_counter()
@@ -628,6 +628,10 @@ def main():
         try:
             v, info = cpu_reference_sample("dense", spec["k"] if spec["k"] <= 8192 else 8192, args.cpu_budget)
             line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", **info}
+            # the simulator built with PTO_CPU_MAX_THREADS=1 (the reference's own single-thread knob), briefly
+            v1, info1 = cpu_reference_sample("dense", spec["k"] if spec["k"] <= 8192 else 8192,
+                                             max(1.0, args.cpu_budget / 5), single_thread=True)
+            line["cpu_baseline"]["single_thread"] = {"value": v1, "cores": info1["cores"], "sample": info1["sample"]}
         except Exception as e:  # noqa: BLE001
             line["cpu_baseline"] = {"value": None, "unit": "TFLOP/s", "cores": 0, "kind": "port", "sample": repr(e)}
     elif world > 1:
