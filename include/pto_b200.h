@@ -243,6 +243,47 @@ int pto_b200_ksplit_reduce(void* stream, void* const* partial_ptrs, void* const*
 int pto_b200_ksplit_wait(void* stream, const int* done_local, int world, int slot0, int slots, int epoch);
 
 /*
+ * One rank's whole step of the K-split GEMM + allreduce in ONE kernel launch: this rank's GEMM over its K slice,
+ * row panel by row panel into its fp32 partial, and - by extra warps of the same kernel - the exchange of every
+ * finished panel over peer memory: wait for all ranks' partials of the panel, sum this rank's row shard of it (NVSwitch
+ * multimem.ld_reduce when multicast addresses are given, else plain peer loads in rank order), cast to bf16, store into
+ * every rank's output, and finally wait until every rank has delivered every panel into this rank's output.
+ * Replaces: launchGemmCompute + launchGemmCommAll running on two streams (kernels/manual/a2a3/gemm_ar/
+ * gemm_compute_kernel.cpp:150-259 tile loop that fills the ready queue, comm_kernel.cpp:165-210 reduce-scatter,
+ * :377-400 all-gather, :528-590 queue consumer, :725 launcher; main.cpp:761-800 the two-stream step).
+ *   src0 / src1   : this rank's K slice of A [m, k_local] (lda) and of column-major B [n, k_local] (ldb), F16 or BF16
+ *   partial_ptrs  : every rank's fp32 partial [m, ld_partial] of THIS step (double-buffer across steps: a slow peer may
+ *                   still be reading the previous step's partial); entry `rank` is written by this launch
+ *   out_ptrs      : every rank's bf16 output [m, ld_out]
+ *   ready_arrays / done_arrays : every rank's flag arrays (PTO_B200_KSPLIT_FLAG_STRIDE ints per slot, zero before the
+ *                   first step); slots [slot0, slot0 + panels) are used, with panels = ceil(m / panel_rows)
+ *   panel_counters_local / exchange_counters_local : this rank's scratch, one int per slot, zero before the first step
+ *   epoch         : 1, 2, 3, ... one per step, the same on every rank
+ *   panel_rows    : rows of a panel, a multiple of 256
+ *   multicast_partial / multicast_out : NVSwitch multicast addresses of the same partial / output buffers, or null
+ *   launch_block_count : cap on thread blocks, 0 = every SM
+ * All ranks must launch the same step at about the same time: a rank waits at most the wait limit
+ * (pto_b200_set_wait_limit) for the others, then records a code in the status word and returns. The launch must be
+ * able to hold all its thread blocks on the GPU at once (nothing else resident that takes whole SMs), because blocks
+ * wait for panels that other blocks of the same launch complete. No TMA load and no multicast load reads peer memory:
+ * peers are reached by the exchange warps' own loads and stores only. Every rank receives identical bits.
+ */
+int pto_b200_ksplit_gemm_allreduce(void* stream, const uint8_t* src0, const uint8_t* src1, int m, int n, int k_local,
+                                   long long lda, long long ldb, int in_dtype, void* const* partial_ptrs,
+                                   void* const* out_ptrs, void* const* ready_arrays, void* const* done_arrays,
+                                   int* panel_counters_local, int* exchange_counters_local, int world, int rank,
+                                   int slot0, int epoch, int panel_rows, long long ld_partial, long long ld_out,
+                                   const void* multicast_partial, void* multicast_out, int launch_block_count);
+
+/*
+ * Cycles a kernel of this library waits on one barrier or flag before it gives up (records a code in the status
+ * word, see pto_b200_device_status, and returns without trapping). Default 4e9 (about two seconds); cycles <= 0
+ * restores the default. Applies to launches made after the call; returns the previous value. The reference has no
+ * counterpart (its TWAIT spins without a limit, kernels/manual/a2a3/gemm_ar/comm_kernel.cpp:528-590).
+ */
+long long pto_b200_set_wait_limit(long long cycles);
+
+/*
  * Fixed-shape launchers with the reference's exact signatures.
  * call_kernel: demos/torch_jit/gemm/gemm_kernel.cpp:263-266 (fp16 6144^3, B column-major, fp32 out; blockDim ignored).
  */

@@ -62,6 +62,7 @@ def _lib() -> ctypes.CDLL:
         lib.pto_oracle_store_cast.argtypes = [_p, _p, _ll, _i]
         lib.pto_oracle_dequant_bf16.argtypes = [_p, _p, _p, _p, _i, _i, _ll, _ll, _i]
         lib.pto_oracle_mx_quantize_e4m3.argtypes = [_p, _p, _p, _i, _i, _ll]
+        lib.pto_oracle_quant_store.argtypes = [_p, _i, _p, _i, _i, _i, _p, _i, _i, _ll, _ll]
         lib.pto_oracle_float_to_bf16.argtypes = [ctypes.c_float]
         lib.pto_oracle_float_to_bf16.restype = ctypes.c_uint16
         lib.pto_oracle_float_to_half.argtypes = [ctypes.c_float]
@@ -167,6 +168,21 @@ def dequant_bf16(acc: np.ndarray, s_row: np.ndarray, s_col: np.ndarray, truncate
     return out
 
 
+def quant_store(acc: np.ndarray, words, vector: bool, relu: bool = False, out_f16: bool = False) -> np.ndarray:
+    """TSTORE with a pre-quant scale: int32 or float32 accumulators [m, n] -> bf16 / f16 bit patterns. ``words``: one
+    64-bit scale word (scalar form) or n of them (vector form, one per column)."""
+    acc = np.ascontiguousarray(acc)
+    if acc.dtype not in (np.dtype(np.int32), np.dtype(np.float32)):
+        raise TypeError("accumulators must be int32 or float32")
+    words = np.ascontiguousarray(np.atleast_1d(np.asarray(words, dtype=np.uint64)))
+    m, n = acc.shape
+    assert words.shape == ((n,) if vector else (1,))
+    out = np.empty((m, n), dtype=np.uint16)
+    _lib().pto_oracle_quant_store(_ptr(acc), int(acc.dtype == np.int32), _ptr(words), int(vector), int(relu),
+                                  int(out_f16), _ptr(out), m, n, n, n)
+    return out
+
+
 def mx_quantize_e4m3(src: np.ndarray):
     """OCP MX quantisation of fp32 [rows, k] along k in blocks of 32 -> (e4m3 bytes [rows, k], e8m0 bytes [rows, k/32])."""
     src = _c(src, np.float32)
@@ -212,6 +228,9 @@ class Ref:
         lib.ref_cast_bf16.restype = ctypes.c_uint16
         lib.ref_cast_f16.argtypes = [ctypes.c_float]
         lib.ref_cast_f16.restype = ctypes.c_uint16
+        if hasattr(lib, "ref_quant_store"):
+            lib.ref_quant_store.argtypes = [_i, _i, _i, _i, ctypes.c_int32, ctypes.c_float, ctypes.c_uint64]
+            lib.ref_quant_store.restype = ctypes.c_uint16
         lib.ref_mx_quantize_e4m3.argtypes = [_p, _p, _p, _i, _i]
         lib.ref_fp8_to_double.argtypes = [ctypes.c_uint8, _i]
         lib.ref_fp8_to_double.restype = ctypes.c_double
@@ -286,6 +305,22 @@ class Ref:
         out = np.empty((self.TILE_M, self.TILE_N), dtype=np.float32)
         if self.lib.ref_tile_mx_bias(_ptr(out), _ptr(a), _ptr(b_dn), _ptr(sfa), _ptr(sfb), _ptr(bias), k) != 0:
             raise ValueError("K must be a positive multiple of 128")
+        return out
+
+    def quant_store(self, acc, words, vector, relu=False, out_f16=False):
+        """TSTORE with a pre-quant scale through the simulator's quantize_element, element by element."""
+        acc = np.ascontiguousarray(acc)
+        is_int = acc.dtype == np.int32
+        words = np.atleast_1d(np.asarray(words, dtype=np.uint64))
+        m, n = acc.shape
+        out = np.empty((m, n), dtype=np.uint16)
+        fn = self.lib.ref_quant_store
+        for i in range(m):
+            for j in range(n):
+                w = int(words[j if vector else 0])
+                v = acc[i, j]
+                out[i, j] = fn(int(is_int), int(out_f16), int(vector), int(relu), int(v) if is_int else 0,
+                               0.0 if is_int else float(v), w)
         return out
 
     def mx_quantize_e4m3(self, src):

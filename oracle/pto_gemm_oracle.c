@@ -518,6 +518,38 @@ void pto_oracle_dequant_bf16(const int32_t* acc, const float* s_row, const float
     }
 }
 
+/* TSTORE with a pre-quant scale word (cpu/TStore.hpp:154-181 -> quantize_element, cpu/common.hpp:139-185), modes as
+   the overloads select them (common.hpp:58-108): int32 / float accumulators to bf16 / half, scalar form (fp32 scale in
+   bits [31:0] of the word, one word for the whole tile) or vector form (one word per column, scale = the 19-bit float
+   in bits [31:13]), optional ReLU after the scaling. Saturation control of the task cookie is off (its default). */
+void pto_oracle_quant_store(const void* acc, int acc_is_int, const uint64_t* words, int vector, int relu, int out_f16,
+                            uint16_t* out, int m, int n, long long ld_acc, long long ld_out)
+{
+    for (int i = 0; i < m; ++i) {
+        for (int j = 0; j < n; ++j) {
+            const uint64_t w = words[vector ? j : 0];
+            const float lo = bits_to_float((uint32_t)(w & 0xFFFFFFFFu));
+            const float scale = vector ? scale_from_19_bits(lo) : lo;
+            const float src = acc_is_int ? (float)((const int32_t*)acc)[(size_t)i * ld_acc + j]
+                                         : ((const float*)acc)[(size_t)i * ld_acc + j];
+            volatile float t = src * scale;
+            float r = t;
+            if (out_f16) {
+                /* DEQF16 / VDEQF16 clamp always; QF322F16_PRE / VQF322F16_PRE clamp finite values (common.hpp:157-164) */
+                if (acc_is_int || isfinite(r)) {
+                    r = fminf(fmaxf(r, -65504.0f), 65504.0f);
+                }
+            } else if (isfinite(r)) {
+                r = fminf(fmaxf(r, -3.402823466e38f), 3.402823466e38f);
+            }
+            if (relu) {
+                r = (r > 0.0f) ? r : 0.0f;
+            }
+            out[(size_t)i * ld_out + j] = out_f16 ? pto_oracle_float_to_half(r) : pto_oracle_float_to_bf16(r);
+        }
+    }
+}
+
 /* ------------------------------------------------------------------ MX quantiser (data preparation) */
 
 /* Nearest e4m3fn code, ties to the even code; magnitudes that round to zero give +0 (code 0x00), as the

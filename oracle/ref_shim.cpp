@@ -267,6 +267,56 @@ float ref_dequant_col(int32_t acc, float s_col)
     return quantize_element<float, int32_t, QuantMode_t::VQS322BF16_PRE, false>(acc, static_cast<uint64_t>(bits));
 }
 
+// TSTORE with a pre-quant scale word, one accumulator value through the simulator's own ConvertStoreValue /
+// quantize_element (include/pto/cpu/TStore.hpp:154-181, include/pto/cpu/common.hpp:139-198), with the mode the
+// TSTORE overloads pick (GetScalarPreQuantMode / GetVectorPreQuantMode, common.hpp:58-108):
+//   acc_is_int  1: int32 accumulator (acc_i), 0: float accumulator (acc_f)
+//   out_f16     1: half destination, 0: bfloat16_t destination
+//   vector      1: TSTORE(dst, acc, fpTile) / TSTORE_FP, scale in bits [31:13]; 0: TSTORE(dst, acc, preQuantScalar)
+//   relu        ReluPreMode::NormalRelu
+// Returns the 16 destination bits.
+uint16_t ref_quant_store(int acc_is_int, int out_f16, int vector, int relu, int32_t acc_i, float acc_f, uint64_t word)
+{
+    uint16_t bits = 0;
+    auto run = [&](auto dst_tag, auto src_tag, auto vec_tag, auto relu_tag) {
+        using D = decltype(dst_tag);
+        using S = decltype(src_tag);
+        constexpr bool kVec = decltype(vec_tag)::value;
+        constexpr bool kRelu = decltype(relu_tag)::value;
+        constexpr QuantMode_t mode = kVec ? GetVectorPreQuantMode<S, D>() : GetScalarPreQuantMode<S, D>();
+        const S v = std::is_same_v<S, int32_t> ? static_cast<S>(acc_i) : static_cast<S>(acc_f);
+        const D d = ConvertStoreValue<D, S, mode, kRelu>(v, word);
+        std::memcpy(&bits, &d, 2);
+    };
+    auto with_relu = [&](auto d, auto s, auto v) {
+        if (relu) {
+            run(d, s, v, std::true_type{});
+        } else {
+            run(d, s, v, std::false_type{});
+        }
+    };
+    auto with_vec = [&](auto d, auto s) {
+        if (vector) {
+            with_relu(d, s, std::true_type{});
+        } else {
+            with_relu(d, s, std::false_type{});
+        }
+    };
+    auto with_src = [&](auto d) {
+        if (acc_is_int) {
+            with_vec(d, int32_t{});
+        } else {
+            with_vec(d, float{});
+        }
+    };
+    if (out_f16) {
+        with_src(half{});
+    } else {
+        with_src(bfloat16_t{});
+    }
+    return bits;
+}
+
 // TSTORE's no-quant cast, static_cast<Dst>(float) (include/pto/cpu/common.hpp:187-198).
 uint16_t ref_cast_bf16(float v)
 {

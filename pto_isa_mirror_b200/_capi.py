@@ -65,6 +65,13 @@ SYMBOLS = {
          ctypes.c_void_p, ctypes.c_void_p],
     ),
     "pto_b200_ksplit_wait": (_i, [ctypes.c_void_p, ctypes.c_void_p, _i, _i, _i, _i]),
+    "pto_b200_ksplit_gemm_allreduce": (
+        _i,
+        [ctypes.c_void_p, _u8p, _u8p, _i, _i, _i, _ll, _ll, _i, ctypes.POINTER(ctypes.c_void_p),
+         ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p),
+         ctypes.c_void_p, ctypes.c_void_p, _i, _i, _i, _i, _i, _ll, _ll, ctypes.c_void_p, ctypes.c_void_p, _i],
+    ),
+    "pto_b200_set_wait_limit": (_ll, [_ll]),
     "call_kernel": (None, [ctypes.c_uint32, ctypes.c_void_p, _u8p, _u8p, _u8p]),
     "pto_b200_device_status": (_i, [ctypes.POINTER(_i)]),
     "pto_b200_error_string": (ctypes.c_char_p, [_i]),

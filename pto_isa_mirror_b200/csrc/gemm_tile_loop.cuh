@@ -53,6 +53,9 @@ struct GemmParams {
     int tail_tiles;      // leftover tiles that are split (0 = none)
     uint32_t* ws_partial; // [tail_tiles][256][256] 32-bit accumulators
     int* ws_flags;        // [2 * tail_tiles]: arrivals of the first halves' store warps, departures of the readers
+    long long wait_limit; // cycles one bounded wait may take before the kernel gives up (kWaitLimitCycles by default)
+    int tma_store;        // CTA-pair kernels: C is 16-byte aligned with a 16-byte row pitch, so finished tiles leave
+                          // through shared memory and TMA stores; 0 = per-thread global stores
 };
 
 constexpr int kBlockM = 128;
@@ -60,7 +63,7 @@ constexpr int kBlockKBytes = 128; // one 128-byte swizzle row per matrix row
 constexpr int kUmmaKBytes = 32;
 constexpr int kNumThreads = 192;
 constexpr int kTmemCols = 512;
-constexpr long long kWaitLimitCycles = 4000000000ll; // about two seconds
+constexpr long long kWaitLimitCycles = 4000000000ll; // default limit of one wait: about two seconds
 
 enum StatusCode : int {
     ST_OK = 0,
@@ -89,7 +92,7 @@ struct SmemLayout {
 
 // Bounded mbarrier wait. Returns false after the limit or once another role raised the abort flag.
 __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                             int* status, int code)
+                                             int* status, int code, long long limit)
 {
     if (ptx::mbar_try_wait(bar, parity)) {
         return true;
@@ -101,7 +104,7 @@ __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, vol
             if (*abort_flag != 0) {
                 return false;
             }
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > limit) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code);
                 return false;
@@ -124,26 +127,44 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& mi,
     ni = r / gm;
 }
 
+// Words one 32-column chunk of an accumulator row becomes on its way out: 32 for 32-bit outputs, 16 (two values each)
+// for 16-bit outputs.
 template <int EPI>
-__device__ __forceinline__ void store_chunk_nobias(const uint32_t (&v)[32], const GemmParams& p, int row, int col0,
-                                                   bool vec_ok, float s_row)
+struct OutWords {
+    static constexpr int kCount = (EPI == EPI_F32 || EPI == EPI_S32) ? 32 : 16;
+};
+
+// One 32-column chunk of one accumulator row -> output words: optional bias, then cast / dequantise. The bias is
+// added to the finished accumulator in the accumulator's own type, once per output element (TMATMUL_BIAS adds it
+// after the first matmul of the K loop, include/pto/cpu/TMatmul.hpp:219-230: exact for int32, one fp32 rounding apart
+// otherwise). Columns at or past N read neither bias nor scale; their words are never stored.
+template <int EPI>
+__device__ __forceinline__ void convert_chunk(const uint32_t (&v)[32], const GemmParams& p, int col0, float s_row,
+                                              uint32_t (&o)[OutWords<EPI>::kCount])
 {
     const int n_left = p.n - col0;
+    uint32_t w[32];
+    if (p.bias != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if constexpr (EPI == EPI_S32 || EPI == EPI_DEQ_BF16) {
+                const uint32_t b = (i < n_left) ? __ldg(static_cast<const uint32_t*>(p.bias) + col0 + i) : 0u;
+                w[i] = v[i] + b; // two's complement: the int32 sum
+            } else {
+                const float b = (i < n_left) ? __ldg(static_cast<const float*>(p.bias) + col0 + i) : 0.0f;
+                w[i] = __float_as_uint(__fadd_rn(__uint_as_float(v[i]), b));
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            w[i] = v[i];
+        }
+    }
     if constexpr (EPI == EPI_F32 || EPI == EPI_S32) {
-        uint32_t* dst = reinterpret_cast<uint32_t*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
-        if (vec_ok && n_left >= 32) {
-            uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                d4[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                if (i < n_left) {
-                    dst[i] = v[i];
-                }
-            }
+        for (int i = 0; i < 32; ++i) {
+            o[i] = w[i];
         }
     } else {
         float f[32];
@@ -154,50 +175,74 @@ __device__ __forceinline__ void store_chunk_nobias(const uint32_t (&v)[32], cons
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
                 const float sc = (i < n_left) ? __ldg(p.s_col + col0 + i) : 0.0f;
-                const float t = __fmul_rn(__int2float_rn(static_cast<int>(v[i])), sc);
+                const float t = __fmul_rn(__int2float_rn(static_cast<int>(w[i])), sc);
                 f[i] = __fmul_rn(t, s_row);
             }
         } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-                f[i] = __uint_as_float(v[i]);
+                f[i] = __uint_as_float(w[i]);
             }
         }
-        uint32_t packed[16];
         if constexpr (EPI == EPI_F16) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
-                packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+                o[i] = *reinterpret_cast<const uint32_t*>(&h);
             }
         } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-                packed[i] = *reinterpret_cast<const uint32_t*>(&h);
+                o[i] = *reinterpret_cast<const uint32_t*>(&h);
             }
         }
-        uint16_t* dst = reinterpret_cast<uint16_t*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
+    }
+}
+
+// The words of one chunk stored straight to C by the thread that owns the row: 16-byte stores when C allows them,
+// element by element on unaligned or ragged edges.
+template <int EPI>
+__device__ __forceinline__ void store_words(const uint32_t (&o)[OutWords<EPI>::kCount], const GemmParams& p, int row,
+                                            int col0, bool vec_ok)
+{
+    const int n_left = p.n - col0;
+    if constexpr (EPI == EPI_F32 || EPI == EPI_S32) {
+        uint32_t* dst = reinterpret_cast<uint32_t*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
         if (vec_ok && n_left >= 32) {
             uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                d4[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+            for (int i = 0; i < 8; ++i) {
+                d4[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
             }
         } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
                 if (i < n_left) {
-                    dst[i] = static_cast<uint16_t>((packed[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu);
+                    dst[i] = o[i];
+                }
+            }
+        }
+    } else {
+        uint16_t* dst = reinterpret_cast<uint16_t*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
+        if (vec_ok && n_left >= 32) {
+            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                d4[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                if (i < n_left) {
+                    dst[i] = static_cast<uint16_t>((o[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu);
                 }
             }
         }
     }
 }
 
-// One 32-column chunk of one accumulator row: optional bias, then cast / dequantise and store. The bias is added to
-// the finished accumulator in the accumulator's own type, once per output element (TMATMUL_BIAS adds it after the
-// first matmul of the K loop, include/pto/cpu/TMatmul.hpp:219-230: exact for int32, one fp32 rounding apart otherwise).
+// One 32-column chunk of one accumulator row: bias, cast / dequantise, store.
 template <int EPI>
 __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], const GemmParams& p, int row, int col0,
                                             bool vec_ok, float s_row)
@@ -205,23 +250,9 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], const GemmP
     if (row >= p.m) {
         return;
     }
-    if (p.bias == nullptr) {
-        store_chunk_nobias<EPI>(v, p, row, col0, vec_ok, s_row);
-        return;
-    }
-    const int n_left = p.n - col0;
-    uint32_t w[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        if constexpr (EPI == EPI_S32 || EPI == EPI_DEQ_BF16) {
-            const uint32_t b = (i < n_left) ? __ldg(static_cast<const uint32_t*>(p.bias) + col0 + i) : 0u;
-            w[i] = v[i] + b; // two's complement: the int32 sum
-        } else {
-            const float b = (i < n_left) ? __ldg(static_cast<const float*>(p.bias) + col0 + i) : 0.0f;
-            w[i] = __float_as_uint(__fadd_rn(__uint_as_float(v[i]), b));
-        }
-    }
-    store_chunk_nobias<EPI>(w, p, row, col0, vec_ok, s_row);
+    uint32_t o[OutWords<EPI>::kCount];
+    convert_chunk<EPI>(v, p, col0, s_row, o);
+    store_words<EPI>(o, p, row, col0, vec_ok);
 }
 
 template <int KIND, int BLOCK_N, int STAGES, int EPI, bool B_MN_MAJOR>
@@ -285,7 +316,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
                 int mi, ni;
                 tile_coords(tile, p, mi, ni);
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    ok = bounded_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, ST_PRODUCER_TIMEOUT);
+                    ok = bounded_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, ST_PRODUCER_TIMEOUT, p.wait_limit);
                     if (!ok) {
                         break;
                     }
@@ -330,14 +361,14 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             uint32_t acc_phase = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-                ok = bounded_wait(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag, p.status, ST_MMA_ACC_TIMEOUT);
+                ok = bounded_wait(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag, p.status, ST_MMA_ACC_TIMEOUT, p.wait_limit);
                 if (!ok) {
                     break;
                 }
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kAccCols);
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
-                    ok = bounded_wait(&full_bar[stage], phase, abort_flag, p.status, ST_MMA_FULL_TIMEOUT);
+                    ok = bounded_wait(&full_bar[stage], phase, abort_flag, p.status, ST_MMA_FULL_TIMEOUT, p.wait_limit);
                     if (!ok) {
                         break;
                     }
@@ -407,7 +438,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
         for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
             int mi, ni;
             tile_coords(tile, p, mi, ni);
-            ok = bounded_wait(&acc_full_bar[acc], acc_phase, abort_flag, p.status, ST_EPILOGUE_TIMEOUT);
+            ok = bounded_wait(&acc_full_bar[acc], acc_phase, abort_flag, p.status, ST_EPILOGUE_TIMEOUT, p.wait_limit);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) {
                 break;

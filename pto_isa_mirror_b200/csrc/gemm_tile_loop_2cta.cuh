@@ -10,10 +10,30 @@
 //   empty[stage]  one in each CTA, released by the leader's tcgen05.commit to both
 //   acc_full[a]   one in each CTA, published by the leader's tcgen05.commit to both
 //   acc_empty[a]  lives in the leader; the peer's TSTORE warps arrive on it across the cluster
+//
+// TSTORE: a finished accumulator leaves tensor memory through registers into a 128-byte-swizzled shared-memory
+// buffer per warp and from there with TMA tensor stores (one 32-row x 128-byte box at a time), so the tensor
+// memory is free again after the read-back instead of after the global stores, and every store is a full line.
+// When C does not meet the TMA alignment rule the warps store from registers as gemm_tile_loop does.
+//
+// Block-scaled kind: the e8m0 scale atoms of a stage arrive in shared memory with the operands; the MMA warp of the
+// second CTA, which issues no MMAs, copies them into tensor memory (tcgen05.cp, every stage of the ring has its own
+// scale columns) and commits to the leader, so no scale copy sits in the leader's MMA instruction stream.
+//
+// K-split form (FUSED_AR): the kernel of one rank of the reference's GEMM + AllReduce
+// (kernels/manual/a2a3/gemm_ar: gemm_compute_kernel.cpp:150-240 fills a ready queue tile by tile, comm_kernel.cpp
+// :165-210 reduce-scatters, :377-400 all-gathers, :528-590 waits). Here both halves are ONE kernel: the tile loop
+// walks the output row panel by row panel and counts finished tiles per panel; the warp that completes a panel
+// publishes ready[panel][rank] to every rank; four extra warps per CTA (the exchange role) wait for all ranks' flags
+// of a panel, sum this rank's row shard of it over the ranks' fp32 partials through peer memory (NVSwitch multimem
+// or plain peer loads), cast to bf16, store the result into every rank's output, publish done[panel][rank], and at
+// the end wait until every rank has delivered every panel here. No TMA load and no multicast load touches peer memory.
+//
 // Every wait is bounded as in gemm_tile_loop; the pair leaves through a cluster barrier so neither CTA's shared
 // or tensor memory disappears while the other can still touch it.
 #pragma once
 #include "gemm_tile_loop.cuh"
+#include "ksplit_reduce.cuh"
 
 namespace pto_b200 {
 
@@ -22,6 +42,10 @@ constexpr int kPairBlockN = 256;
 
 constexpr int ST_TAIL_TIMEOUT = 5;
 
+constexpr int kExchangeThreads = 128; // four exchange warps per CTA in the K-split form
+constexpr int kExchangeBarrierId = 1;
+constexpr int ST_SCALE_TIMEOUT = 6;
+
 __device__ __forceinline__ int ld_acquire_gpu(const int* ptr)
 {
     int v;
@@ -29,19 +53,41 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* ptr)
     return v;
 }
 
-template <int KIND, int STAGES>
+// What the K-split form needs besides the GEMM's own arguments. Peer pointer arrays hold one entry per rank (the
+// rank's buffer as mapped in this process, own rank included).
+struct KsplitFusedArgs {
+    PeerPointers ready;      // every rank's ready-flag array
+    PeerPointers done;       // every rank's done-flag array
+    PeerPointers partial;    // every rank's fp32 partial [m, ld_partial] of this step
+    PeerPointers out;        // every rank's bf16 output [m, ld_out]
+    const float* mc_partial; // NVSwitch multicast address of the partials, or null (plain peer loads)
+    void* mc_out;            // NVSwitch multicast address of the outputs, or null (one store per rank)
+    int* panel_counter;      // local, one int per slot, zero between steps: finished TSTORE warps of a panel
+    int* exchange_counter;   // local, one int per slot, zero between steps: CTAs that reduced their part of a shard
+    long long ld_partial, ld_out;
+    int world, rank, epoch;
+    int slot0;               // first flag slot of this step (slots alternate with the partial buffer)
+    int panels;              // row panels of the output
+    int panel_tile_rows;     // 256-row tiles per panel (= the raster's group height)
+};
+
+template <int KIND, int STAGES, int EPI_BUFS>
 struct PairSmemLayout {
     static constexpr int kABytes = kBlockM * kBlockKBytes;        // this CTA's 128 rows of A
     static constexpr int kBBytes = (kPairBlockN / 2) * kBlockKBytes; // this CTA's 128 columns of B
     static constexpr int kSfaBytes = (KIND == KIND_MXF8) ? 512 : 0;
     static constexpr int kSfbBytes = (KIND == KIND_MXF8) ? 1024 : 0; // scales of all 256 columns, in both CTAs
-    static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+    static constexpr int kStageBytes = kABytes + kBBytes; // operand bytes per CTA that complete on the leader's barrier
+    static constexpr int kEpiBufBytes = 32 * 128;                 // 32 rows x 128 bytes: one TMA store box
+    static constexpr int kEpiBytes = 4 * EPI_BUFS * kEpiBufBytes; // per TSTORE warp EPI_BUFS buffers
     static constexpr int kAOff = 0;
     static constexpr int kBOff = STAGES * kABytes;
-    static constexpr int kSfaOff = kBOff + STAGES * kBBytes;
+    static constexpr int kEpiOff = kBOff + STAGES * kBBytes;      // 1024-byte aligned (swizzle atom)
+    static constexpr int kSfaOff = kEpiOff + kEpiBytes;
     static constexpr int kSfbOff = kSfaOff + STAGES * kSfaBytes;
     static constexpr int kBarOff = kSfbOff + STAGES * kSfbBytes;
-    static constexpr int kNumBars = 2 * STAGES + 4;
+    // per stage: full, empty, scale bytes landed (local), scales in tensor memory (leader); 2 x 2 accumulator barriers
+    static constexpr int kNumBars = 4 * STAGES + 4;
     static constexpr int kMiscOff = kBarOff + kNumBars * 8;
     static constexpr int kTotal = kMiscOff + 16 + 1024;
 };
@@ -79,27 +125,44 @@ __device__ __forceinline__ bool pair_unit(int u, const GemmParams& p, PairUnit& 
 
 constexpr int kTailWarps = 8; // store warps of a pair: four in each CTA
 
-template <int KIND, int STAGES, int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+// Parked accumulators of a split tile: per CTA of the pair 128 rows x 256 columns of 32-bit words, laid out so that a
+// warp's 16-byte accesses are contiguous: word index ((chunk * 8 + i) * 128 + row) * 4 for the i-th 16 bytes of the
+// 32-column chunk `chunk` of row `row`.
+__device__ __forceinline__ uint4* parked_quad(uint32_t* cta_base, int chunk, int i, int row_in_cta)
+{
+    return reinterpret_cast<uint4*>(cta_base) + (chunk * 8 + i) * kBlockM + row_in_cta;
+}
+
+template <int KIND, int STAGES, int EPI, bool FUSED_AR>
+__global__ void __cluster_dims__(2, 1, 1)
+    __launch_bounds__(kNumThreads + (FUSED_AR ? kExchangeThreads : 0), 1)
     gemm_tile_loop_2cta(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                        const GemmParams p)
+                        const __grid_constant__ CUtensorMap tmap_c, const GemmParams p, const KsplitFusedArgs ar)
 {
-    using L = PairSmemLayout<KIND, STAGES>;
+    constexpr int kEpiBufs = (KIND == KIND_MXF8) ? 1 : 2;
+    using L = PairSmemLayout<KIND, STAGES, kEpiBufs>;
     constexpr int kNumAcc = (KIND == KIND_MXF8) ? 1 : 2;
     constexpr int kAccCols = 256;
-    constexpr uint32_t kSfaCol = 256;
-    constexpr uint32_t kSfbCol = 260;
+    constexpr uint32_t kSfCol0 = 256;   // scale columns of stage s: [kSfCol0 + 12 s, +4) for A, the next 8 for B
+    constexpr uint32_t kSfColsPerStage = 12;
+    static_assert(KIND != KIND_MXF8 || kAccCols + STAGES * 12 <= kTmemCols, "scale columns of every stage beside one accumulator");
     constexpr int kBlockKElems = (KIND == KIND_F16) ? 64 : 128;
+    constexpr bool kOut32 = (EPI == EPI_F32 || EPI == EPI_S32);
+    constexpr int kWords = OutWords<EPI>::kCount;
+    static_assert(!FUSED_AR || (KIND == KIND_F16 && EPI == EPI_F32), "the K-split form multiplies 16-bit inputs into fp32 partials");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
     uint64_t* empty_bar = full_bar + STAGES;
-    uint64_t* acc_full_bar = empty_bar + STAGES;
+    uint64_t* sf_landed_bar = empty_bar + STAGES;   // second CTA: both CTAs' scale atoms of the stage are in shared memory
+    uint64_t* sf_full_bar = sf_landed_bar + STAGES; // leader: the stage's scales are in both CTAs' tensor memory
+    uint64_t* acc_full_bar = sf_full_bar + STAGES;
     uint64_t* acc_empty_bar = acc_full_bar + 2;
     uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + L::kMiscOff + 4);
+    volatile uint32_t* exchange_ok = reinterpret_cast<volatile uint32_t*>(smem + L::kMiscOff + 8);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -112,15 +175,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
         for (int s = 0; s < STAGES; ++s) {
             ptx::mbar_init(&full_bar[s], 1);
             ptx::mbar_init(&empty_bar[s], 1);
+            ptx::mbar_init(&sf_landed_bar[s], 1);
+            ptx::mbar_init(&sf_full_bar[s], 1);
         }
         for (int a = 0; a < 2; ++a) {
             ptx::mbar_init(&acc_full_bar[a], 1);
             ptx::mbar_init(&acc_empty_bar[a], 8); // four TSTORE warps in each CTA of the pair
         }
         *abort_flag = 0;
+        *exchange_ok = 1;
         ptx::fence_mbar_init();
         ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_b);
+        if (p.tma_store != 0) {
+            ptx::prefetch_tensormap(&tmap_c);
+        }
     }
     if (warp == 1) {
         ptx::tmem_alloc_pair(tmem_base_slot, kTmemCols);
@@ -145,7 +214,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                 const int row_a = mi * kPairBlockM + static_cast<int>(cta_rank) * kBlockM;
                 const int row_b = ni * kPairBlockN + static_cast<int>(cta_rank) * (kPairBlockN / 2);
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
-                    ok = bounded_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, ST_PRODUCER_TIMEOUT);
+                    ok = bounded_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, ST_PRODUCER_TIMEOUT,
+                                      p.wait_limit);
                     if (!ok) {
                         break;
                     }
@@ -160,13 +230,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                     if constexpr (KIND == KIND_MXF8) {
                         // Scale atoms through tensor maps over the re-tiled workspace viewed as rows of 256 bytes
                         // (an atom is two rows): A rows of this CTA (row block 2*mi + rank), B columns of the whole
-                        // tile (two atoms). The tensor form lets the bytes complete on the leader's barrier.
+                        // tile (two atoms). Both CTAs' scale bytes complete on a barrier of the second CTA, whose
+                        // otherwise idle MMA warp copies them into tensor memory.
                         const int sfa_row = (kb * (2 * p.m_tiles) + 2 * mi + static_cast<int>(cta_rank)) * 2;
                         const int sfb_row = (kb * p.n_tiles + ni) * 4;
-                        ptx::tma_load_2d_pair(smem + L::kSfaOff + stage * L::kSfaBytes, &tmap_sfa, full_addr, 0,
-                                              sfa_row);
-                        ptx::tma_load_2d_pair(smem + L::kSfbOff + stage * L::kSfbBytes, &tmap_sfb, full_addr, 0,
-                                              sfb_row);
+                        if (!leader) {
+                            ptx::mbar_arrive_expect_tx(&sf_landed_bar[stage], 2u * (L::kSfaBytes + L::kSfbBytes));
+                        }
+                        const uint32_t landed_addr = ptx::map_to_cta(ptx::smem_u32(&sf_landed_bar[stage]), 1);
+                        ptx::tma_load_2d_pair(smem + L::kSfaOff + stage * L::kSfaBytes, &tmap_sfa, landed_addr, 0, sfa_row);
+                        ptx::tma_load_2d_pair(smem + L::kSfbOff + stage * L::kSfbBytes, &tmap_sfb, landed_addr, 0, sfb_row);
                     }
                     if (++stage == STAGES) {
                         stage = 0;
@@ -176,6 +249,40 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
             }
         }
     } else if (warp == 1) {
+        if constexpr (KIND == KIND_MXF8) {
+            // ------------------------------------------------------------ scale copies (second CTA's MMA warp)
+            // tcgen05.cp.cta_group::2 copies the same shared-memory offsets of both CTAs into both CTAs' tensor
+            // memory; every stage of the ring has its own 12 scale columns. Issued from the CTA that issues no MMAs,
+            // the copies stay out of the leader's MMA instruction stream; the commit tells the leader.
+            if (!leader && lane == 0) {
+                int stage = 0;
+                uint32_t phase = 0;
+                bool ok = true;
+                PairUnit w;
+                for (int u = pair; ok && pair_unit(u, p, w); u += num_pairs) {
+                    for (int kb = w.kb0; kb < w.kb1; ++kb) {
+                        ok = bounded_wait(&sf_landed_bar[stage], phase, abort_flag, p.status, ST_SCALE_TIMEOUT,
+                                          p.wait_limit);
+                        if (!ok) {
+                            break;
+                        }
+                        ptx::tc_fence_after_sync();
+                        const uint32_t sfa_base = ptx::smem_u32(smem + L::kSfaOff + stage * L::kSfaBytes);
+                        const uint32_t sfb_base = ptx::smem_u32(smem + L::kSfbOff + stage * L::kSfbBytes);
+                        const uint32_t sf = tmem_base + kSfCol0 + kSfColsPerStage * static_cast<uint32_t>(stage);
+                        ptx::tmem_cp_32x128b_warpx4_pair(sf, ptx::make_smem_desc(sfa_base, 0, 128, ptx::kSwizzleNone));
+                        ptx::tmem_cp_32x128b_warpx4_pair(sf + 4u, ptx::make_smem_desc(sfb_base, 0, 128, ptx::kSwizzleNone));
+                        ptx::tmem_cp_32x128b_warpx4_pair(sf + 8u,
+                                                         ptx::make_smem_desc(sfb_base + 512u, 0, 128, ptx::kSwizzleNone));
+                        ptx::umma_commit_pair(&sf_full_bar[stage], 0x1);
+                        if (++stage == STAGES) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                    }
+                }
+            }
+        }
         // ---------------------------------------------------------------- TMATMUL / TMATMUL_ACC role (leader only)
         if (leader && lane == 0) {
             int stage = 0;
@@ -185,14 +292,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
             bool ok = true;
             PairUnit w;
             for (int u = pair; ok && pair_unit(u, p, w); u += num_pairs) {
-                ok = bounded_wait(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag, p.status, ST_MMA_ACC_TIMEOUT);
+                ok = bounded_wait(&acc_empty_bar[acc], acc_phase ^ 1u, abort_flag, p.status, ST_MMA_ACC_TIMEOUT,
+                                  p.wait_limit);
                 if (!ok) {
                     break;
                 }
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kAccCols);
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
-                    ok = bounded_wait(&full_bar[stage], phase, abort_flag, p.status, ST_MMA_FULL_TIMEOUT);
+                    ok = bounded_wait(&full_bar[stage], phase, abort_flag, p.status, ST_MMA_FULL_TIMEOUT, p.wait_limit);
                     if (!ok) {
                         break;
                     }
@@ -200,14 +308,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                     const uint32_t a_base = ptx::smem_u32(smem + L::kAOff + stage * L::kABytes);
                     const uint32_t b_base = ptx::smem_u32(smem + L::kBOff + stage * L::kBBytes);
                     if constexpr (KIND == KIND_MXF8) {
-                        const uint32_t sfa_base = ptx::smem_u32(smem + L::kSfaOff + stage * L::kSfaBytes);
-                        const uint32_t sfb_base = ptx::smem_u32(smem + L::kSfbOff + stage * L::kSfbBytes);
-                        ptx::tmem_cp_32x128b_warpx4_pair(tmem_base + kSfaCol,
-                                                         ptx::make_smem_desc(sfa_base, 0, 128, ptx::kSwizzleNone));
-                        ptx::tmem_cp_32x128b_warpx4_pair(tmem_base + kSfbCol,
-                                                         ptx::make_smem_desc(sfb_base, 0, 128, ptx::kSwizzleNone));
-                        ptx::tmem_cp_32x128b_warpx4_pair(tmem_base + kSfbCol + 4u,
-                                                         ptx::make_smem_desc(sfb_base + 512u, 0, 128, ptx::kSwizzleNone));
+                        // the scale role of both CTAs has put this stage's scales into tensor memory
+                        ok = bounded_wait(&sf_full_bar[stage], phase, abort_flag, p.status, ST_SCALE_TIMEOUT, p.wait_limit);
+                        if (!ok) {
+                            break;
+                        }
+                        ptx::tc_fence_after_sync();
                     }
 #pragma unroll
                     for (int kk = 0; kk < kBlockKBytes / kUmmaKBytes; ++kk) {
@@ -223,8 +329,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                         } else {
                             const uint32_t idesc =
                                 p.idesc | (static_cast<uint32_t>(kk) << 4) | (static_cast<uint32_t>(kk) << 29);
-                            ptx::umma_mxf8_pair(d_tmem, a_desc, b_desc, idesc, tmem_base + kSfaCol, tmem_base + kSfbCol,
-                                                accumulate);
+                            const uint32_t sf = tmem_base + kSfCol0 + kSfColsPerStage * static_cast<uint32_t>(stage);
+                            ptx::umma_mxf8_pair(d_tmem, a_desc, b_desc, idesc, sf, sf + 4u, accumulate);
                         }
                     }
                     ptx::umma_commit_pair(&empty_bar[stage], 0x3);
@@ -243,36 +349,41 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                 }
             }
         }
-    } else {
+    } else if (warp < 6) {
         // ---------------------------------------------------------------- TSTORE role (both CTAs)
         const int quarter = warp & 3;
-        const int esize = (EPI == EPI_F32 || EPI == EPI_S32) ? 4 : 2;
+        const int esize = kOut32 ? 4 : 2;
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0) && (((p.ldc * esize) & 15) == 0);
+        uint8_t* epi_buf = smem + L::kEpiOff + quarter * kEpiBufs * L::kEpiBufBytes;
+        uint8_t* my_line = epi_buf + lane * 128; // this thread's row inside a store box
         int acc = 0;
         uint32_t acc_phase = 0;
+        uint32_t boxes = 0; // TMA store boxes this warp has issued
         bool ok = true;
         PairUnit w;
         for (int u = pair; ok && pair_unit(u, p, w); u += num_pairs) {
             const int mi = w.mi, ni = w.ni;
-            ok = bounded_wait(&acc_full_bar[acc], acc_phase, abort_flag, p.status, ST_EPILOGUE_TIMEOUT);
+            ok = bounded_wait(&acc_full_bar[acc], acc_phase, abort_flag, p.status, ST_EPILOGUE_TIMEOUT, p.wait_limit);
             ok = __all_sync(0xFFFFFFFFu, ok);
             if (!ok) {
                 break;
             }
             ptx::tc_fence_after_sync();
-            const int row = mi * kPairBlockM + static_cast<int>(cta_rank) * kBlockM + quarter * 32 + lane;
+            const int row_in_cta = quarter * 32 + lane;
+            const int row0_warp = mi * kPairBlockM + static_cast<int>(cta_rank) * kBlockM + quarter * 32;
+            const int row = row0_warp + lane;
             float s_row = 1.0f;
             if constexpr (EPI == EPI_DEQ_BF16) {
                 s_row = (row < p.m) ? __ldg(p.s_row + row) : 0.0f;
             }
             const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * kAccCols) +
                                    (static_cast<uint32_t>(quarter * 32) << 16);
-            // this thread's row of the parked accumulators of a split tile
-            uint32_t* ws_row = nullptr;
+            const bool use_tma = (w.role == 0) && (p.tma_store != 0);
+            // parked accumulators of a split tile (this CTA's 128 x 256 words) and the tile's two counters
+            uint32_t* ws_cta = nullptr;
             int* ws_arrive = nullptr;
             if (w.role != 0) {
-                ws_row = p.ws_partial + (static_cast<size_t>(w.tail_idx) * kPairBlockM +
-                                         cta_rank * kBlockM + quarter * 32 + lane) * kPairBlockN;
+                ws_cta = p.ws_partial + (static_cast<size_t>(w.tail_idx) * 2 + cta_rank) * (kBlockM * kPairBlockN);
                 ws_arrive = p.ws_flags + 2 * w.tail_idx;
             }
             if (w.role == 2) {
@@ -282,7 +393,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                     const long long t0 = clock64();
                     while (ld_acquire_gpu(ws_arrive) < kTailWarps) {
                         __nanosleep(32);
-                        if (*abort_flag != 0 || clock64() - t0 > kWaitLimitCycles) {
+                        if (*abort_flag != 0 || clock64() - t0 > p.wait_limit) {
                             *abort_flag = 1;
                             atomicCAS(p.status, 0, ST_TAIL_TIMEOUT);
                             parked = false;
@@ -296,27 +407,33 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                     break;
                 }
             }
-            // one 32-column chunk of this thread's row: park it (first K half), add the parked half (second K half),
-            // then cast / scale and store
+            // One 32-column chunk of this thread's row. Whole tiles: convert and either write the words into the
+            // warp's swizzled store box (a box is one chunk of 32-bit outputs or two chunks of 16-bit outputs; the
+            // box leaves with one TMA store when it is full) or store them from registers. Split tiles: park the raw
+            // accumulators (first K half) or add the parked half and store from registers (second K half).
             auto finish_chunk = [&](uint32_t (&v)[32], int chunk) {
+                constexpr int kChunksPerBox = kOut32 ? 1 : 2;
                 const int col0 = ni * kPairBlockN + chunk * 32;
-                if (col0 >= p.n) {
+                // nothing to do past N; a store box that starts before N is still filled and sent whole (TMA clips it)
+                if ((use_tma ? col0 - (chunk % kChunksPerBox) * 32 : col0) >= p.n) {
                     return;
                 }
                 if (w.role == 1) {
-                    uint4* d4 = reinterpret_cast<uint4*>(ws_row + chunk * 32);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        d4[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                        *parked_quad(ws_cta, chunk, i, row_in_cta) = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
                     }
                     return;
                 }
                 if (w.role == 2) {
-                    const uint4* s4 = reinterpret_cast<const uint4*>(ws_row + chunk * 32);
+                    uint4 q[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        const uint4 q = __ldcg(s4 + i);
-                        const uint32_t qa[4] = {q.x, q.y, q.z, q.w};
+                        q[i] = __ldcg(parked_quad(ws_cta, chunk, i, row_in_cta));
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint32_t qa[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             if constexpr (EPI == EPI_S32 || EPI == EPI_DEQ_BF16) {
@@ -327,12 +444,42 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                         }
                     }
                 }
-                store_chunk<EPI>(v, p, row, col0, vec_ok, s_row);
+                if (!use_tma) {
+                    store_chunk<EPI>(v, p, row, col0, vec_ok, s_row);
+                    return;
+                }
+                uint32_t o[kWords];
+                convert_chunk<EPI>(v, p, col0, s_row, o);
+                const int part = chunk % kChunksPerBox; // which half of the 128-byte line (16-bit outputs)
+                uint8_t* line = my_line + (boxes % kEpiBufs) * L::kEpiBufBytes;
+                if (part == 0) {
+                    // the box that used this buffer kEpiBufs boxes ago must have been read out of shared memory
+                    if (lane == 0) {
+                        ptx::bulk_wait_group_read<kEpiBufs - 1>();
+                    }
+                    __syncwarp();
+                }
+                constexpr int kQuads = kWords / 4; // 16-byte pieces this chunk fills: 8 (32-bit) or 4 (16-bit)
+#pragma unroll
+                for (int i = 0; i < kQuads; ++i) {
+                    const int piece = part * kQuads + i;          // 0..7 within the 128-byte line
+                    const int sw = piece ^ (lane & 7);            // 128-byte swizzle: piece index XOR (row mod 8)
+                    *reinterpret_cast<uint4*>(line + sw * 16) = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                }
+                if (part == kChunksPerBox - 1) {
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int box_col0 = col0 - part * 32;
+                        ptx::tma_store_2d(&tmap_c, epi_buf + (boxes % kEpiBufs) * L::kEpiBufBytes, box_col0, row0_warp);
+                        ptx::bulk_commit_group();
+                    }
+                    ++boxes;
+                }
             };
             // Accumulator read-back, software-pipelined over 32-column chunks: the TMEM load of the next chunk is in
             // flight while the current one is converted and stored (columns past N are loaded but never stored).
-            // Two chunks of registers keep the kernel near 128 registers per thread, so that a reduction CTA of the
-            // K-split path still fits beside this CTA on the SM.
+            // The accumulator is handed back to the MMA role as soon as its last chunk is in registers.
             {
                 uint32_t va[32], vb[32];
                 ptx::tmem_ld_32x32b_x32(t_row + 0u, va);
@@ -344,6 +491,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                     ptx::tmem_ld_wait();
                     if (g + 1 < kPairBlockN / 64) {
                         ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(g * 64 + 64), va);
+                    } else {
+                        ptx::tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (leader) {
+                                ptx::mbar_arrive(&acc_empty_bar[acc]);
+                            } else {
+                                ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&acc_empty_bar[acc]), 0));
+                            }
+                        }
                     }
                     finish_chunk(vb, g * 2 + 1);
                 }
@@ -364,18 +521,106 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
                     }
                 }
             }
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-                if (leader) {
-                    ptx::mbar_arrive(&acc_empty_bar[acc]);
-                } else {
-                    ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&acc_empty_bar[acc]), 0));
+            if constexpr (FUSED_AR) {
+                // This warp's rows of the tile are written: count it for the tile's row panel. The warp that completes
+                // the panel tells every rank that this rank's partial of the panel can be read.
+                if (use_tma) {
+                    if (lane == 0) {
+                        ptx::bulk_wait_group<0>(); // the box stores have been performed, not merely read out
+                    }
+                }
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) {
+                    const int panel = mi / ar.panel_tile_rows;
+                    const int tile_rows = min(p.m_tiles - panel * ar.panel_tile_rows, ar.panel_tile_rows);
+                    const int expected = tile_rows * p.n_tiles * kTailWarps;
+                    const int slot = ar.slot0 + panel;
+                    if (atomicAdd(ar.panel_counter + slot, 1) == expected - 1) {
+                        ar.panel_counter[slot] = 0;
+                        __threadfence_system();
+                        for (int r = 0; r < ar.world; ++r) {
+                            st_release_sys(static_cast<int*>(ar.ready.p[r]) + slot * kFlagStride + ar.rank, ar.epoch);
+                        }
+                    }
                 }
             }
             if (++acc == kNumAcc) {
                 acc = 0;
                 acc_phase ^= 1u;
+            }
+        }
+        // shared memory must outlive the reads of the last store boxes
+        if (lane == 0) {
+            ptx::bulk_wait_group_read<0>();
+        }
+    } else if constexpr (FUSED_AR) {
+        // ---------------------------------------------------------------- exchange role (both CTAs, K-split form)
+        const int tid = static_cast<int>(threadIdx.x) - kNumThreads;
+        const long long first = static_cast<long long>(blockIdx.x) * kExchangeThreads + tid;
+        const long long stride = static_cast<long long>(gridDim.x) * kExchangeThreads;
+        const int* ready_local = static_cast<const int*>(ar.ready.p[ar.rank]);
+        const int* done_local = static_cast<const int*>(ar.done.p[ar.rank]);
+        const int panel_rows = ar.panel_tile_rows * kPairBlockM;
+        bool ok = true;
+        for (int panel = 0; panel < ar.panels; ++panel) {
+            const int slot = ar.slot0 + panel;
+            if (tid < ar.world) {
+                if (!wait_epoch(ready_local + slot * kFlagStride + tid, ar.epoch, p.status, ST_KSPLIT_READY_TIMEOUT,
+                                p.wait_limit)) {
+                    *exchange_ok = 0;
+                }
+            }
+            ptx::named_barrier_sync(kExchangeBarrierId, kExchangeThreads);
+            ok = (*exchange_ok != 0);
+            if (ok) {
+                // this rank's row shard of the panel; every CTA of the grid takes a slice of it
+                const int r0 = panel * panel_rows;
+                const int rows = min(p.m - r0, panel_rows);
+                const int per = (rows + ar.world - 1) / ar.world;
+                const int s0 = min(rows, ar.rank * per);
+                const int s1 = min(rows, s0 + per);
+                ShardView v;
+                v.partial = ar.partial;
+                v.out = ar.out;
+                v.mc_partial = ar.mc_partial;
+                v.mc_out = ar.mc_out;
+                v.world = ar.world;
+                v.row0 = r0 + s0;
+                v.rows = s1 - s0;
+                v.n = p.n;
+                v.ld_partial = ar.ld_partial;
+                v.ld_out = ar.ld_out;
+                reduce_shard(v, first, stride);
+            }
+            // The last CTA to finish its slice publishes the shard as delivered, unless a CTA gave up on its wait.
+            __threadfence_system();
+            ptx::named_barrier_sync(kExchangeBarrierId, kExchangeThreads);
+            if (tid == 0) {
+                const int add = ok ? 1 : 1 + kCounterFailed;
+                const int after = atomicAdd(ar.exchange_counter + slot, add) + add;
+                if ((after & (kCounterFailed - 1)) == static_cast<int>(gridDim.x)) {
+                    ar.exchange_counter[slot] = 0;
+                    __threadfence_system();
+                    if (after < kCounterFailed) {
+                        for (int r = 0; r < ar.world; ++r) {
+                            st_release_sys(static_cast<int*>(ar.done.p[r]) + slot * kFlagStride + ar.rank, ar.epoch);
+                        }
+                    }
+                }
+            }
+            if (!ok) {
+                break; // the remaining panels would only wait for the same missing rank
+            }
+        }
+        if (ok) {
+            // the step is complete here once every owner has delivered every panel into this rank's output
+            for (int i = tid; i < ar.panels * ar.world; i += kExchangeThreads) {
+                const int slot = ar.slot0 + i / ar.world;
+                if (!wait_epoch(done_local + slot * kFlagStride + i % ar.world, ar.epoch, p.status,
+                                ST_KSPLIT_DONE_TIMEOUT, p.wait_limit)) {
+                    break;
+                }
             }
         }
     }

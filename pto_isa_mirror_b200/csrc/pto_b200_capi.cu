@@ -17,8 +17,13 @@
 #include "ksplit_reduce.cuh"
 #include "mx_quantize.cuh"
 
-#if !defined(__CUDA_ARCH_LIST__)
-#error "pto_b200 is built with nvcc for sm_100a only"
+#if !defined(__CUDACC__)
+#error "pto_b200 is CUDA source: build it with nvcc -gencode arch=compute_100a,code=sm_100a"
+#endif
+// Device passes: only the architecture-specific sm_100a target has tcgen05, tensor memory and the TMA forms used
+// here. There is no other back end and no fallback, so any other target is a build error, not a slower path.
+#if defined(__CUDA_ARCH__) && !(__CUDA_ARCH__ == 1000 && defined(__CUDA_ARCH_FEAT_SM100_ALL))
+#error "pto_b200 kernels are written for sm_100a only (nvcc -gencode arch=compute_100a,code=sm_100a)"
 #endif
 
 namespace pto_b200 {
@@ -28,6 +33,7 @@ __device__ int g_status_word = 0;
 
 thread_local char t_cuda_error[256] = "";
 std::atomic<unsigned long long> g_launches{0};
+std::atomic<long long> g_wait_limit{kWaitLimitCycles}; // cycles one bounded wait may take (pto_b200_set_wait_limit)
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -38,7 +44,8 @@ struct DeviceInfo {
     int err = PTO_B200_OK;
     int sm_count = 0;
     int* status_ptr = nullptr;
-    bool force_1cta = false; // PTO_B200_FORCE_1CTA=1 in the environment: never pick the two-CTA kernels
+    bool force_1cta = false;   // PTO_B200_FORCE_1CTA=1 in the environment: never pick the two-CTA kernels
+    bool no_tma_store = false; // PTO_B200_NO_TMA_STORE=1: the two-CTA kernels store C from registers (A/B measurements)
 };
 
 constexpr int kMaxDevices = 64;
@@ -77,6 +84,8 @@ int device_info(DeviceInfo** out)
             cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
             const char* force = std::getenv("PTO_B200_FORCE_1CTA");
             d.force_1cta = (force != nullptr && force[0] == '1');
+            const char* no_tma = std::getenv("PTO_B200_NO_TMA_STORE");
+            d.no_tma_store = (no_tma != nullptr && no_tma[0] == '1');
             d.err = note_cuda(cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status_ptr), g_status_word),
                               "cudaGetSymbolAddress(status)");
             if (d.err == PTO_B200_OK && g_encode == nullptr) {
@@ -126,6 +135,10 @@ int make_tensor_map(CUtensorMap* map, int dtype, const void* base, long long row
             break;
         case PTO_B200_BF16:
             dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+            break;
+        case PTO_B200_F32:
+        case PTO_B200_S32:
+            dt = CU_TENSOR_MAP_DATA_TYPE_UINT32; // store maps only: the bytes move unchanged
             break;
         default:
             dt = CU_TENSOR_MAP_DATA_TYPE_UINT8;
@@ -217,17 +230,29 @@ int launch_block_n(int block_n, cudaStream_t stream, const CUtensorMap& ta, cons
 
 // Two-CTA kernels: 256 x 256 tiles on clusters of two CTAs. Returns -1 when the problem should stay on the
 // one-CTA kernel (fewer tiles than CTA pairs the device can hold at once), otherwise a PTO_B200 code.
-template <int KIND, int EPI>
+struct PairLaunch {
+    const CUtensorMap* sfa_map = nullptr; // block-scaled kinds only
+    const CUtensorMap* sfb_map = nullptr;
+    int block_limit = 0;                  // cap on thread blocks (launch_block_count), 0 = every SM
+    uint8_t* workspace = nullptr;         // split last wave, or null
+    size_t workspace_bytes = 0;
+    int out_dtype = PTO_B200_F32;         // element type of C (for the store map)
+    const KsplitFusedArgs* fused = nullptr; // K-split form: exchange arguments (group height = its panel height)
+    bool no_tma_store = false;
+};
+
+template <int KIND, int EPI, bool FUSED_AR = false>
 int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, const Problem& q,
-                const CUtensorMap* sfa_map = nullptr, const CUtensorMap* sfb_map = nullptr, int block_limit = 0,
-                uint8_t* workspace = nullptr, size_t workspace_bytes = 0)
+                const PairLaunch& o)
 {
 #ifndef PTO_B200_PAIR_STAGES
 #define PTO_B200_PAIR_STAGES 6
 #endif
     constexpr int STAGES = (KIND == KIND_MXF8) ? 6 : PTO_B200_PAIR_STAGES;
-    using L = PairSmemLayout<KIND, STAGES>;
-    auto kernel = gemm_tile_loop_2cta<KIND, STAGES, EPI>;
+    constexpr int kEpiBufs = (KIND == KIND_MXF8) ? 1 : 2;
+    constexpr int kThreads = kNumThreads + (FUSED_AR ? kExchangeThreads : 0);
+    using L = PairSmemLayout<KIND, STAGES, kEpiBufs>;
+    auto kernel = gemm_tile_loop_2cta<KIND, STAGES, EPI, FUSED_AR>;
     static std::atomic<int> max_clusters[kMaxDevices];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -237,7 +262,7 @@ int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& t
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
-    cfg.blockDim = dim3(kNumThreads, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = L::kTotal;
     cfg.stream = stream;
     cfg.attrs = attr;
@@ -261,33 +286,55 @@ int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& t
     }
     p.m_tiles = (q.m + kPairBlockM - 1) / kPairBlockM;
     p.n_tiles = (q.n + kPairBlockN - 1) / kPairBlockN;
-    p.group_m = 8;
+    p.group_m = FUSED_AR ? o.fused->panel_tile_rows : 8;
     const int tiles = p.m_tiles * p.n_tiles;
-    if (tiles < clusters) {
+    if (tiles < clusters && !FUSED_AR) {
         return -1;
     }
-    int pairs = clusters;
-    if (block_limit > 0 && block_limit / 2 < pairs) {
-        pairs = block_limit / 2 > 0 ? block_limit / 2 : 1;
+    int pairs = tiles < clusters ? tiles : clusters;
+    if (o.block_limit > 0 && o.block_limit / 2 < pairs) {
+        pairs = o.block_limit / 2 > 0 ? o.block_limit / 2 : 1;
     }
     cfg.gridDim = dim3(2 * pairs, 1, 1);
     // Last wave: when the leftover tiles would occupy at most half of the pairs, cut each of them into two K halves
-    // that run on two pairs at once (accumulators of the first half parked in the caller's workspace).
+    // that run on two pairs at once (accumulators of the first half parked in the caller's workspace). The second
+    // half waits in the kernel for the first, so the split is only used when this launch may take every SM (no block
+    // cap) and is never combined with the K-split form.
     const int leftover = tiles % pairs;
     p.tail_first_unit = tiles;
     p.tail_tiles = 0;
-    if (workspace != nullptr && workspace_bytes >= kGemmWorkspaceBytes && leftover > 0 && 2 * leftover <= pairs &&
-        leftover <= kGemmWorkspaceTiles && p.k_blocks >= 2) {
+    if (!FUSED_AR && o.workspace != nullptr && o.workspace_bytes >= kGemmWorkspaceBytes && o.block_limit == 0 &&
+        leftover > 0 && 2 * leftover <= pairs && leftover <= kGemmWorkspaceTiles && p.k_blocks >= 2) {
         p.tail_first_unit = tiles - leftover;
         p.tail_tiles = leftover;
-        p.ws_flags = reinterpret_cast<int*>(workspace);
-        p.ws_partial = reinterpret_cast<uint32_t*>(workspace + kGemmWorkspaceFlagBytes);
+        p.ws_flags = reinterpret_cast<int*>(o.workspace);
+        p.ws_partial = reinterpret_cast<uint32_t*>(o.workspace + kGemmWorkspaceFlagBytes);
+        // counters start from zero whatever an earlier launch that gave up left behind
+        if (int rc = note_cuda(cudaMemsetAsync(o.workspace, 0, kGemmWorkspaceFlagBytes, stream), "workspace flags")) {
+            return rc;
+        }
+    }
+    // C leaves through TMA stores when it is 16-byte aligned with a 16-byte row pitch (the rule for any TMA copy)
+    constexpr int esize = (EPI == EPI_F32 || EPI == EPI_S32) ? 4 : 2;
+    CUtensorMap tc = ta;
+    p.tma_store = 0;
+    // ... and its rows end on a 16-byte boundary: at a ragged end the store unit is a whole 16-byte piece, which
+    // would run past column N (measured: bf16, N = 2500 wrote columns 2500..2503)
+    if (!o.no_tma_store && (reinterpret_cast<uintptr_t>(p.c) & 15u) == 0 && ((p.ldc * esize) & 15) == 0 &&
+        ((static_cast<long long>(q.n) * esize) & 15) == 0) {
+        if (int rc = make_tensor_map(&tc, o.out_dtype, p.c, q.m, q.n, p.ldc, 128 / esize, 32)) {
+            return rc;
+        }
+        p.tma_store = 1;
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     // the scale maps are only read by the block-scaled instantiations; the others get copies of the A map
-    const CUtensorMap& ma = sfa_map ? *sfa_map : ta;
-    const CUtensorMap& mb = sfb_map ? *sfb_map : ta;
-    return note_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, ma, mb, p), "gemm_tile_loop_2cta launch");
+    const CUtensorMap& ma = o.sfa_map ? *o.sfa_map : ta;
+    const CUtensorMap& mb = o.sfb_map ? *o.sfb_map : ta;
+    KsplitFusedArgs none;
+    std::memset(&none, 0, sizeof(none));
+    const KsplitFusedArgs& fa = o.fused ? *o.fused : none;
+    return note_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, ma, mb, tc, p, fa), "gemm_tile_loop_2cta launch");
 }
 
 // 128-wide tiles when 256-wide ones would leave SMs without work and the narrower split fills more of them.
@@ -330,6 +377,7 @@ void fill_params(GemmParams& p, void* out, const Problem& q, int block_n, int k_
     p.k_blocks = (q.k + k_elems_per_block - 1) / k_elems_per_block;
     p.group_m = 16;
     p.status = status;
+    p.wait_limit = g_wait_limit.load(std::memory_order_relaxed);
 }
 
 } // namespace
@@ -418,20 +466,26 @@ static int gemm_dense_impl(void* stream, uint8_t* out, const uint8_t* src0, cons
         }
         GemmParams pp = p;
         int rc = -1;
+        PairLaunch o;
+        o.block_limit = launch_block_count;
+        o.workspace = workspace;
+        o.workspace_bytes = workspace_bytes;
+        o.out_dtype = out_dtype;
+        o.no_tma_store = dev->no_tma_store;
         if (is8) {
             pp.idesc = make_idesc(2, 1, 1, false, kPairBlockN, false, kPairBlockM);
-            rc = launch_pair<KIND_I8, EPI_S32>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count, workspace, workspace_bytes);
+            rc = launch_pair<KIND_I8, EPI_S32>(s, ta, tb_half, pp, q, o);
         } else {
             pp.idesc = make_idesc(1, fmt, fmt, false, kPairBlockN, false, kPairBlockM);
             switch (out_dtype) {
                 case PTO_B200_F32:
-                    rc = launch_pair<KIND_F16, EPI_F32>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count, workspace, workspace_bytes);
+                    rc = launch_pair<KIND_F16, EPI_F32>(s, ta, tb_half, pp, q, o);
                     break;
                 case PTO_B200_BF16:
-                    rc = launch_pair<KIND_F16, EPI_BF16>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count, workspace, workspace_bytes);
+                    rc = launch_pair<KIND_F16, EPI_BF16>(s, ta, tb_half, pp, q, o);
                     break;
                 default:
-                    rc = launch_pair<KIND_F16, EPI_F16>(s, ta, tb_half, pp, q, nullptr, nullptr, launch_block_count, workspace, workspace_bytes);
+                    rc = launch_pair<KIND_F16, EPI_F16>(s, ta, tb_half, pp, q, o);
                     break;
             }
         }
@@ -518,7 +572,10 @@ extern "C" int pto_b200_gemm_s8_dequant(void* stream, uint8_t* out, const uint8_
         }
         GemmParams pp = p;
         pp.idesc = make_idesc(2, 1, 1, false, kPairBlockN, false, kPairBlockM);
-        const int rc = launch_pair<KIND_I8, EPI_DEQ_BF16>(static_cast<cudaStream_t>(stream), ta, tb_half, pp, q);
+        PairLaunch o;
+        o.out_dtype = PTO_B200_BF16;
+        o.no_tma_store = dev->no_tma_store;
+        const int rc = launch_pair<KIND_I8, EPI_DEQ_BF16>(static_cast<cudaStream_t>(stream), ta, tb_half, pp, q, o);
         if (rc != -1) {
             return rc;
         }
@@ -539,10 +596,10 @@ extern "C" size_t pto_b200_gemm_mx_workspace_bytes(int m, int n, int k)
     return k_blocks * (m_blocks + n_blocks) * 512;
 }
 
-static int gemm_mx_impl(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, const uint8_t* src2,
-                        const uint8_t* src3, uint8_t* workspace, size_t workspace_bytes, int m, int n, int k,
-                        long long lda, long long ldb, long long ldc, long long ld_sfa, long long ld_sfb, int a_dtype,
-                        int b_dtype, int out_dtype, const void* bias)
+// Argument checks of the block-scaled GEMM that need no device: dtype table, pointers, sizes, TMA alignment.
+static int mx_check_args(const uint8_t* out, const uint8_t* src0, const uint8_t* src1, const uint8_t* src2,
+                         const uint8_t* src3, int m, int n, int k, long long lda, long long ldb, long long ldc,
+                         long long ld_sfa, long long ld_sfb, int a_dtype, int b_dtype, int out_dtype, const void* bias)
 {
     if (bias != nullptr && (reinterpret_cast<uintptr_t>(bias) & 3u)) {
         return PTO_B200_EALIGN;
@@ -562,6 +619,19 @@ static int gemm_mx_impl(void* stream, uint8_t* out, const uint8_t* src0, const u
     if (k % 32 != 0 || ld_sfa < k / 32 || ld_sfb < k / 32) {
         return PTO_B200_EINVAL;
     }
+    return PTO_B200_OK;
+}
+
+static int gemm_mx_impl(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, const uint8_t* src2,
+                        const uint8_t* src3, uint8_t* workspace, size_t workspace_bytes, int m, int n, int k,
+                        long long lda, long long ldb, long long ldc, long long ld_sfa, long long ld_sfb, int a_dtype,
+                        int b_dtype, int out_dtype, const void* bias)
+{
+    if (int rc = mx_check_args(out, src0, src1, src2, src3, m, n, k, lda, ldb, ldc, ld_sfa, ld_sfb, a_dtype, b_dtype,
+                               out_dtype, bias)) {
+        return rc;
+    }
+    const Problem q{m, n, k, lda, ldb, ldc};
     if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 15u) ||
         workspace_bytes < pto_b200_gemm_mx_workspace_bytes(m, n, k)) {
         return PTO_B200_EWORKSPACE;
@@ -623,10 +693,15 @@ static int gemm_mx_impl(void* stream, uint8_t* out, const uint8_t* src0, const u
             return rc;
         }
         if (pairs) {
+            PairLaunch o;
+            o.sfa_map = &tsa;
+            o.sfb_map = &tsb;
+            o.out_dtype = out_dtype;
+            o.no_tma_store = dev->no_tma_store;
             if (out_dtype == PTO_B200_F32) {
-                return launch_pair<KIND_MXF8, EPI_F32>(s, ta, tb, p, q, &tsa, &tsb);
+                return launch_pair<KIND_MXF8, EPI_F32>(s, ta, tb, p, q, o);
             }
-            return launch_pair<KIND_MXF8, EPI_BF16>(s, ta, tb, p, q, &tsa, &tsb);
+            return launch_pair<KIND_MXF8, EPI_BF16>(s, ta, tb, p, q, o);
         }
         if (out_dtype == PTO_B200_F32) {
             return launch_block_n<KIND_MXF8, EPI_F32, false>(block_n, s, ta, tb, p, dev->sm_count);
@@ -833,10 +908,10 @@ extern "C" int pto_b200_ksplit_reduce(void* stream, void* const* partial_ptrs, v
         return PTO_B200_EALIGN;
     }
     KsplitReduceArgs a;
-    if (int rc = fill_peers(a.partial, partial_ptrs, world)) {
+    if (int rc = fill_peers(a.shard.partial, partial_ptrs, world)) {
         return rc;
     }
-    if (int rc = fill_peers(a.out, out_ptrs, world)) {
+    if (int rc = fill_peers(a.shard.out, out_ptrs, world)) {
         return rc;
     }
     if (int rc = fill_peers(a.done, done_arrays, world)) {
@@ -847,27 +922,28 @@ extern "C" int pto_b200_ksplit_reduce(void* stream, void* const* partial_ptrs, v
             return PTO_B200_EALIGN;
         }
     }
+    if ((reinterpret_cast<uintptr_t>(multicast_partial) & 15u) || (reinterpret_cast<uintptr_t>(multicast_out) & 7u)) {
+        return PTO_B200_EALIGN;
+    }
     DeviceInfo* dev = nullptr;
     if (int rc = device_info(&dev)) {
         return rc;
     }
-    if ((reinterpret_cast<uintptr_t>(multicast_partial) & 15u) || (reinterpret_cast<uintptr_t>(multicast_out) & 7u)) {
-        return PTO_B200_EALIGN;
-    }
-    a.mc_partial = static_cast<const float*>(multicast_partial);
-    a.mc_out = multicast_out;
+    a.shard.mc_partial = static_cast<const float*>(multicast_partial);
+    a.shard.mc_out = multicast_out;
+    a.shard.world = world;
+    a.shard.row0 = row0;
+    a.shard.rows = rows;
+    a.shard.n = n;
+    a.shard.ld_partial = ld_partial;
+    a.shard.ld_out = ld_out;
     a.ready = ready_local;
     a.cta_counter = cta_counters_local;
     a.status = dev->status_ptr;
-    a.world = world;
+    a.wait_limit = g_wait_limit.load(std::memory_order_relaxed);
     a.rank = rank;
     a.slot = slot;
     a.epoch = epoch;
-    a.row0 = row0;
-    a.rows = rows;
-    a.n = n;
-    a.ld_partial = ld_partial;
-    a.ld_out = ld_out;
     const long long work = (static_cast<long long>(rows) * (n / 4) + kReduceThreads - 1) / kReduceThreads;
     int grid = launch_block_count > 0 ? launch_block_count : 32;
     if (work < grid) {
@@ -887,10 +963,99 @@ extern "C" int pto_b200_ksplit_wait(void* stream, const int* done_local, int wor
     if (int rc = device_info(&dev)) {
         return rc;
     }
-    ksplit_wait_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(done_local, world, slot0, slots, epoch,
-                                                                         dev->status_ptr);
+    ksplit_wait_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(
+        done_local, world, slot0, slots, epoch, dev->status_ptr, g_wait_limit.load(std::memory_order_relaxed));
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return note_cuda(cudaGetLastError(), "ksplit_wait launch");
+}
+
+extern "C" int pto_b200_ksplit_gemm_allreduce(void* stream, const uint8_t* src0, const uint8_t* src1, int m, int n,
+                                              int k_local, long long lda, long long ldb, int in_dtype,
+                                              void* const* partial_ptrs, void* const* out_ptrs,
+                                              void* const* ready_arrays, void* const* done_arrays,
+                                              int* panel_counters_local, int* exchange_counters_local, int world,
+                                              int rank, int slot0, int epoch, int panel_rows, long long ld_partial,
+                                              long long ld_out, const void* multicast_partial, void* multicast_out,
+                                              int launch_block_count)
+{
+    if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || slot0 < 0 || epoch < 1 ||
+        panel_counters_local == nullptr || exchange_counters_local == nullptr || launch_block_count < 0 ||
+        panel_rows <= 0 || panel_rows % kPairBlockM != 0 || ld_partial < n || ld_out < n) {
+        return PTO_B200_EINVAL;
+    }
+    if (in_dtype != PTO_B200_F16 && in_dtype != PTO_B200_BF16) {
+        return PTO_B200_EDTYPE;
+    }
+    KsplitFusedArgs fa;
+    std::memset(&fa, 0, sizeof(fa));
+    if (int rc = fill_peers(fa.partial, partial_ptrs, world)) {
+        return rc;
+    }
+    if (int rc = fill_peers(fa.out, out_ptrs, world)) {
+        return rc;
+    }
+    if (int rc = fill_peers(fa.ready, ready_arrays, world)) {
+        return rc;
+    }
+    if (int rc = fill_peers(fa.done, done_arrays, world)) {
+        return rc;
+    }
+    uint8_t* partial_local = static_cast<uint8_t*>(partial_ptrs[rank]);
+    const Problem q{m, n, k_local, lda, ldb, ld_partial};
+    if (int rc = check_common(partial_local, src0, src1, q, 2, 2, false)) {
+        return rc;
+    }
+    if ((n & 3) || (ld_partial & 3) || (ld_out & 3)) {
+        return PTO_B200_EALIGN;
+    }
+    for (int r = 0; r < world; ++r) {
+        if ((reinterpret_cast<uintptr_t>(partial_ptrs[r]) & 15u) || (reinterpret_cast<uintptr_t>(out_ptrs[r]) & 7u)) {
+            return PTO_B200_EALIGN;
+        }
+    }
+    if ((reinterpret_cast<uintptr_t>(multicast_partial) & 15u) || (reinterpret_cast<uintptr_t>(multicast_out) & 7u)) {
+        return PTO_B200_EALIGN;
+    }
+    DeviceInfo* dev = nullptr;
+    if (int rc = device_info(&dev)) {
+        return rc;
+    }
+    fa.mc_partial = static_cast<const float*>(multicast_partial);
+    fa.mc_out = multicast_out;
+    fa.panel_counter = panel_counters_local;
+    fa.exchange_counter = exchange_counters_local;
+    fa.ld_partial = ld_partial;
+    fa.ld_out = ld_out;
+    fa.world = world;
+    fa.rank = rank;
+    fa.epoch = epoch;
+    fa.slot0 = slot0;
+    fa.panel_tile_rows = panel_rows / kPairBlockM;
+    fa.panels = (m + panel_rows - 1) / panel_rows;
+    const int kelems = kBlockKBytes / 2;
+    GemmParams p;
+    fill_params(p, partial_local, q, kPairBlockN, kelems, dev->status_ptr);
+    const int fmt = (in_dtype == PTO_B200_BF16) ? 1 : 0;
+    p.idesc = make_idesc(1, fmt, fmt, false, kPairBlockN, false, kPairBlockM);
+    CUtensorMap ta, tb_half;
+    if (int rc = make_tensor_map(&ta, in_dtype, src0, m, k_local, lda, kelems, kBlockM)) {
+        return rc;
+    }
+    if (int rc = make_tensor_map(&tb_half, in_dtype, src1, n, k_local, ldb, kelems, kPairBlockN / 2)) {
+        return rc;
+    }
+    PairLaunch o;
+    o.block_limit = launch_block_count;
+    o.out_dtype = PTO_B200_F32;
+    o.fused = &fa;
+    o.no_tma_store = dev->no_tma_store;
+    const int rc = launch_pair<KIND_F16, EPI_F32, true>(static_cast<cudaStream_t>(stream), ta, tb_half, p, q, o);
+    return rc == -1 ? PTO_B200_EDEVICE : rc;
+}
+
+extern "C" long long pto_b200_set_wait_limit(long long cycles)
+{
+    return g_wait_limit.exchange(cycles > 0 ? cycles : kWaitLimitCycles, std::memory_order_relaxed);
 }
 
 extern "C" void call_kernel(uint32_t blockDim, void* stream, uint8_t* out, uint8_t* src0, uint8_t* src1)
@@ -976,7 +1141,6 @@ static __device__ __align__(256) uint8_t g_mx_static_scratch[PTO_B200_MX_STATIC_
 
 struct StaticScratch {
     bool ready = false;
-    int err = PTO_B200_OK;
     uint8_t* ptr = nullptr;
 };
 StaticScratch g_static_scratch[kMaxDevices];
@@ -994,16 +1158,22 @@ int static_scratch_for_current_device(uint8_t** out)
     std::lock_guard<std::mutex> lock(g_mutex);
     StaticScratch& s = g_static_scratch[dev];
     if (!s.ready) {
+        // A failed lookup (for instance a first call made while the stream is being captured) is reported to this
+        // caller and tried again by the next one; only a resolved address is cached.
         void* p = nullptr;
-        s.err = note_cuda(cudaGetSymbolAddress(&p, g_mx_static_scratch), "cudaGetSymbolAddress(mx static scratch)");
-        s.ptr = static_cast<uint8_t*>(p);
-        if (s.err == PTO_B200_OK && s.ptr == nullptr) {
-            s.err = PTO_B200_ECUDA;
+        int err = note_cuda(cudaGetSymbolAddress(&p, g_mx_static_scratch), "cudaGetSymbolAddress(mx static scratch)");
+        if (err == PTO_B200_OK && p == nullptr) {
+            err = PTO_B200_ECUDA;
         }
+        if (err != PTO_B200_OK) {
+            (void)cudaGetLastError(); // do not leave the failure sticky for the caller's next CUDA call
+            return err;
+        }
+        s.ptr = static_cast<uint8_t*>(p);
         s.ready = true;
     }
     *out = s.ptr;
-    return s.err;
+    return PTO_B200_OK;
 }
 
 } // namespace
@@ -1014,8 +1184,10 @@ extern "C" int pto_b200_gemm_mx_static(void* stream, uint8_t* out, const uint8_t
                                        long long ldb, long long ldc, long long ld_sfa, long long ld_sfb, int a_dtype,
                                        int b_dtype, int out_dtype)
 {
-    if (m <= 0 || n <= 0 || k <= 0) {
-        return PTO_B200_EINVAL;
+    // the same argument errors, in the same order, as pto_b200_gemm_mx, before any CUDA call is made
+    if (int rc = mx_check_args(out, src0, src1, src2, src3, m, n, k, lda, ldb, ldc, ld_sfa, ld_sfb, a_dtype, b_dtype,
+                               out_dtype, nullptr)) {
+        return rc;
     }
     if (pto_b200_gemm_mx_workspace_bytes(m, n, k) > static_cast<size_t>(PTO_B200_MX_STATIC_SCRATCH_BYTES)) {
         return PTO_B200_ESCRATCH;

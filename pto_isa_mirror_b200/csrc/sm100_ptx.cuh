@@ -84,6 +84,39 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_sr
         : "memory");
 }
 
+// 2-D tiled bulk-tensor store, this CTA's shared memory -> global, tracked by the thread's bulk async-groups.
+// Elements outside the tensor's extents are not written, so ragged edges need no masks. x * element size must be a
+// multiple of 16 bytes and neither coordinate may be negative.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+                 : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+
+// Wait until at most N of this thread's bulk async-groups are still reading their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read()
+{
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
+// Wait until at most N of this thread's bulk async-groups are incomplete (their global writes performed).
+template <int N>
+__device__ __forceinline__ void bulk_wait_group()
+{
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Barrier among `threads` threads of the CTA (a multiple of 32) on hardware barrier `id` (1..15; 0 is __syncthreads).
+__device__ __forceinline__ void named_barrier_sync(int id, int threads)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05: tensor memory management
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols)
 {
@@ -177,6 +210,16 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)
 }
 
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Each thread of the warp writes 4 consecutive 32-bit columns of its own TMEM lane (same lane rule as the loads).
+__device__ __forceinline__ void tmem_st_32x32b_x4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c),
+                 "r"(d)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ---------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor (64-bit): start address, leading/stride byte offsets (all >> 4),

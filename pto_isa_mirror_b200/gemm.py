@@ -214,9 +214,11 @@ def gemv(x: torch.Tensor, b_dn: torch.Tensor, out_dtype: torch.dtype = torch.flo
     return out
 
 
-def mx_quantize_e4m3(src: torch.Tensor, stream: Optional[torch.cuda.Stream] = None):
+def mx_quantize_e4m3(src: torch.Tensor, stream: Optional[torch.cuda.Stream] = None,
+                     data: Optional[torch.Tensor] = None, scales: Optional[torch.Tensor] = None):
     """OCP MX quantisation (TQUANT, MXFP8): float32 src [rows, K] -> (e4m3 bytes [rows, K] uint8, e8m0 scales
-    [rows, K/32] uint8), one scale per 32 elements along K. Finite input only."""
+    [rows, K/32] uint8), one scale per 32 elements along K. Finite input only. ``data`` / ``scales``: caller's output
+    buffers of those shapes (allocated when omitted)."""
     lib = _capi.load()
     _require_cuda_2d(src, "src")
     if src.dtype != torch.float32:
@@ -224,8 +226,14 @@ def mx_quantize_e4m3(src: torch.Tensor, stream: Optional[torch.cuda.Stream] = No
     rows, k = src.shape
     if k % 32 != 0:
         raise ValueError("K must be a multiple of 32")
-    data = torch.empty((rows, k), dtype=torch.uint8, device=src.device)
-    scales = torch.empty((rows, k // 32), dtype=torch.uint8, device=src.device)
+    if data is None:
+        data = torch.empty((rows, k), dtype=torch.uint8, device=src.device)
+    if scales is None:
+        scales = torch.empty((rows, k // 32), dtype=torch.uint8, device=src.device)
+    for t, shape, name in ((data, (rows, k), "data"), (scales, (rows, k // 32), "scales")):
+        _require_cuda_2d(t, name)
+        if t.dtype != torch.uint8 or tuple(t.shape) != shape:
+            raise ValueError(f"{name} must be a uint8 CUDA tensor of shape {shape}")
     rc = lib.pto_b200_mx_quantize_e4m3(_stream_ptr(stream), data.data_ptr(), scales.data_ptr(), src.data_ptr(), rows,
                                        k, src.stride(0), data.stride(0), scales.stride(0))
     _capi.check(rc, "pto_b200_mx_quantize_e4m3")

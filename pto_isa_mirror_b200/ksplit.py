@@ -6,9 +6,14 @@ partials are summed across ranks (reduce-scatter by atomic add into the owner's 
 and every rank ends with the full result (all-gather, comm_kernel.cpp:377-400), compute and communication running
 on two streams (main.cpp:761-800).
 
-Here rank r computes P_r = A[:, K_r] @ B[K_r, :] with the tcgen05 tile loop, panel by panel over M; each panel's
-fp32 partial is reduced with NCCL over NVLink on a second stream while the next panel is being multiplied, and
-the reduced panel is cast to bf16 (the TSTORE cast). Two reductions are offered:
+Here rank r computes P_r = A[:, K_r] @ B[K_r, :] with the tcgen05 tile loop, panel by panel over M, and each
+panel's fp32 partial is reduced across the ranks while later panels are being multiplied; the reduced panel is cast
+to bf16 (the TSTORE cast). Three implementations, fastest first:
+
+* :class:`KSplitGemmFused`  - one kernel launch per step: the GEMM's own extra warps exchange the finished panels
+  over peer memory (NVSwitch multimem or plain peer loads);
+* :class:`KSplitGemmP2P`    - one GEMM launch per panel plus this library's reduction kernels on a second stream;
+* :class:`KSplitGemmAllReduce` - the same panel pipeline with NCCL collectives (the baseline), two reductions:
 
 * ``"allreduce"``: ncclAllReduce(fp32 sum) then cast;
 * ``"rs_ag"``    : reduce-scatter (fp32) -> cast of the owned shard -> all-gather (bf16), which moves 25 % fewer
@@ -172,24 +177,9 @@ class KSplitGemmP2P:
         """``panels`` equal row panels, or explicit ``panel_rows`` heights (decreasing heights leave only a small
         reduction exposed after the last GEMM). ``reduce_blocks`` thread blocks run each reduction beside the next
         GEMM; ``reduce_blocks_last`` (0 = four times that) run the last one, which has the GPU to itself."""
-        import ctypes
-
-        import torch.distributed._symmetric_memory as symm_mem
-
-        from . import _capi
-
         if not dist.is_initialized():
             raise RuntimeError("KSplitGemmP2P needs an initialised process group (one process per GPU)")
-        self._ctypes = ctypes
-        self._capi = _capi
-        self.lib = _capi.load()
-        self.group = group if group is not None else dist.group.WORLD
-        self.world_size = dist.get_world_size(self.group)
-        self.rank = dist.get_rank(self.group)
-        if self.world_size > 8:
-            raise ValueError("at most 8 ranks (one NVSwitch domain)")
-        self.m, self.n = m, n
-        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self._setup_ranks(group, device, m, n)
         align = 128 * self.world_size
         self.panels = panels_from_rows(m, panel_rows, align) if panel_rows else panel_bounds(m, panels, align)
         if any((r1 - r0) % self.world_size for r0, r1 in self.panels) or n % 4:
@@ -197,36 +187,8 @@ class KSplitGemmP2P:
         self.reduce_blocks = reduce_blocks
         self.reduce_blocks_last = reduce_blocks_last if reduce_blocks_last > 0 else 4 * reduce_blocks
         self.launch_block_count = launch_block_count
-        self.num_slots = 2 * len(self.panels)
-        # symmetric allocations: two fp32 partial buffers, the bf16 output, ready + done flags
-        self.partial = symm_mem.empty((2, m, n), dtype=torch.float32, device=self.device)
-        self.out = symm_mem.empty((m, n), dtype=torch.bfloat16, device=self.device)
-        self.flags = symm_mem.empty((2, self.num_slots, 8), dtype=torch.int32, device=self.device)
-        self.flags.zero_()
+        self._allocate(use_multicast)
         self.cta_counters = torch.zeros(self.num_slots, dtype=torch.int32, device=self.device)
-        torch.cuda.synchronize(self.device)
-        h_partial = symm_mem.rendezvous(self.partial, self.group)
-        h_out = symm_mem.rendezvous(self.out, self.group)
-        h_flags = symm_mem.rendezvous(self.flags, self.group)
-        self._handles = (h_partial, h_out, h_flags)
-        ws = self.world_size
-        PtrArray = ctypes.c_void_p * ws
-        pbytes = m * n * 4
-        self._partial_ptrs = [PtrArray(*[int(h_partial.buffer_ptrs[r]) + b * pbytes for r in range(ws)]) for b in (0, 1)]
-        self._out_ptrs = PtrArray(*[int(h_out.buffer_ptrs[r]) for r in range(ws)])
-        fbytes = self.num_slots * 8 * 4
-        self._ready_ptrs = PtrArray(*[int(h_flags.buffer_ptrs[r]) for r in range(ws)])
-        self._done_ptrs = PtrArray(*[int(h_flags.buffer_ptrs[r]) + fbytes for r in range(ws)])
-        # NVSwitch multicast addresses (NVLS) of the partial and output buffers, when the platform maps them:
-        # the reduction then happens inside the switch (multimem.ld_reduce) and the result is broadcast by one store
-        mc_p = int(getattr(h_partial, "multicast_ptr", 0) or 0) if use_multicast else 0
-        mc_o = int(getattr(h_out, "multicast_ptr", 0) or 0) if use_multicast else 0
-        self.multicast = bool(mc_p and mc_o)
-        self._mc_partial = [mc_p + b * pbytes if self.multicast else None for b in (0, 1)]
-        self._mc_out = mc_o if self.multicast else None
-        self._ready_local = self.flags[0].data_ptr()
-        self._done_local = self.flags[1].data_ptr()
-        self.epoch = 0
         self.comm_stream = torch.cuda.Stream(device=self.device)
         # With two GEMM streams consecutive panels' persistent GEMM kernels overlap at their edges: the CTAs of panel
         # p+1 start on the SMs that ran out of tiles in the last wave of panel p, so the partly filled last wave is
@@ -234,8 +196,84 @@ class KSplitGemmP2P:
         self.aux_stream = torch.cuda.Stream(device=self.device) if gemm_streams > 1 else None
         self.events = [torch.cuda.Event() for _ in self.panels]
         self.start_event = torch.cuda.Event()
-        dist.barrier(self.group)          # every rank's flags are zero and mapped before anyone signals
+        self._ready_to_start()
+
+    # ---------------------------------------------------------------- shared set-up of the peer-memory variants
+    def _setup_ranks(self, group, device, m, n):
+        import ctypes
+
+        from . import _capi
+
+        self._ctypes = ctypes
+        self._capi = _capi
+        self.lib = _capi.load()
+        self.distributed = dist.is_initialized()
+        self.group = (group if group is not None else dist.group.WORLD) if self.distributed else None
+        self.world_size = dist.get_world_size(self.group) if self.distributed else 1
+        self.rank = dist.get_rank(self.group) if self.distributed else 0
+        if self.world_size > 8:
+            raise ValueError("at most 8 ranks (one NVSwitch domain)")
+        self.m, self.n = m, n
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+
+    def _allocate(self, use_multicast: bool):
+        """Two fp32 partial buffers (alternating by step), the bf16 output and the ready / done flags, mapped into
+        every rank (torch symmetric memory); a single process without a process group gets plain device memory."""
+        ctypes = self._ctypes
+        m, n, ws = self.m, self.n, self.world_size
+        self.num_slots = 2 * len(self.panels)
+        if self.distributed:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            self.partial = symm_mem.empty((2, m, n), dtype=torch.float32, device=self.device)
+            self.out = symm_mem.empty((m, n), dtype=torch.bfloat16, device=self.device)
+            self.flags = symm_mem.empty((2, self.num_slots, 8), dtype=torch.int32, device=self.device)
+            self.flags.zero_()
+            torch.cuda.synchronize(self.device)
+            h_partial = symm_mem.rendezvous(self.partial, self.group)
+            h_out = symm_mem.rendezvous(self.out, self.group)
+            h_flags = symm_mem.rendezvous(self.flags, self.group)
+            self._handles = (h_partial, h_out, h_flags)
+            partial_base = [int(h_partial.buffer_ptrs[r]) for r in range(ws)]
+            out_base = [int(h_out.buffer_ptrs[r]) for r in range(ws)]
+            flag_base = [int(h_flags.buffer_ptrs[r]) for r in range(ws)]
+            # NVSwitch multicast addresses (NVLS) of the partial and output buffers, when the platform maps them:
+            # the reduction then happens inside the switch (multimem.ld_reduce), the result is broadcast by one store
+            mc_p = int(getattr(h_partial, "multicast_ptr", 0) or 0) if use_multicast else 0
+            mc_o = int(getattr(h_out, "multicast_ptr", 0) or 0) if use_multicast else 0
+        else:
+            self.partial = torch.empty((2, m, n), dtype=torch.float32, device=self.device)
+            self.out = torch.empty((m, n), dtype=torch.bfloat16, device=self.device)
+            self.flags = torch.zeros((2, self.num_slots, 8), dtype=torch.int32, device=self.device)
+            self._handles = ()
+            partial_base, out_base, flag_base = [self.partial.data_ptr()], [self.out.data_ptr()], [self.flags.data_ptr()]
+            mc_p = mc_o = 0
+        PtrArray = ctypes.c_void_p * ws
+        pbytes = m * n * 4
+        fbytes = self.num_slots * 8 * 4
+        self._partial_ptrs = [PtrArray(*[base + b * pbytes for base in partial_base]) for b in (0, 1)]
+        self._out_ptrs = PtrArray(*out_base)
+        self._ready_ptrs = PtrArray(*flag_base)
+        self._done_ptrs = PtrArray(*[base + fbytes for base in flag_base])
+        self.multicast = bool(mc_p and mc_o)
+        self._mc_partial = [mc_p + b * pbytes if self.multicast else None for b in (0, 1)]
+        self._mc_out = mc_o if self.multicast else None
+        self._ready_local = self.flags[0].data_ptr()
+        self._done_local = self.flags[1].data_ptr()
+        self.epoch = 0
+
+    def _ready_to_start(self):
+        if self.distributed:
+            dist.barrier(self.group)      # every rank's flags are zero and mapped before anyone signals
         torch.cuda.synchronize(self.device)
+
+    def release(self):
+        """Drop the symmetric buffers. Call on every rank at the same point (after a barrier, nothing in flight): the
+        peers' mappings, and the NVSwitch multicast bindings, then go away together."""
+        torch.cuda.synchronize(self.device)
+        for name in ("partial", "out", "flags", "_handles"):
+            if hasattr(self, name):
+                delattr(self, name)
 
     def step(self, a_slice: torch.Tensor, b_slice_dn: torch.Tensor) -> torch.Tensor:
         from .gemm import gemm as _gemm
@@ -267,4 +305,55 @@ class KSplitGemmP2P:
         check(lib.pto_b200_ksplit_wait(self.comm_stream.cuda_stream, self._done_local, ws, buf * npan, npan, self.epoch),
               "pto_b200_ksplit_wait")
         main.wait_stream(self.comm_stream)
+        return self.out
+
+
+class KSplitGemmFused(KSplitGemmP2P):
+    """K-split GEMM + allreduce as ONE kernel launch per rank and step (``pto_b200_ksplit_gemm_allreduce``).
+
+    The reference runs its compute kernel and its communication kernel side by side on two streams and couples them
+    with a device-side ready queue that the compute kernel fills tile by tile (kernels/manual/a2a3/gemm_ar/
+    gemm_compute_kernel.cpp:150-240, comm_kernel.cpp:528-590). Here the two are one persistent kernel: the tile loop
+    walks the output panel by panel, the warp that finishes a panel publishes the ready flag to every rank, and four
+    extra warps per CTA reduce this rank's row shard of each ready panel over peer memory and deliver the bf16 result
+    to every rank while the tensor cores work on later panels. Against one launch per panel this removes the partly
+    filled last wave of every panel and all launch seams; only the last panel's exchange is exposed.
+
+    Without an initialised process group the instance runs as a single rank on plain device memory (the exchange
+    warps then cast this GPU's own partial): the one-GPU test and profiling form of the same kernel.
+    """
+
+    def __init__(self, m: int, n: int, group: Optional[dist.ProcessGroup] = None, panels: int = 8,
+                 device: Optional[torch.device] = None, launch_block_count: int = 0, use_multicast: bool = True):
+        self._setup_ranks(group, device, m, n)
+        if n % 4:
+            raise ValueError("n must be a multiple of 4")
+        per = -(-m // max(1, panels))
+        self.panel_rows = -(-per // 256) * 256          # whole 256-row tiles per panel
+        self.panels = [(r0, min(m, r0 + self.panel_rows)) for r0 in range(0, m, self.panel_rows)]
+        self.launch_block_count = launch_block_count
+        self._allocate(use_multicast)
+        self.panel_counters = torch.zeros(self.num_slots, dtype=torch.int32, device=self.device)
+        self.exchange_counters = torch.zeros(self.num_slots, dtype=torch.int32, device=self.device)
+        self._ready_to_start()
+
+    def step(self, a_slice: torch.Tensor, b_slice_dn: torch.Tensor) -> torch.Tensor:
+        from .gemm import _TORCH_TO_PTO, _require_cuda_2d
+
+        _require_cuda_2d(a_slice, "a_slice")
+        _require_cuda_2d(b_slice_dn, "b_slice_dn")
+        if a_slice.dtype != b_slice_dn.dtype or a_slice.dtype not in (torch.float16, torch.bfloat16):
+            raise ValueError("operands must both be float16 or bfloat16")
+        if a_slice.shape[0] != self.m or b_slice_dn.shape[0] != self.n or a_slice.shape[1] != b_slice_dn.shape[1]:
+            raise ValueError("operand slices must be [m, k_local] and [n, k_local]")
+        self.epoch += 1
+        buf = self.epoch & 1
+        stream = torch.cuda.current_stream(self.device)
+        rc = self.lib.pto_b200_ksplit_gemm_allreduce(
+            stream.cuda_stream, a_slice.data_ptr(), b_slice_dn.data_ptr(), self.m, self.n, a_slice.shape[1],
+            a_slice.stride(0), b_slice_dn.stride(0), _TORCH_TO_PTO[a_slice.dtype], self._partial_ptrs[buf],
+            self._out_ptrs, self._ready_ptrs, self._done_ptrs, self.panel_counters.data_ptr(),
+            self.exchange_counters.data_ptr(), self.world_size, self.rank, buf * len(self.panels), self.epoch,
+            self.panel_rows, self.n, self.n, self._mc_partial[buf], self._mc_out, self.launch_block_count)
+        self._capi.check(rc, "pto_b200_ksplit_gemm_allreduce")
         return self.out

@@ -363,3 +363,116 @@ def test_host_pipeline_matches_one_product_at_a_time():
     assert max_rel_err(got[0].numpy(), ref) <= DENSE_TOL
     with pytest.raises(ValueError):
         pipe.result(0)                                              # overwritten four submissions ago
+
+
+# ------------------------------------------------------------------ the CTA-pair kernel at depth, its store paths, fixed-shape launcher
+
+def test_pair_kernel_at_k65536():
+    """2304 x 2304 x 65536 bf16: 81 tiles of 256 x 256, more than the 74 CTA pairs, so the cta_group::2 kernel runs the
+    depth of the K-split configuration unsplit (1024 k-blocks per tile, 170 wraps of its stage ring). The reference's
+    own golden tile for K = 65536 sits at a tile position inside the matrix; two more tiles are checked against the
+    oracle's sequential chain."""
+    m = n = 2304
+    k = 65536
+    g = golden("bf16_tile_k65536")
+    ga, gb = gd.dense_inputs(128, 256, k, "bf16", 4)
+    gen = torch.Generator(device=DEV).manual_seed(65536)
+    ta = (torch.randn((m, k), generator=gen, device=DEV) / 256.0).to(torch.bfloat16)
+    tb = (torch.randn((n, k), generator=gen, device=DEV) / 256.0).to(torch.bfloat16)
+    r0g, c0g = 384, 1280                 # second CTA of a pair in M, second tile half in N
+    ta[r0g:r0g + 128] = dev16(ga, torch.bfloat16)
+    tb[c0g:c0g + 256] = dev16(gb, torch.bfloat16)
+    out32 = pto.gemm(ta, tb, torch.float32)
+    out16 = pto.gemm(ta, tb, torch.bfloat16)
+    o32, o16 = host(out32), host(out16)
+    assert np.array_equal(o16, gd.f32_to_bf16_bits(o32))
+    tile = o32[r0g:r0g + 128, c0g:c0g + 256]
+    assert max_rel_err(tile, g["out"]) <= DENSE_TOL
+    assert max_elem_rel_err(tile, g["out"]) <= DENSE_TOL
+    a_h, b_h = host(ta), host(tb)
+    for r0, c0 in ((0, 0), (2176, 2048)):
+        ref = oracle.gemm_f32acc(a_h[r0:r0 + 128], b_h[c0:c0 + 256], oracle.BF16)
+        assert max_rel_err(o32[r0:r0 + 128, c0:c0 + 256], ref) <= DENSE_TOL
+
+
+def test_call_kernel_fixed_shape_launcher():
+    """call_kernel(blockDim, stream, out, src0, src1): fp16 6144^3, B column-major, fp32 out, through the C ABI."""
+    from pto_isa_mirror_b200 import _capi
+
+    lib = _capi.load()
+    dim = 6144
+    gen = torch.Generator(device=DEV).manual_seed(6144)
+    ta = (torch.randn((dim, dim), generator=gen, device=DEV) / dim ** 0.5).to(torch.float16)
+    tb = (torch.randn((dim, dim), generator=gen, device=DEV) / dim ** 0.5).to(torch.float16)
+    out = torch.full((dim, dim), float("nan"), dtype=torch.float32, device=DEV)
+    before = lib.pto_b200_launch_count()
+    lib.call_kernel(24, torch.cuda.current_stream().cuda_stream, out.data_ptr(), ta.data_ptr(), tb.data_ptr())
+    assert lib.pto_b200_launch_count() == before + 1
+    o = host(out)
+    assert not np.isnan(o).any()
+    a_h, b_h = host(ta), host(tb)
+    for r0, c0 in sample_tiles(dim, dim, 2, 61):
+        ref = oracle.gemm_f32acc(a_h[r0:r0 + 128], b_h[c0:c0 + 256], oracle.F16)
+        assert max_rel_err(o[r0:r0 + 128, c0:c0 + 256], ref) <= DENSE_TOL
+
+
+@pytest.mark.parametrize("kind", ["bf16", "f32", "s32", "deq", "mx"])
+def test_pair_kernel_store_paths_agree(kind):
+    """The CTA-pair kernel sends finished tiles through shared memory and TMA stores when C is 16-byte aligned with a
+    16-byte pitch, and stores from registers otherwise. Both paths must write the same bits, ragged edges included,
+    and leave everything around C untouched."""
+    m, n, k = 2400, 2500, 256            # 10 x 10 tiles of 256 x 256 (ragged in both directions) on 74 pairs
+    fill = -768.0
+    if kind in ("bf16", "f32"):
+        a, b = gd.dense_inputs(m, n, k, "bf16", 71)
+        ta, tb = dev16(a, torch.bfloat16), dev16(b, torch.bfloat16)
+        odt = torch.bfloat16 if kind == "bf16" else torch.float32
+        run = lambda out: pto.gemm(ta, tb, out=out)  # noqa: E731
+    elif kind in ("s32", "deq"):
+        a, b, s_row, s_col = gd.s8_inputs(m, n, k, 72)
+        ta, tb, sr, sc = dev8(a), dev8(b), dev8(s_row), dev8(s_col)
+        odt = torch.int32 if kind == "s32" else torch.bfloat16
+        fill = -768
+        run = (lambda out: pto.gemm(ta, tb, out=out)) if kind == "s32" else (
+            lambda out: pto.gemm_s8_dequant(ta, tb, sr, sc, out=out))
+    else:
+        a, b, sfa, sfb = gd.mx_inputs(m, n, k, 73)
+        ta, tb, tsa, tsb = dev8(a), dev8(b), dev8(sfa), dev8(sfb)
+        odt = torch.bfloat16
+        run = lambda out: pto.gemm_mx(ta, tb, tsa, tsb, out=out)  # noqa: E731
+    results = []
+    for pitch in (n + 12, n + 5):        # n + 12: 16-byte multiple for 2- and 4-byte elements (TMA); n + 5: odd pitch
+        buf = torch.full((m + 2, pitch), fill, dtype=odt, device=DEV)
+        run(buf[1:m + 1, :n])
+        got = buf.cpu()
+        assert (got[0] == fill).all() and (got[m + 1] == fill).all() and (got[:, n:] == fill).all()
+        results.append(got[1:m + 1, :n].contiguous())
+    assert torch.equal(results[0].view(torch.uint8), results[1].view(torch.uint8))
+    if kind == "s32":
+        assert np.array_equal(results[0].numpy()[:128, :256], oracle.gemm_s8(a[:128], b[:256]))
+
+
+def test_bounded_wait_expires_and_reports():
+    """A wait that nothing satisfies gives up after the run-time limit: the kernel returns, the status word names the
+    wait, reading it clears it, and the device goes on working. The wait is pto_b200_ksplit_wait on flags that nobody
+    sets, with the limit lowered to about a millisecond; nothing traps and no kernel is left waiting."""
+    import ctypes
+
+    from pto_isa_mirror_b200 import _capi
+
+    lib = _capi.load()
+    flags = torch.zeros((4, 8), dtype=torch.int32, device=DEV)
+    torch.cuda.synchronize()
+    old = lib.pto_b200_set_wait_limit(2_000_000)
+    try:
+        rc = lib.pto_b200_ksplit_wait(torch.cuda.current_stream().cuda_stream, flags.data_ptr(), 2, 0, 2, 1)
+        assert rc == _capi.OK
+        st = ctypes.c_int(0)
+        assert lib.pto_b200_device_status(ctypes.byref(st)) == _capi.ETIMEOUT
+        assert st.value == 17                                   # ST_KSPLIT_DONE_TIMEOUT
+        assert lib.pto_b200_device_status(ctypes.byref(st)) == _capi.OK and st.value == 0
+    finally:
+        assert lib.pto_b200_set_wait_limit(old) == 2_000_000
+    a, b = gd.dense_inputs(256, 256, 256, "bf16", 43)
+    out = host(pto.gemm(dev16(a, torch.bfloat16), dev16(b, torch.bfloat16), torch.float32))
+    assert max_rel_err(out, oracle.gemm_f32acc(a, b, oracle.BF16)) <= DENSE_TOL
