@@ -771,7 +771,8 @@ def main():
         "timed_regions": {"n": len(region_ms), "steps_each": args.steps,
                           "ms_per_step_median": ms_per_step,
                           "ms_per_step_min": min(region_ms) / args.steps,
-                          "ms_per_step_max": max(region_ms) / args.steps},
+                          "ms_per_step_max": max(region_ms) / args.steps,
+                          "ms_per_step_each": [round(x / args.steps, 6) for x in region_ms]},
     }
     # sampled output tiles against the oracle, outside every timed region (all ranks take part in the gathers)
     try:
@@ -897,9 +898,11 @@ def main():
                 del a, b, out, step
                 torch.cuda.empty_cache()
                 ustep, uflops, _, _ = make_step(name, spec, dev, seed=1, world=1, rank=0)
-                ums = time_steps(ustep, args.steps, args.warmup, dev, 1) / args.steps
+                u_regions = [time_steps(ustep, args.steps, args.warmup if r == 0 else 1, dev, 1) / args.steps
+                             for r in range(max(1, args.regions))]
+                ums = sorted(u_regions)[len(u_regions) // 2]
                 line["unsplit_1gpu"] = {"tflops": uflops / (ums * 1e-3) / 1e12, "ms": ums, "steps": args.steps,
-                                        "warmup": args.warmup}
+                                        "warmup": args.warmup, "ms_each": [round(x, 6) for x in u_regions]}
                 # like for like: the same product unsplit on one GPU of this box over n times the n-GPU step
                 line["scaling_efficiency"] = ums / (world * ms_per_step)
             except Exception as e:  # noqa: BLE001

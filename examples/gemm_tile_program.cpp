@@ -1,13 +1,18 @@
-// gemm_tile_program.cpp - the reference's two GEMM tile programs written against include/pto/pto-inst.hpp and run
+// gemm_tile_program.cpp - the reference's GEMM tile programs written against include/pto/pto-inst.hpp and run
 // on a B200: (1) the CPU demo's TLOAD / TMOV / TMATMUL / TSTORE sequence (demos/cpu/gemm_demo/gemm_demo.cpp:83-121,
 // B row-major), (2) the gemm_performance K loop with TEXTRACT slices and TMATMUL / TMATMUL_ACC
 // (kernels/manual/a2a3/gemm_performance/gemm_performance_kernel.cpp:69-131, B column-major), (3) the fixed-signature
 // launcher, (4) the bias form of the K loop (TMATMUL_BIAS then TMATMUL_ACC, tests/cpu/st/testcase/tmatmul/
-// tmatmul_kernel.cpp:86-96) and (5) a one-row TGEMV_BIAS. Inputs are small integers so the fp32 results are exact;
-// the program checks them against a host loop and prints "tile programs ok".
+// tmatmul_kernel.cpp:86-96), (5) a one-row TGEMV_BIAS, (6) the int8 K loop stored with a per-column scaling tile
+// (TSTORE_FP) and with one pre-quant scalar plus ReLU (kernels/manual/a2a3/dispatch_mega_combine/op_kernel/utils/
+// pto_gmm_preload_async_fixpipe_quant.hpp:75-124), (7) the block-scaled K loop with MX_A_ND / MX_B_DN scale tensors
+// (kernels/manual/a5/matmul_mxfp8_performance/mxmatmul_performance_kernel.cpp:153-344) and (8) LaunchMxMatmul on e5m2
+// operands. Inputs are small integers so the fp32 results are exact; the program checks them against host loops and
+// prints "tile programs ok".
 //
 // Build (one line): g++ -std=c++17 -I include -I /usr/local/cuda/include examples/gemm_tile_program.cpp
 //   -L pto_isa_mirror_b200/lib -lpto_b200 -L /usr/local/cuda/lib64 -lcudart -o examples/gemm_tile_program
+#include <cmath>
 #include <cstdio>
 #include <cstring>
 #include <vector>
@@ -27,6 +32,26 @@ static uint16_t f32_to_f16_small_int(int v)
     while ((a >> (e + 1)) != 0) ++e;
     unsigned man = (a << (10 - e)) & 0x3FF;
     return sign | static_cast<uint16_t>((e + 15) << 10) | static_cast<uint16_t>(man);
+}
+
+static uint16_t f32_to_bf16_rne(float f)
+{
+    uint32_t u;
+    std::memcpy(&u, &f, 4);
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    return static_cast<uint16_t>(u >> 16);
+}
+
+// small integers |v| <= 4 as fp8: e4m3 (bias 7, 3 mantissa bits) and e5m2 (bias 15, 2 mantissa bits)
+static uint8_t int_to_e4m3(int v)
+{
+    static const uint8_t mag[5] = {0x00, 0x38, 0x40, 0x44, 0x48};
+    return static_cast<uint8_t>((v < 0 ? 0x80 : 0) | mag[v < 0 ? -v : v]);
+}
+static uint8_t int_to_e5m2(int v)
+{
+    static const uint8_t mag[5] = {0x00, 0x3C, 0x40, 0x42, 0x44};
+    return static_cast<uint8_t>((v < 0 ? 0x80 : 0) | mag[v < 0 ? -v : v]);
 }
 
 template <typename T>
@@ -193,6 +218,171 @@ int main()
             bad += n;
         }
         cudaFree(dBias);
+    }
+    { // (6) int8 K loop, stored through the fixpipe quant forms: per-column scaling tile, then one scalar with ReLU
+        std::vector<int8_t> a8(M * K), b8(N * K);
+        std::vector<int> acc(M * N, 0);
+        for (int i = 0; i < M * K; ++i) a8[i] = static_cast<int8_t>(ai[i] * 9);
+        for (int k = 0; k < K; ++k)
+            for (int j = 0; j < N; ++j) b8[j * K + k] = static_cast<int8_t>(bi[k * N + j] * 11);
+        for (int i = 0; i < M; ++i)
+            for (int k = 0; k < K; ++k)
+                for (int j = 0; j < N; ++j) acc[i * N + j] += static_cast<int>(a8[i * K + k]) * b8[j * K + k];
+        // scale words: fp32 bits in [31:0]; the vector form reads [31:13], so these values carry low mantissa bits
+        std::vector<uint64_t> words(N);
+        std::vector<float> col_scale(N);
+        for (int j = 0; j < N; ++j) {
+            const float sc = 0.001f * static_cast<float>(1 + j % 7) * (j % 5 == 0 ? -1.0f : 1.0f);
+            uint32_t bits;
+            std::memcpy(&bits, &sc, 4);
+            words[j] = bits;
+            bits &= 0xFFFFE000u;
+            std::memcpy(&col_scale[j], &bits, 4);
+        }
+        const float scalar = 0.00314159f;
+        uint32_t scalar_bits;
+        std::memcpy(&scalar_bits, &scalar, 4);
+        int8_t* dA8 = to_device(a8);
+        int8_t* dB8 = to_device(b8);
+        uint64_t* dWords = to_device(words);
+        uint16_t* dOut16 = nullptr;
+        cudaMalloc(&dOut16, M * N * sizeof(uint16_t));
+        using GlobalA = GlobalTensor<int8_t, TileShape2D<int8_t, M, baseK, Layout::ND>, BaseShape2D<int8_t, M, K, Layout::ND>>;
+        using GlobalB = GlobalTensor<int8_t, TileShape2D<int8_t, baseK, N, Layout::DN>, BaseShape2D<int8_t, K, N, Layout::DN>,
+                                     Layout::DN>;
+        using GlobalOut = GlobalTensor<bfloat16_t, Shape<1, 1, 1, M, N>, Stride<M * N, M * N, M * N, N, 1>>;
+        using GlobalScale = GlobalTensor<uint64_t, Shape<1, 1, 1, 1, N>, Stride<N, N, N, N, 1>>;
+        using ScaleMatTile = Tile<TileType::Mat, uint64_t, 1, N, BLayout::RowMajor, 1, N, SLayout::NoneBox>;
+        using ScalingTile = Tile<TileType::Scaling, uint64_t, 1, N, BLayout::RowMajor, 1, N, SLayout::NoneBox>;
+        using AccTile = TileAcc<int32_t, M, N, M, N>;
+        TileLeft<int8_t, M, baseK, M, baseK> aTile;
+        TileRight<int8_t, baseK, N, baseK, N> bTile;
+        AccTile cTile;
+        for (int kIter = 0; kIter < K / baseK; ++kIter) {
+            GlobalA gmA(dA8 + kIter * baseK);
+            GlobalB gmB(dB8 + kIter * baseK);
+            TLOAD(aTile, gmA);
+            TLOAD(bTile, gmB);
+            if (kIter == 0) {
+                TMATMUL(cTile, aTile, bTile);
+            } else {
+                TMATMUL_ACC(cTile, cTile, aTile, bTile);
+            }
+        }
+        ScaleMatTile scaleMat;
+        ScalingTile scalingTile;
+        GlobalScale scaleGlobal(dWords);
+        TLOAD(scaleMat, scaleGlobal);
+        TMOV(scalingTile, scaleMat);
+        GlobalOut outGlobal(reinterpret_cast<bfloat16_t*>(dOut16));
+        std::vector<uint16_t> out16(M * N);
+        TSTORE_FP<AccTile, GlobalOut, ScalingTile>(outGlobal, cTile, scalingTile);
+        cudaDeviceSynchronize();
+        cudaMemcpy(out16.data(), dOut16, out16.size() * 2, cudaMemcpyDeviceToHost);
+        int n6 = 0;
+        for (int i = 0; i < M; ++i)
+            for (int j = 0; j < N; ++j)
+                n6 += (out16[i * N + j] != f32_to_bf16_rne(static_cast<float>(acc[i * N + j]) * col_scale[j]));
+        std::printf("int8 program (TMATMUL/TMATMUL_ACC + TSTORE_FP per-column scale): %d mismatches\n", n6);
+        bad += n6;
+        TSTORE<AccTile, GlobalOut, AtomicType::AtomicNone, ReluPreMode::NormalRelu>(outGlobal, cTile,
+                                                                                   static_cast<uint64_t>(scalar_bits));
+        cudaDeviceSynchronize();
+        cudaMemcpy(out16.data(), dOut16, out16.size() * 2, cudaMemcpyDeviceToHost);
+        n6 = 0;
+        for (int i = 0; i < M * N; ++i) {
+            float r = static_cast<float>(acc[i]) * scalar;
+            r = r > 0.0f ? r : 0.0f;
+            n6 += (out16[i] != f32_to_bf16_rne(r));
+        }
+        std::printf("int8 program (TSTORE with a pre-quant scalar and ReLU): %d mismatches\n", n6);
+        bad += n6;
+        cudaFree(dA8);
+        cudaFree(dB8);
+        cudaFree(dWords);
+        cudaFree(dOut16);
+    }
+    { // (7) block-scaled K loop: e4m3 operands, e8m0 scales in MX_A_ND / MX_B_DN tensors; (8) LaunchMxMatmul on e5m2
+        constexpr int mxK = 128, KG = K / 32;
+        std::vector<uint8_t> a43(M * K), b43(N * K), a52(M * K), b52(N * K), sfa(M * KG), sfb(N * KG);
+        for (int i = 0; i < M * K; ++i) {
+            a43[i] = int_to_e4m3(ai[i]);
+            a52[i] = int_to_e5m2(ai[i]);
+        }
+        for (int k = 0; k < K; ++k)
+            for (int j = 0; j < N; ++j) {
+                b43[j * K + k] = int_to_e4m3(bi[k * N + j]);
+                b52[j * K + k] = int_to_e5m2(bi[k * N + j]);
+            }
+        for (int i = 0; i < M * KG; ++i) sfa[i] = static_cast<uint8_t>(127 + (i * 3) % 3);
+        for (int i = 0; i < N * KG; ++i) sfb[i] = static_cast<uint8_t>(126 + (i * 5) % 3);
+        std::vector<float> ref_mx(M * N, 0.f);
+        for (int i = 0; i < M; ++i)
+            for (int k = 0; k < K; ++k)
+                for (int j = 0; j < N; ++j) {
+                    const float sc = std::ldexp(1.0f, sfa[i * KG + k / 32] - 127) * std::ldexp(1.0f, sfb[j * KG + k / 32] - 127);
+                    ref_mx[i * N + j] += static_cast<float>(ai[i * K + k] * bi[k * N + j]) * sc;
+                }
+        auto* dA43 = reinterpret_cast<float8_e4m3_t*>(to_device(a43));
+        auto* dB43 = reinterpret_cast<float8_e4m3_t*>(to_device(b43));
+        auto* dSfa = reinterpret_cast<float8_e8m0_t*>(to_device(sfa));
+        auto* dSfb = reinterpret_cast<float8_e8m0_t*>(to_device(sfb));
+        using GlobalA = GlobalTensor<float8_e4m3_t, TileShape2D<float8_e4m3_t, M, mxK, Layout::ND>,
+                                     BaseShape2D<float8_e4m3_t, M, K, Layout::ND>, Layout::ND>;
+        using GlobalB = GlobalTensor<float8_e4m3_t, TileShape2D<float8_e4m3_t, mxK, N, Layout::DN>,
+                                     BaseShape2D<float8_e4m3_t, K, N, Layout::DN>, Layout::DN>;
+        using GlobalSA = GlobalTensor<float8_e8m0_t, TileShape2D<float8_e8m0_t, M, mxK / 32, Layout::MX_A_ND>,
+                                      BaseShape2D<float8_e8m0_t, M, KG, Layout::MX_A_ND>, Layout::MX_A_ND>;
+        using GlobalSB = GlobalTensor<float8_e8m0_t, TileShape2D<float8_e8m0_t, mxK / 32, N, Layout::MX_B_DN>,
+                                      BaseShape2D<float8_e8m0_t, KG, N, Layout::MX_B_DN>, Layout::MX_B_DN>;
+        using GlobalC = GlobalTensor<float, Shape<1, 1, 1, M, N>, Stride<M * N, M * N, M * N, N, 1>>;
+        TileLeft<float8_e4m3_t, M, mxK, M, mxK> aTile;
+        TileRight<float8_e4m3_t, mxK, N, mxK, N> bTile;
+        TileLeftScale<float8_e8m0_t, M, mxK / 32, M, mxK / 32> aScale;
+        TileRightScale<float8_e8m0_t, mxK / 32, N, mxK / 32, N> bScale;
+        TileAcc<float, M, N, M, N> cTile;
+        for (int kIter = 0; kIter < K / mxK; ++kIter) {
+            GlobalA gmA(dA43 + kIter * mxK);
+            GlobalB gmB(dB43 + kIter * mxK);
+            GlobalSA gmSA(dSfa + kIter * (mxK / 32));
+            GlobalSB gmSB(dSfb + kIter * (mxK / 32));
+            TLOAD(aTile, gmA);
+            TLOAD(aScale, gmSA);
+            TLOAD(bTile, gmB);
+            TLOAD(bScale, gmSB);
+            if (kIter == 0) {
+                TMATMUL_MX(cTile, aTile, aScale, bTile, bScale);
+            } else {
+                TMATMUL_MX(cTile, cTile, aTile, aScale, bTile, bScale);
+            }
+        }
+        GlobalC cGlobal(dC);
+        TSTORE(cGlobal, cTile);
+        ref.swap(ref_mx);
+        check("block-scaled program (TLOAD scales / TMATMUL_MX K loop / TSTORE)");
+        // (8) the six-argument launcher: e5m2 operands, bf16 result (the integers here stay exact in bf16 only when
+        // small, so compare after the same rounding)
+        uint8_t* dA52 = to_device(a52);
+        uint8_t* dB52 = to_device(b52);
+        uint16_t* dOut16 = nullptr;
+        cudaMalloc(&dOut16, M * N * sizeof(uint16_t));
+        LaunchMxMatmul(reinterpret_cast<uint8_t*>(dOut16), dA52, dB52, reinterpret_cast<uint8_t*>(dSfa),
+                       reinterpret_cast<uint8_t*>(dSfb), nullptr, {M, N, K});
+        cudaDeviceSynchronize();
+        std::vector<uint16_t> out16(M * N);
+        cudaMemcpy(out16.data(), dOut16, out16.size() * 2, cudaMemcpyDeviceToHost);
+        int n8 = 0;
+        for (int i = 0; i < M * N; ++i) n8 += (out16[i] != f32_to_bf16_rne(ref[i]));
+        std::printf("LaunchMxMatmul (e5m2, bf16 out): %d mismatches\n", n8);
+        bad += n8;
+        ref.swap(ref_mx);
+        cudaFree(dA43);
+        cudaFree(dB43);
+        cudaFree(dSfa);
+        cudaFree(dSfb);
+        cudaFree(dA52);
+        cudaFree(dB52);
+        cudaFree(dOut16);
     }
     int status = 0;
     pto_b200_device_status(&status);

@@ -46,18 +46,18 @@ inline void LaunchMxMatmul(uint8_t* out, uint8_t* src0, uint8_t* src1, uint8_t* 
 }
 
 // Per-rank GEMM of the GEMM + allreduce pipeline: src0 [m, k_per_rank] and src1 [n, k_per_rank] are this rank's
-// packed K slices, gemm_output [m, n] is fp16 as in the reference. queue_set, rank and launch_block_count belong to
-// the reference's device-side tile queue and core partition and are not used: completion is stream-ordered.
+// packed K slices, gemm_output [m, n] is fp16 as in the reference. launch_block_count caps the thread blocks (SMs) the
+// GEMM occupies, as it caps the cores in the reference (0 = all). queue_set and rank belong to the reference's
+// device-side tile queue and are not used: completion is stream-ordered.
 inline void launchGemmCompute(uint8_t* gemm_output, uint8_t* src0, uint8_t* src1, uint8_t* queue_set, int rank,
                               void* stream, int launch_block_count, uint32_t k_per_rank,
                               pto::b200::GemmShape shape = {5416, 1408, 6144}, int out_dtype = PTO_B200_F16)
 {
     (void)queue_set;
     (void)rank;
-    (void)launch_block_count;
     const int k = static_cast<int>(k_per_rank);
-    const int rc = pto_b200_gemm(stream, gemm_output, src0, src1, shape.m, shape.n, k, k, k, shape.n, PTO_B200_F16,
-                                 out_dtype, PTO_B200_B_DN);
+    const int rc = pto_b200_gemm_ex(stream, gemm_output, src0, src1, shape.m, shape.n, k, k, k, shape.n, PTO_B200_F16,
+                                    out_dtype, PTO_B200_B_DN, launch_block_count > 0 ? launch_block_count : 0);
     if (rc != PTO_B200_OK) {
         pto::b200::fail("launchGemmCompute", rc);
     }

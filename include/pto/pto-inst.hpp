@@ -103,6 +103,24 @@ inline void*& current_stream()
 }
 inline void set_stream(void* stream) { current_stream() = stream; }
 
+// Optional device scratch for tile programs whose TSTORE needs one (block-scaled chains: the re-tiled scale factors).
+// Without it a block-scaled chain uses the library's built-in array (pto_b200_gemm_mx_static); the bias form of a
+// block-scaled chain has no such variant and needs this workspace.
+struct Workspace {
+    uint8_t* ptr = nullptr;
+    size_t bytes = 0;
+};
+inline Workspace& current_workspace()
+{
+    thread_local Workspace w;
+    return w;
+}
+inline void set_workspace(void* ptr, size_t bytes)
+{
+    current_workspace().ptr = static_cast<uint8_t*>(ptr);
+    current_workspace().bytes = bytes;
+}
+
 // A bound tile: a rows x cols window of device memory with element strides.
 struct View {
     const uint8_t* ptr = nullptr;
@@ -404,14 +422,33 @@ PTO_INST RecordEvent TMATMUL_MX(TileRes& cMatrix, TileLeft_& aMatrix, TileLeftSc
     return {};
 }
 
+// The bias form (include/pto/common/pto_instr.hpp:918-942): one fp32 value per column joins the accumulator.
 template <AccPhase Phase = AccPhase::Unspecified, typename TileRes, typename TileLeft_, typename TileLeftScale_,
-          typename TileRight_, typename TileRightScale_>
+          typename TileRight_, typename TileRightScale_, typename TileBias_,
+          std::enable_if_t<TileBias_::Loc == TileType::Bias, int> = 0>
+PTO_INST RecordEvent TMATMUL_MX(TileRes& cMatrix, TileLeft_& aMatrix, TileLeftScale_& aScaleMatrix, TileRight_& bMatrix,
+                                TileRightScale_& bScaleMatrix, TileBias_& biasData)
+{
+    static_assert(std::is_same_v<typename TileBias_::DType, float> && TileBias_::Rows == 1,
+                  "[PTO][SA] TMatmulMX: the bias is one row of float");
+    TMATMUL_MX<Phase>(cMatrix, aMatrix, aScaleMatrix, bMatrix, bScaleMatrix);
+    if (!biasData.view.bound()) {
+        b200::fail("TMATMUL_MX: bias tile was never loaded", 0);
+    }
+    cMatrix.bias = biasData.view;
+    return {};
+}
+
+template <AccPhase Phase = AccPhase::Unspecified, typename TileRes, typename TileLeft_, typename TileLeftScale_,
+          typename TileRight_, typename TileRightScale_,
+          std::enable_if_t<TileRight_::Loc == TileType::Right, int> = 0>
 PTO_INST RecordEvent TMATMUL_MX(TileRes& cOutMatrix, TileRes& cInMatrix, TileLeft_& aMatrix, TileLeftScale_& aScaleMatrix,
                                 TileRight_& bMatrix, TileRightScale_& bScaleMatrix)
 {
     b200::check_mad_mx_valid<TileRes, TileLeft_, TileRight_>();
     if (&cOutMatrix != &cInMatrix) {
         cOutMatrix.products = cInMatrix.products;
+        cOutMatrix.bias = cInMatrix.bias;
     }
     cOutMatrix.products.push_back(b200::Product{aMatrix.view, bMatrix.view, aScaleMatrix.view, bScaleMatrix.view, true,
                                                 b200::dtype_of<typename TileLeft_::DType>::value,
@@ -432,75 +469,190 @@ inline bool b_continues(const View& prev, const View& next)
     return next.ptr == prev.ptr + prev.rows * prev.row_stride * prev.elem_size && next.cols == prev.cols &&
            next.row_stride == prev.row_stride && next.col_stride == prev.col_stride;
 }
-} // namespace b200
 
-// TSTORE of an accumulator tile: launches the GEMM for the pending product chain and stores cast(acc) to dst.
-template <typename GlobalData, typename TileAcc_>
-PTO_INST RecordEvent TSTORE(GlobalData& dst, TileAcc_& src)
+// The pre-quant part of a TSTORE: none, one scale word for the tile, or one word per column.
+struct StoreQuant {
+    bool on = false;
+    uint64_t scalar = 0;
+    const uint8_t* words = nullptr; // device memory, n 64-bit words
+    long long word_count = 0;
+    bool relu = false;
+};
+
+// Launch the GEMM of an accumulator tile's pending product chain and store into dst.
+template <typename TileAcc_, typename GlobalData>
+inline void store_chain(GlobalData& dst, TileAcc_& src, const StoreQuant& quant)
 {
     static_assert(TileAcc_::Loc == TileType::Acc, "[PTO][SA] this TSTORE form takes an accumulator tile");
     if (src.products.empty()) {
-        b200::fail("TSTORE: accumulator tile holds no TMATMUL result", 0);
-        return {};
+        fail("TSTORE: accumulator tile holds no TMATMUL result", 0);
+        return;
     }
-    const b200::Product& first = src.products.front();
-    b200::View a = first.a, b = first.b, sa = first.sa, sb = first.sb;
+    const Product& first = src.products.front();
+    View a = first.a, b = first.b, sa = first.sa, sb = first.sb;
     long long k_total = a.cols;
     for (size_t i = 1; i < src.products.size(); ++i) {
-        const b200::Product& prev = src.products[i - 1];
-        const b200::Product& cur = src.products[i];
-        if (cur.mx != first.mx || !b200::a_continues(prev.a, cur.a) || !b200::b_continues(prev.b, cur.b)) {
-            b200::fail("TSTORE: the TMATMUL_ACC chain is not a run of adjacent K slices; only such chains map to one GEMM", 0);
-            return {};
+        const Product& prev = src.products[i - 1];
+        const Product& cur = src.products[i];
+        if (cur.mx != first.mx || !a_continues(prev.a, cur.a) || !b_continues(prev.b, cur.b)) {
+            fail("TSTORE: the TMATMUL_ACC chain is not a run of adjacent K slices; only such chains map to one GEMM", 0);
+            return;
+        }
+        // block-scaled chains: the scale windows must continue the same way, one scale per 32 K elements, or the one
+        // GEMM over the whole K would read scales the program never named
+        if (first.mx && (!a_continues(prev.sa, cur.sa) || !b_continues(prev.sb, cur.sb) ||
+                         prev.sa.cols * MX_BLOCK_SIZE != prev.a.cols || prev.sb.rows * MX_BLOCK_SIZE != prev.b.rows)) {
+            fail("TSTORE: the scale tiles of the TMATMUL_MX chain are not adjacent K/32 slices of one scale tensor", 0);
+            return;
         }
         k_total += cur.a.cols;
     }
     if (!a.bound() || !b.bound() || a.col_stride != 1 || b.rows != a.cols) {
-        b200::fail("TSTORE: operand tiles are not bound to row-major A / K x N B regions", 0);
-        return {};
+        fail("TSTORE: operand tiles are not bound to row-major A / K x N B regions", 0);
+        return;
     }
     const int m = static_cast<int>(a.rows);
     const int n = static_cast<int>(b.cols);
+    if (dst.GetShape(3) < m || dst.GetShape(4) < n) {
+        fail("TSTORE: the destination tensor is smaller than the accumulator tile's m x n", 0);
+        return;
+    }
     // B: DN (element (k, n) at k + n * ld) -> col_stride = ld, row_stride = 1; ND -> row_stride = ld, col_stride = 1
     const bool b_dn = (b.row_stride == 1);
     const long long ldb = b_dn ? b.col_stride : b.row_stride;
     const long long ldc = dst.GetStride(3);
     if (dst.GetStride(4) != 1) {
-        b200::fail("TSTORE: destination must be row-major (ND)", 0);
-        return {};
+        fail("TSTORE: destination must be row-major (ND)", 0);
+        return;
     }
     using OutT = typename GlobalData::DType;
     uint8_t* out = reinterpret_cast<uint8_t*>(dst.data());
+    void* stream = current_stream();
+    const int k = static_cast<int>(k_total);
     int rc;
-    if (first.mx && src.bias.bound()) {
-        b200::fail("TSTORE: the bias form of TMATMUL_MX needs a workspace; call pto_b200_gemm_mx_bias", 0);
-        return {};
-    }
-    if (first.mx) {
-        rc = pto_b200_gemm_mx_static(b200::current_stream(), out, a.ptr, b.ptr, sa.ptr, sb.ptr, m, n,
-                                     static_cast<int>(k_total), a.row_stride, ldb, ldc, sa.row_stride,
-                                     sb.col_stride != 1 ? sb.col_stride : sb.row_stride, first.a_dtype, first.b_dtype,
-                                     b200::dtype_of<OutT>::value);
+    if (quant.on) {
+        if (first.mx || src.bias.bound() || !b_dn) {
+            fail("TSTORE: the pre-quant forms apply to TMATMUL / TMATMUL_ACC chains with a column-major B and no bias", 0);
+            return;
+        }
+        if (quant.words != nullptr && quant.word_count < n) {
+            fail("TSTORE: the scaling tile has fewer words than the accumulator has columns", 0);
+            return;
+        }
+        rc = pto_b200_gemm_quant(stream, out, a.ptr, b.ptr, m, n, k, a.row_stride, ldb, ldc, first.a_dtype,
+                                 dtype_of<OutT>::value, quant.scalar,
+                                 reinterpret_cast<const unsigned long long*>(quant.words), quant.relu ? 1 : 0);
+    } else if (first.mx) {
+        // scale tensors: A's is row-major [m, K/32] (MX_A_ND), B's holds the K/32 scales of a column contiguously
+        // (MX_B_DN: element (kg, n) at kg + n * ld), the layouts TLOAD binds for the reference's MX kernels
+        if (sa.col_stride != 1 || sb.row_stride != 1 || !b_dn) {
+            fail("TSTORE: TMATMUL_MX chains take MX_A_ND / MX_B_DN scale tensors and a column-major B", 0);
+            return;
+        }
+        const long long ld_sfa = sa.row_stride, ld_sfb = sb.col_stride;
+        const Workspace& ws = current_workspace();
+        if (src.bias.bound()) {
+            if (ws.ptr == nullptr) {
+                fail("TSTORE: the bias form of TMATMUL_MX needs scratch: call pto::b200::set_workspace first", 0);
+                return;
+            }
+            rc = pto_b200_gemm_mx_bias(stream, out, a.ptr, b.ptr, sa.ptr, sb.ptr, src.bias.ptr, ws.ptr, ws.bytes, m, n, k,
+                                       a.row_stride, ldb, ldc, ld_sfa, ld_sfb, first.a_dtype, first.b_dtype,
+                                       dtype_of<OutT>::value);
+        } else if (ws.ptr != nullptr) {
+            rc = pto_b200_gemm_mx(stream, out, a.ptr, b.ptr, sa.ptr, sb.ptr, ws.ptr, ws.bytes, m, n, k, a.row_stride, ldb,
+                                  ldc, ld_sfa, ld_sfb, first.a_dtype, first.b_dtype, dtype_of<OutT>::value);
+        } else {
+            rc = pto_b200_gemm_mx_static(stream, out, a.ptr, b.ptr, sa.ptr, sb.ptr, m, n, k, a.row_stride, ldb, ldc,
+                                         ld_sfa, ld_sfb, first.a_dtype, first.b_dtype, dtype_of<OutT>::value);
+        }
     } else {
         rc = PTO_B200_EALIGN;
         if (src.one_row && m == 1 && b_dn) {
-            rc = pto_b200_gemv(b200::current_stream(), out, a.ptr, b.ptr, src.bias.ptr, n, static_cast<int>(k_total), ldb,
-                               first.a_dtype, b200::dtype_of<OutT>::value);
+            rc = pto_b200_gemv(stream, out, a.ptr, b.ptr, src.bias.ptr, n, k, ldb, first.a_dtype, dtype_of<OutT>::value);
         }
         if (rc == PTO_B200_EALIGN && src.bias.bound()) { // not a one-row chain, or its row is not 16-byte aligned
-            rc = pto_b200_gemm_bias(b200::current_stream(), out, a.ptr, b.ptr, src.bias.ptr, m, n,
-                                    static_cast<int>(k_total), a.row_stride, ldb, ldc, first.a_dtype,
-                                    b200::dtype_of<OutT>::value, b_dn ? PTO_B200_B_DN : PTO_B200_B_ND);
+            rc = pto_b200_gemm_bias(stream, out, a.ptr, b.ptr, src.bias.ptr, m, n, k, a.row_stride, ldb, ldc, first.a_dtype,
+                                    dtype_of<OutT>::value, b_dn ? PTO_B200_B_DN : PTO_B200_B_ND);
         } else if (rc == PTO_B200_EALIGN) {
-            rc = pto_b200_gemm(b200::current_stream(), out, a.ptr, b.ptr, m, n, static_cast<int>(k_total), a.row_stride,
-                               ldb, ldc, first.a_dtype, b200::dtype_of<OutT>::value,
-                               b_dn ? PTO_B200_B_DN : PTO_B200_B_ND);
+            rc = pto_b200_gemm(stream, out, a.ptr, b.ptr, m, n, k, a.row_stride, ldb, ldc, first.a_dtype,
+                               dtype_of<OutT>::value, b_dn ? PTO_B200_B_DN : PTO_B200_B_ND);
         }
     }
     if (rc != PTO_B200_OK) {
-        b200::fail("TSTORE: launch rejected", rc);
+        fail("TSTORE: launch rejected", rc);
     }
+}
+
+// CheckStoreQuantValid: the pre-quant forms implemented here take int32 or float accumulators to half / bfloat16
+// (QS322BF16_PRE, VQS322BF16_PRE, DEQF16, VDEQF16, QF322BF16_PRE, VQF322BF16_PRE, QF322F16_PRE, VQF322F16_PRE of
+// include/pto/cpu/common.hpp:19-37); the int8 / int16 destinations are not built.
+template <typename TileData, typename GlobalData>
+constexpr void check_store_quant_valid()
+{
+    using S = typename TileData::DType;
+    using D = typename GlobalData::DType;
+    static_assert((std::is_same_v<S, int32_t> || std::is_same_v<S, float>) &&
+                      (std::is_same_v<D, half> || std::is_same_v<D, bfloat16_t>),
+                  "[PTO][SA] TSTORE pre-quant: int32 / float accumulators to half / bfloat16_t only");
+}
+} // namespace b200
+
+// TSTORE of an accumulator tile: launches the GEMM for the pending product chain and stores cast(acc) to dst
+// (include/pto/common/pto_instr.hpp:378-439). Template parameter order as in the reference: tile, tensor, atomic, relu.
+template <typename TileData, typename GlobalData, AtomicType atomicType = AtomicType::AtomicNone,
+          ReluPreMode reluPreMode = ReluPreMode::NoRelu>
+PTO_INST RecordEvent TSTORE(GlobalData& dst, TileData& src)
+{
+    static_assert(atomicType == AtomicType::AtomicNone && reluPreMode == ReluPreMode::NoRelu,
+                  "[PTO][SA] plain TSTORE: atomic add and ReLU are not built on this path");
+    b200::store_chain(dst, src, b200::StoreQuant{});
     return {};
+}
+
+// TSTORE(dst, acc, preQuantScalar) (pto_instr.hpp:441-462): one scale for the whole tile, the fp32 value in bits [31:0].
+template <typename TileData, typename GlobalData, AtomicType atomicType = AtomicType::AtomicNone,
+          ReluPreMode reluPreMode = ReluPreMode::NoRelu>
+PTO_INST RecordEvent TSTORE(GlobalData& dst, TileData& src, uint64_t preQuantScalar)
+{
+    static_assert(atomicType == AtomicType::AtomicNone, "[PTO][SA] TSTORE pre-quant: atomic add is not built");
+    b200::check_store_quant_valid<TileData, GlobalData>();
+    b200::StoreQuant q;
+    q.on = true;
+    q.scalar = preQuantScalar;
+    q.relu = (reluPreMode == ReluPreMode::NormalRelu);
+    b200::store_chain(dst, src, q);
+    return {};
+}
+
+// TSTORE(dst, acc, fpTile) (pto_instr.hpp:464-489): one 64-bit scale word per column in a TileType::Scaling tile that
+// was loaded (TLOAD, or TMOV from a Mat tile) from device memory; the scale is read from bits [31:13] of each word.
+template <typename TileData, typename GlobalData, typename FpTileData, AtomicType atomicType = AtomicType::AtomicNone,
+          ReluPreMode reluPreMode = ReluPreMode::NoRelu, std::enable_if_t<FpTileData::Loc == TileType::Scaling, int> = 0>
+PTO_INST RecordEvent TSTORE(GlobalData& dst, TileData& src, FpTileData& fp)
+{
+    static_assert(atomicType == AtomicType::AtomicNone, "[PTO][SA] TSTORE pre-quant: atomic add is not built");
+    static_assert(sizeof(typename FpTileData::DType) == 8, "[PTO][SA] the scaling tile holds 64-bit words");
+    b200::check_store_quant_valid<TileData, GlobalData>();
+    if (!fp.view.bound() || fp.view.col_stride != 1) {
+        b200::fail("TSTORE: the scaling tile was never loaded from a contiguous row of words", 0);
+        return {};
+    }
+    b200::StoreQuant q;
+    q.on = true;
+    q.words = fp.view.ptr;
+    q.word_count = fp.view.cols;
+    q.relu = (reluPreMode == ReluPreMode::NormalRelu);
+    b200::store_chain(dst, src, q);
+    return {};
+}
+
+// TSTORE_FP (pto_instr.hpp:491-518): the same store under its own name.
+template <typename TileData, typename GlobalData, typename FpTileData, AtomicType atomicType = AtomicType::AtomicNone,
+          ReluPreMode reluPreMode = ReluPreMode::NoRelu>
+PTO_INST RecordEvent TSTORE_FP(GlobalData& dst, TileData& src, FpTileData& fp)
+{
+    return TSTORE<TileData, GlobalData, FpTileData, atomicType, reluPreMode>(dst, src, fp);
 }
 
 } // namespace pto

@@ -122,6 +122,27 @@ int pto_b200_gemm_s8_dequant(void* stream, uint8_t* out, const uint8_t* src0, co
                              long long ldb, long long ldc);
 
 /*
+ * GEMM whose store applies a pre-quant scale word: out[i][j] = cast16( relu?( clamp( float(acc[i][j]) * scale_j ) ) ).
+ * Replaces: TMATMUL / TMATMUL_ACC followed by TSTORE(dst, acc, uint64_t preQuantScalar) (include/pto/common/
+ * pto_instr.hpp:441-462) or by TSTORE(dst, acc, fpTile) / TSTORE_FP (:464-518), with the mode the overloads pick
+ * (GetScalarPreQuantMode / GetVectorPreQuantMode, include/pto/cpu/common.hpp:58-108) and the arithmetic of
+ * quantize_element (:139-185); kernel usage kernels/manual/a2a3/dispatch_mega_combine/op_kernel/utils/
+ * pto_gmm_preload_async_fixpipe_quant.hpp:75-124.
+ *   in_dtype S8 (int32 accumulators: QS322BF16_PRE / VQS322BF16_PRE, DEQF16 / VDEQF16) or F16 / BF16 (fp32
+ *   accumulators: QF322BF16_PRE / VQF322BF16_PRE, QF322F16_PRE / VQF322F16_PRE); out_dtype BF16 or F16; B is PTO_B200_B_DN.
+ *   fp_words == NULL : scalar form, scale = the fp32 value in bits [31:0] of pre_quant_scalar for every column
+ *   fp_words != NULL : vector form, n 64-bit words in device memory (8-byte aligned), one per column; the scale is the
+ *                      19-bit float (sign, 8 exponent, 10 mantissa bits) in bits [31:13] of the word, i.e. fp32 with
+ *                      the low 13 mantissa bits ignored (extract_m1_from_quant, common.hpp:116-137)
+ *   relu != 0        : ReluPreMode::NormalRelu, applied after the scaling
+ * Half outputs are clamped to +-65504 as the reference does. The integer destinations (REQ8 / VREQ8, SHIFTS322S16) and
+ * the offset / sign fields of the word (bits 37-46) belong to them and are not implemented.
+ */
+int pto_b200_gemm_quant(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, int m, int n, int k,
+                        long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype,
+                        unsigned long long pre_quant_scalar, const unsigned long long* fp_words, int relu);
+
+/*
  * MX block-scaled fp8 GEMM: C[i][j] = sum_k A[i][k] * B[k][j] * 2^(SA[i][k/32]-127) * 2^(SB[j][k/32]-127).
  * Replaces: RunMxMatmul / LaunchMxMatmul (uint8_t* out, src0, src1, src2, src3, void* stream),
  * kernels/manual/a5/matmul_mxfp8_performance/mxmatmul_performance_kernel.cpp:284-380; arithmetic

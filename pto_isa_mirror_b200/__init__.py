@@ -1,7 +1,8 @@
 """B200 (sm_100a) implementation of the PTO tile library's GEMM hot path.
 
 Host-side mirror of the reference's GEMM entry points over the C ABI in ``include/pto_b200.h``:
-``gemm`` (TLOAD -> TMATMUL/TMATMUL_ACC -> TSTORE), ``gemm_s8_dequant`` (int8 + fixpipe dequant),
+``gemm`` (TLOAD -> TMATMUL/TMATMUL_ACC -> TSTORE), ``gemm_s8_dequant`` (int8 + fixpipe dequant), ``gemm_quant``
+(TSTORE with a pre-quant scale word / TSTORE_FP),
 ``gemm_mx`` (TMATMUL_MX, e8m0 block scales), ``gemv`` (TGEMV), ``mx_quantize_e4m3`` (TQUANT, MXFP8),
 ``pto_gemm_basic`` (the torch op of demos/baseline/gemm_basic)
 and the K-split GEMM + allreduce (``ksplit``). PyTorch is used for device memory, streams and
@@ -15,6 +16,7 @@ from .gemm import (
     gemm,
     gemm_mx,
     gemm_mx_workspace_bytes,
+    gemm_quant,
     gemm_s8_dequant,
     gemv,
     launch_count,
@@ -23,7 +25,7 @@ from .gemm import (
 )
 
 __all__ = [
-    "gemm", "gemm_s8_dequant", "gemm_mx", "gemm_mx_workspace_bytes", "gemv", "mx_quantize_e4m3", "cast_f32_to_bf16",
+    "gemm", "gemm_s8_dequant", "gemm_quant", "gemm_mx", "gemm_mx_workspace_bytes", "gemv", "mx_quantize_e4m3", "cast_f32_to_bf16",
     "pto_gemm_basic",
     "device_status", "launch_count", "PtoB200Error",
     "F16", "BF16", "F32", "S8", "S32", "E4M3", "E5M2", "B_DN", "B_ND",

@@ -35,6 +35,10 @@ SYMBOLS = {
         _i,
         [ctypes.c_void_p, _u8p, _u8p, _u8p, _u8p, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i],
     ),
+    "pto_b200_gemm_quant": (
+        _i,
+        [ctypes.c_void_p, _u8p, _u8p, _u8p, _i, _i, _i, _ll, _ll, _ll, _i, _i, ctypes.c_ulonglong, ctypes.c_void_p, _i],
+    ),
     "pto_b200_gemm_s8_dequant": (
         _i,
         [ctypes.c_void_p, _u8p, _u8p, _u8p, ctypes.c_void_p, ctypes.c_void_p, _i, _i, _i, _ll, _ll, _ll],

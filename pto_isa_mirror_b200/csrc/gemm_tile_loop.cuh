@@ -32,8 +32,14 @@ enum EpilogueMode : int {
     EPI_BF16 = 1,    // static_cast<bfloat16>(fp32), round to nearest even
     EPI_F16 = 2,     // static_cast<half>(fp32), round to nearest even
     EPI_S32 = 3,     // store the int32 accumulator
-    EPI_DEQ_BF16 = 4 // bf16((float(acc) * s_col[j]) * s_row[i])
+    EPI_DEQ_BF16 = 4, // bf16((float(acc) * s_col[j]) * s_row[i])
+    EPI_QUANT16 = 5   // TSTORE with a pre-quant scale word: cast16(relu?(clamp(float(acc) * scale_j))), see QuantFlags
 };
+
+// EPI_QUANT16 variants (GemmParams::quant_flags): the accumulator type, the 16-bit destination, ReLU, and whether the
+// scale is one word for the tile (TSTORE(dst, acc, preQuantScalar): fp32 in bits [31:0]) or one word per column
+// (TSTORE(dst, acc, fpTile) / TSTORE_FP: the 19-bit (1,8,10) float in bits [31:13]); include/pto/cpu/common.hpp:116-185.
+enum QuantFlags : int { QUANT_ACC_S32 = 1, QUANT_OUT_F16 = 2, QUANT_RELU = 4, QUANT_VECTOR = 8 };
 
 struct GemmParams {
     void* c;
@@ -53,6 +59,9 @@ struct GemmParams {
     int tail_tiles;      // leftover tiles that are split (0 = none)
     uint32_t* ws_partial; // [tail_tiles][256][256] 32-bit accumulators
     int* ws_flags;        // [2 * tail_tiles]: arrivals of the first halves' store warps, departures of the readers
+    const unsigned long long* quant_words; // EPI_QUANT16, vector form: n scale words in device memory
+    unsigned long long quant_word;         // EPI_QUANT16, scalar form: the scale word
+    int quant_flags;                       // EPI_QUANT16: QuantFlags
     long long wait_limit; // cycles one bounded wait may take before the kernel gives up (kWaitLimitCycles by default)
     int tma_store;        // CTA-pair kernels: C is 16-byte aligned with a 16-byte row pitch, so finished tiles leave
                           // through shared memory and TMA stores; 0 = per-thread global stores
@@ -168,7 +177,43 @@ __device__ __forceinline__ void convert_chunk(const uint32_t (&v)[32], const Gem
         }
     } else {
         float f[32];
-        if constexpr (EPI == EPI_DEQ_BF16) {
+        if constexpr (EPI == EPI_QUANT16) {
+            // quantize_element (include/pto/cpu/common.hpp:139-185): float(acc) * scale, the half forms clamp to
+            // +-65504 (always for int32 accumulators, finite values only for float ones), ReLU after the scaling.
+            const bool acc_int = (p.quant_flags & QUANT_ACC_S32) != 0;
+            const bool out_f16 = (p.quant_flags & QUANT_OUT_F16) != 0;
+            const bool relu = (p.quant_flags & QUANT_RELU) != 0;
+            const bool vector = (p.quant_flags & QUANT_VECTOR) != 0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                float scale;
+                if (vector) {
+                    const uint32_t lo = (i < n_left) ? static_cast<uint32_t>(__ldg(p.quant_words + col0 + i)) : 0u;
+                    // sign, 8 exponent and 10 mantissa bits from [31:13]: fp32 with the low 13 mantissa bits dropped;
+                    // a zero exponent field with a non-zero mantissa reads as (1 + m / 1024) * 2^-127 in the reference
+                    const uint32_t e = (lo >> 23) & 0xFFu;
+                    const uint32_t mnt = (lo >> 13) & 0x3FFu;
+                    if (e != 0u || mnt == 0u) {
+                        scale = __uint_as_float(e != 0u ? (lo & 0xFFFFE000u) : 0u);
+                    } else {
+                        const float mag = __fmul_rn(1.0f + static_cast<float>(mnt) * (1.0f / 1024.0f),
+                                                    __uint_as_float(0x00400000u)); // 2^-127
+                        scale = (lo >> 31) ? -mag : mag;
+                    }
+                } else {
+                    scale = __uint_as_float(static_cast<uint32_t>(p.quant_word));
+                }
+                const float src = acc_int ? __int2float_rn(static_cast<int>(w[i])) : __uint_as_float(w[i]);
+                float r = __fmul_rn(src, scale);
+                if (out_f16 && (acc_int || isfinite(r))) {
+                    r = fminf(fmaxf(r, -65504.0f), 65504.0f);
+                }
+                if (relu) {
+                    r = (r > 0.0f) ? r : 0.0f;
+                }
+                f[i] = r;
+            }
+        } else if constexpr (EPI == EPI_DEQ_BF16) {
             // Fixpipe per-column dequant, then the per-row (per-token) scale, two separately rounded
             // fp32 multiplies: quantize_element (include/pto/cpu/common.hpp:139-185) followed by
             // the row-scale multiply of the vector stage.
@@ -184,7 +229,11 @@ __device__ __forceinline__ void convert_chunk(const uint32_t (&v)[32], const Gem
                 f[i] = __uint_as_float(w[i]);
             }
         }
-        if constexpr (EPI == EPI_F16) {
+        bool to_half = (EPI == EPI_F16);
+        if constexpr (EPI == EPI_QUANT16) {
+            to_half = (p.quant_flags & QUANT_OUT_F16) != 0;
+        }
+        if (to_half) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);

@@ -537,6 +537,73 @@ extern "C" int pto_b200_gemm_bias(void* stream, uint8_t* out, const uint8_t* src
                            0, bias);
 }
 
+extern "C" int pto_b200_gemm_quant(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, int m, int n,
+                                   int k, long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype,
+                                   unsigned long long pre_quant_scalar, const unsigned long long* fp_words, int relu)
+{
+    const bool is16 = (in_dtype == PTO_B200_F16 || in_dtype == PTO_B200_BF16);
+    const bool is8 = (in_dtype == PTO_B200_S8);
+    if ((!is16 && !is8) || !(out_dtype == PTO_B200_BF16 || out_dtype == PTO_B200_F16)) {
+        return PTO_B200_EDTYPE;
+    }
+    if (fp_words != nullptr && (reinterpret_cast<uintptr_t>(fp_words) & 7u)) {
+        return PTO_B200_EALIGN;
+    }
+    const Problem q{m, n, k, lda, ldb, ldc};
+    const int es = elem_size(in_dtype);
+    if (int rc = check_common(out, src0, src1, q, es, es, false)) {
+        return rc;
+    }
+    DeviceInfo* dev = nullptr;
+    if (int rc = device_info(&dev)) {
+        return rc;
+    }
+    const int block_n = pick_block_n(m, n, dev->sm_count);
+    const int kelems = kBlockKBytes / es;
+    GemmParams p;
+    fill_params(p, out, q, block_n, kelems, dev->status_ptr);
+    p.quant_word = pre_quant_scalar;
+    p.quant_words = fp_words;
+    p.quant_flags = (is8 ? QUANT_ACC_S32 : 0) | (out_dtype == PTO_B200_F16 ? QUANT_OUT_F16 : 0) |
+                    (relu ? QUANT_RELU : 0) | (fp_words != nullptr ? QUANT_VECTOR : 0);
+    CUtensorMap ta, tb;
+    if (int rc = make_tensor_map(&ta, in_dtype, src0, m, k, lda, kelems, kBlockM)) {
+        return rc;
+    }
+    if (int rc = make_tensor_map(&tb, in_dtype, src1, n, k, ldb, kelems, block_n)) {
+        return rc;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int fmt = (in_dtype == PTO_B200_BF16) ? 1 : 0;
+    if (!dev->force_1cta && m > kBlockM) {
+        CUtensorMap tb_half;
+        if (int rc = make_tensor_map(&tb_half, in_dtype, src1, n, k, ldb, kelems, kPairBlockN / 2)) {
+            return rc;
+        }
+        GemmParams pp = p;
+        PairLaunch o;
+        o.out_dtype = out_dtype;
+        o.no_tma_store = dev->no_tma_store;
+        int rc;
+        if (is8) {
+            pp.idesc = make_idesc(2, 1, 1, false, kPairBlockN, false, kPairBlockM);
+            rc = launch_pair<KIND_I8, EPI_QUANT16>(s, ta, tb_half, pp, q, o);
+        } else {
+            pp.idesc = make_idesc(1, fmt, fmt, false, kPairBlockN, false, kPairBlockM);
+            rc = launch_pair<KIND_F16, EPI_QUANT16>(s, ta, tb_half, pp, q, o);
+        }
+        if (rc != -1) {
+            return rc;
+        }
+    }
+    if (is8) {
+        p.idesc = make_idesc(2, 1, 1, false, block_n, false);
+        return launch_block_n<KIND_I8, EPI_QUANT16, false>(block_n, s, ta, tb, p, dev->sm_count);
+    }
+    p.idesc = make_idesc(1, fmt, fmt, false, block_n, false);
+    return launch_block_n<KIND_F16, EPI_QUANT16, false>(block_n, s, ta, tb, p, dev->sm_count);
+}
+
 extern "C" int pto_b200_gemm_s8_dequant(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1,
                                         const float* s_row, const float* s_col, int m, int n, int k, long long lda,
                                         long long ldb, long long ldc)

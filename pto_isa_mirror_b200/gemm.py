@@ -139,6 +139,39 @@ def gemm_s8_dequant(a: torch.Tensor, b_dn: torch.Tensor, s_row: torch.Tensor, s_
     return out
 
 
+def gemm_quant(a: torch.Tensor, b_dn: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+               pre_quant_scalar: int = 0, fp_words: Optional[torch.Tensor] = None, relu: bool = False,
+               out: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """GEMM with the pre-quant store: TSTORE(dst, acc, preQuantScalar) when ``fp_words`` is None (the scale is the
+    float32 value in the low 32 bits of ``pre_quant_scalar``), TSTORE(dst, acc, fpTile) / TSTORE_FP when ``fp_words`` is a
+    CUDA tensor of n 64-bit words (int64 / uint64), one per column, whose bits [31:13] hold the scale. a, b_dn: int8
+    (int32 accumulators) or float16 / bfloat16 (float32 accumulators); the result is bfloat16 or float16."""
+    lib = _capi.load()
+    _require_cuda_2d(a, "a")
+    _require_cuda_2d(b_dn, "b_dn")
+    if a.dtype != b_dn.dtype or a.dtype not in (torch.float16, torch.bfloat16, torch.int8):
+        raise ValueError("a and b_dn must both be float16, bfloat16 or int8")
+    m, k = a.shape
+    n, kb = b_dn.shape
+    if kb != k:
+        raise ValueError("inner dimensions differ")
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    elif tuple(out.shape) != (m, n) or out.dtype not in (torch.bfloat16, torch.float16):
+        raise ValueError("out must be [m, n] bfloat16 or float16")
+    words_ptr = None
+    if fp_words is not None:
+        if not fp_words.is_cuda or fp_words.element_size() != 8 or fp_words.numel() != n or not fp_words.is_contiguous():
+            raise ValueError(f"fp_words must be a contiguous CUDA tensor of {n} 64-bit words")
+        words_ptr = fp_words.data_ptr()
+    rc = lib.pto_b200_gemm_quant(_stream_ptr(stream), out.data_ptr(), a.data_ptr(), b_dn.data_ptr(), m, n, k,
+                                 a.stride(0), b_dn.stride(0), out.stride(0), _TORCH_TO_PTO[a.dtype],
+                                 _TORCH_TO_PTO[out.dtype], int(pre_quant_scalar) & 0xFFFFFFFFFFFFFFFF, words_ptr,
+                                 int(bool(relu)))
+    _capi.check(rc, "pto_b200_gemm_quant")
+    return out
+
+
 def gemm_mx_workspace_bytes(m: int, n: int, k: int) -> int:
     return int(_capi.load().pto_b200_gemm_mx_workspace_bytes(m, n, k))
 

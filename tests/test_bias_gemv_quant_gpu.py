@@ -221,3 +221,64 @@ def test_quantise_then_multiply_matches_the_oracle_pipeline():
     rb, rsb = oracle.mx_quantize_e4m3(xb)
     assert np.array_equal(host(a), ra) and np.array_equal(host(sfb), rsb)
     assert max_rel_err(out, oracle.gemm_mx(ra, rb, rsa, rsb)) <= MX_TOL
+
+
+# ------------------------------------------------------------------ TSTORE with a pre-quant scale word / TSTORE_FP
+
+def words_dev(words):
+    return torch.from_numpy(np.ascontiguousarray(words).view(np.int64)).to(DEV)
+
+
+QUANT_GOLDEN = [("s32_scalar_bf16", False, False, torch.bfloat16), ("s32_vector_bf16", True, False, torch.bfloat16),
+                ("s32_vector_bf16_relu", True, True, torch.bfloat16), ("s32_scalar_f16", False, False, torch.float16),
+                ("s32_vector_f16_relu", True, True, torch.float16)]
+
+
+@pytest.mark.parametrize("name,vector,relu,odt", QUANT_GOLDEN)
+def test_quant_store_int8_golden_bit_exact(name, vector, relu, odt):
+    """The int8 tile of configuration 3 stored through TSTORE(dst, acc, preQuantScalar) and TSTORE_FP: the simulator's
+    own outputs (tests/golden/quant_store.npz), bit for bit."""
+    g = golden("quant_store")
+    a, b, _, _ = gd.s8_inputs(128, 256, 1024, 2)
+    scalar = int(g["scalar_word"][0])
+    out = pto.gemm_quant(dev(a), dev(b), odt, pre_quant_scalar=scalar,
+                         fp_words=words_dev(g["vector_words"]) if vector else None, relu=relu)
+    assert np.array_equal(host(out), g[name])
+
+
+@pytest.mark.parametrize("kind", ["s8", "f16", "bf16"])
+def test_quant_store_on_the_pair_kernel(kind):
+    """Every pre-quant form on a problem that takes the CTA-pair kernel (ragged 2300 x 2328, store boxes and register
+    stores), against the oracle's store applied to the GPU's own accumulators: bit-exact."""
+    m, n, k = 2300, 2328, 256
+    if kind == "s8":
+        a, b, _, _ = gd.s8_inputs(m, n, k, 81)
+        ta, tb = dev(a), dev(b)
+        acc = host(pto.gemm(ta, tb, torch.int32))
+        scalar = np.array([np.float32(0.0123)]).view(np.uint32).astype(np.uint64)
+    else:
+        a, b = gd.dense_inputs(m, n, k, kind, 82)
+        dt = torch.float16 if kind == "f16" else torch.bfloat16
+        ta, tb = dev16(a, dt), dev16(b, dt)
+        acc = host(pto.gemm(ta, tb, torch.float32))
+        scalar = np.array([np.float32(700000.0)]).view(np.uint32).astype(np.uint64)  # half outputs reach the clamp
+    col = gd.uniform((n,), 0.5, 2.0, 83, 0) * (np.float32(0.01) if kind == "s8" else np.float32(600000.0))
+    col[3] = -col[3]
+    col[5] = 0.0
+    words = col.view(np.uint32).astype(np.uint64)
+    for vector in (False, True):
+        for relu in (False, True):
+            for odt, f16 in ((torch.bfloat16, False), (torch.float16, True)):
+                out = pto.gemm_quant(ta, tb, odt, pre_quant_scalar=int(scalar[0]),
+                                     fp_words=words_dev(words) if vector else None, relu=relu)
+                want = oracle.quant_store(acc, words if vector else scalar, vector, relu, f16)
+                assert np.array_equal(host(out), want), (kind, vector, relu, f16)
+
+
+def test_quant_store_rejects_bad_arguments():
+    a = torch.zeros((128, 64), dtype=torch.int8, device=DEV)
+    with pytest.raises(pto.PtoB200Error) as e:
+        pto.gemm_quant(a, a, torch.float32)                    # only 16-bit destinations
+    assert e.value.code == 3
+    with pytest.raises(ValueError):
+        pto.gemm_quant(a, a, torch.bfloat16, fp_words=torch.zeros(5, dtype=torch.int64, device=DEV))

@@ -84,6 +84,31 @@ def test_argument_errors_come_before_any_launch(lib):
     assert q(None, p, p, p, 4, 64, 64, 64, 1) == _capi.EINVAL                                   # ld_scales < k / 32
     assert q(None, p, p, p + 4, 4, 64, 64, 64, 2) == _capi.EALIGN                               # src not 16-byte aligned
     assert q(None, p, p, p, 4, 64, 66, 64, 2) == _capi.EALIGN                                   # ld_src % 4
+    # the workspace-free MX entry reports argument errors like pto_b200_gemm_mx, before it needs a device
+    mxs = lib.pto_b200_gemm_mx_static
+    assert mxs(None, p, p, p, p, p, 16, 16, 48, 48, 48, 16, 2, 2, E4M3, E4M3, BF16) == _capi.EINVAL           # k % 32
+    assert mxs(None, p, p, p, p, p, 16, 16, 64, 64, 64, 16, 2, 2, S8, E4M3, BF16) == _capi.EDTYPE
+    assert mxs(None, p, p, p, p, None, 16, 16, 64, 64, 64, 16, 2, 2, E4M3, E4M3, BF16) == _capi.EINVAL        # no B scales
+    assert mxs(None, p, p + 2, p, p, p, 16, 16, 64, 64, 64, 16, 2, 2, E4M3, E4M3, BF16) == _capi.EALIGN
+    assert mxs(None, p, p, p, p, p, 32768, 8192, 8192, 8192, 8192, 8192, 256, 256, E4M3, E4M3, BF16) == _capi.ESCRATCH
+    # pre-quant store forms
+    gq = lib.pto_b200_gemm_quant
+    assert gq(None, p, p, p, 16, 16, 16, 16, 16, 16, S8, F32, 0, None, 0) == _capi.EDTYPE         # 16-bit destinations only
+    assert gq(None, p, p, p, 16, 16, 16, 16, 16, 16, F32, BF16, 0, None, 0) == _capi.EDTYPE
+    assert gq(None, p, p, p, 16, 16, 16, 16, 16, 16, S8, BF16, 0, p + 4, 0) == _capi.EALIGN       # words not 8-byte aligned
+    assert gq(None, None, p, p, 16, 16, 16, 16, 16, 16, S8, BF16, 0, None, 0) == _capi.EINVAL
+    # one-kernel K-split step
+    PA = ctypes.c_void_p * 2
+    two = PA(p, p)
+    ks = lib.pto_b200_ksplit_gemm_allreduce
+    common = (two, two, two, two, p, p)
+    assert ks(None, p, p, 256, 256, 64, 64, 64, BF16, *common, 9, 0, 0, 1, 256, 256, 256, None, None, 0) == _capi.EINVAL  # 9 ranks
+    assert ks(None, p, p, 256, 256, 64, 64, 64, BF16, *common, 2, 0, 0, 0, 256, 256, 256, None, None, 0) == _capi.EINVAL  # epoch 0
+    assert ks(None, p, p, 256, 256, 64, 64, 64, BF16, *common, 2, 0, 0, 1, 100, 256, 256, None, None, 0) == _capi.EINVAL  # panel rows
+    assert ks(None, p, p, 256, 256, 64, 64, 64, S8, *common, 2, 0, 0, 1, 256, 256, 256, None, None, 0) == _capi.EDTYPE
+    assert ks(None, p, p, 256, 256, 64, 64, 64, BF16, PA(p, None), two, two, two, p, p, 2, 0, 0, 1, 256, 256, 256, None, None,
+              0) == _capi.EINVAL                                                                   # a rank's buffer missing
+    assert ks(None, p, p, 256, 250, 64, 64, 64, BF16, *common, 2, 0, 0, 1, 256, 250, 250, None, None, 0) == _capi.EALIGN  # n % 4
     assert lib.pto_b200_cast_f32_to_bf16(None, None, p, 4) == _capi.EINVAL
     assert lib.pto_b200_cast_f32_to_bf16(None, p, p, 0) == _capi.OK
     assert lib.pto_b200_launch_count() == before
@@ -103,3 +128,10 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_capi, "LIB_PATH", str(tmp_path / "libpto_b200.so"))
     with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):
         _capi.load()
+
+
+def test_wait_limit_setter_round_trips(lib):
+    default = lib.pto_b200_set_wait_limit(123456)
+    assert default == 4_000_000_000
+    assert lib.pto_b200_set_wait_limit(0) == 123456          # 0 restores the default
+    assert lib.pto_b200_set_wait_limit(default) == default

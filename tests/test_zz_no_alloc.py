@@ -3,9 +3,9 @@
 Some users of the library cannot hand over a scratch buffer and cannot allocate one when they call: a launcher
 that keeps the reference's six-argument LaunchMxMatmul shape, or a process that gave its whole device memory
 to its own pool at start-up. For them the re-tiled scale factors live in an array built into the library. This
-test runs the new entry point twice in a row, the second time on a smaller, different problem, so that bytes left
-in the shared array by the first call would show up as wrong results if any of them were read, and checks both
-results bit for bit against pto_b200_gemm_mx given a fresh workspace. It also checks that a problem larger than the
+test runs the new entry point three times in a row on different problems (the second large enough for the two-CTA
+kernel), so that bytes left in the shared array by an earlier call would show up as wrong results if any were
+read, and checks every result bit for bit against pto_b200_gemm_mx given a fresh workspace. It also checks that a problem larger than the
 built-in array is refused before anything is launched.
 
 This file sorts last on purpose: a run that stops at the first failure has then already run every other test.
@@ -46,16 +46,21 @@ def _call_pair(lib, m, n, k, seed):
     return out.cpu().numpy(), ref.cpu().numpy()
 
 
-def test_static_scratch_matches_workspace_variant_twice_in_a_row():
+def test_static_scratch_matches_workspace_variant_on_calls_in_a_row():
     lib = _capi.load()
     # first call: several tiles in M, N and K, ragged in every dimension
     out1, ref1 = _call_pair(lib, 640, 1000, 1056, seed=51)
     assert not np.isnan(ref1).any()
     assert np.array_equal(out1.view(np.uint32), ref1.view(np.uint32))
-    # second call, straight after: smaller and different, over the first call's leftovers in the shared array
-    out2, ref2 = _call_pair(lib, 130, 260, 160, seed=52)
+    # second call, straight after, over the first call's leftovers in the shared array: 100 tiles of 256 x 256, so
+    # the two-CTA kernel runs, whose scale loads go through tensor maps encoded over the array's device address
+    out2, ref2 = _call_pair(lib, 2560, 2560, 512, seed=53)
     assert not np.isnan(ref2).any()
     assert np.array_equal(out2.view(np.uint32), ref2.view(np.uint32))
+    # third call: smaller and different again, back on the one-CTA kernel
+    out3, ref3 = _call_pair(lib, 130, 260, 160, seed=52)
+    assert not np.isnan(ref3).any()
+    assert np.array_equal(out3.view(np.uint32), ref3.view(np.uint32))
     st = ctypes.c_int(0)
     assert lib.pto_b200_device_status(ctypes.byref(st)) == _capi.OK and st.value == 0
 
