@@ -51,6 +51,9 @@ WORKLOADS = {
     "s8_8192_dequant": dict(kind="s8", m=8192, n=8192, k=8192),
     "mxfp8_16384x8192x8192": dict(kind="mx", m=16384, n=8192, k=8192),
     "ksplit_bf16_8192x65536x8192": dict(kind="ksplit", m=8192, n=8192, k=65536),
+    # the largest shape of the reference's AllGather + GEMM table (kernels/manual/a2a3/allgather_gemm/README.md:112-125):
+    # A split along M over the ranks, B replicated, every rank computes the whole C; run with --workload at any N
+    "allgather_bf16_8192x4096x4096": dict(kind="allgather", m=8192, n=4096, k=4096),
 }
 
 
@@ -430,6 +433,59 @@ def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=8, 
         step.reduce_used = reduce_used
         step.tensors = (a, b, out)
         return step, flops, (m + n) * kr * 2 + m * n * 6, 1
+    if kind == "allgather":
+        import torch.distributed as dist
+
+        from pto_isa_mirror_b200.allgather import AllGatherGemm
+
+        op = AllGatherGemm(m, n, k, torch.bfloat16, torch.float32, device=dev, use_multicast=use_multicast,
+                           launch_block_count=gemm_blocks)
+        gen.manual_seed(seed * 1000 + rank)
+        op.a_local().copy_(_randn_scaled((m // world, k), k, torch.bfloat16, gen, dev))
+        gen.manual_seed(seed * 1000 + 999)                 # B is the same on every rank
+        b = _randn_scaled((n, k), k, torch.bfloat16, gen, dev)
+
+        def step(i):
+            op.step(b)
+
+        def parity():
+            import oracle
+
+            step(0)
+            torch.cuda.synchronize(dev)
+            rows_per_rank = m // world
+            acc, refs, identical, received = [], [], True, True
+            for r0, c0 in _tile_origins(m, n, 2, 105):
+                owner = r0 // rows_per_rank
+                rows = op.a_full[r0:r0 + 128].clone()          # this rank's copy: pushed here by the owner
+                sent = rows.clone()
+                if world > 1:
+                    dist.broadcast(sent, src=owner)            # the owner's original rows
+                ok = torch.tensor([int(torch.equal(rows.view(torch.int16), sent.view(torch.int16)))], device=dev)
+                tile = op.out[r0:r0 + 128, c0:c0 + 256].contiguous()
+                tiles = [tile]
+                if world > 1:
+                    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+                    tiles = [torch.empty_like(tile) for _ in range(world)]
+                    dist.all_gather(tiles, tile)
+                received = received and bool(ok.item())
+                if rank != 0:
+                    continue
+                identical = identical and all(torch.equal(tiles[0].view(torch.int32), t.view(torch.int32)) for t in tiles[1:])
+                refs.append(oracle.gemm_f32acc(_bits16(sent), _bits16(b[c0:c0 + 256]), oracle.BF16))
+                acc.append(tiles[0].cpu().numpy())
+            if rank != 0:
+                return None
+            rep = _dense_tile_report(acc, None, refs, 1e-3)
+            rep["gathered_rows_equal_owners_rows"] = bool(received)
+            rep["all_ranks_identical"] = bool(identical)
+            rep["ok"] = bool(rep["ok"] and received and identical)
+            return rep
+
+        step.parity = parity
+        step.reduce_used = "allgather_one_kernel" + ("_nvls_multimem" if op.multicast else "_peer_stores")
+        step.op = op
+        return step, flops, (m + n) * k * 2 + m * n * 4, 1
     raise ValueError(kind)
 
 
@@ -624,7 +680,7 @@ def reference_arm(args, world, rank):
         oracle.build()
     # one step = one 128 x 256 output tile over a K that keeps the whole run within a few minutes
     full_k = spec["k"] if kind != "ksplit" else spec["k"] // max(args.gpus, 1)
-    sk = "dense" if kind == "ksplit" else kind
+    sk = "dense" if kind in ("ksplit", "allgather") else kind
     depths = (8192, 4096, 1024, 256) if sk == "dense" else (8192, 1024, 256)
     candidates = [kk for kk in depths if kk <= full_k] or [256]
     total_steps = args.steps + args.warmup
@@ -648,7 +704,8 @@ def reference_arm(args, world, rank):
         "impl": "reference", "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": el / max(args.steps, 1) * 1e3,
         "higher_is_better": True, "scaling": "strong" if kind == "ksplit" else "weak", "vs_baseline": None,
-        "dtype": {"dense": "bf16", "ksplit": "bf16", "s8": "s8", "mx": "mxfp8_e4m3"}[kind], "data": "synthetic",
+        "dtype": {"dense": "bf16", "ksplit": "bf16", "allgather": "bf16", "s8": "s8", "mx": "mxfp8_e4m3"}[kind],
+        "data": "synthetic",
         "config": {"workload": name, "m": spec["m"], "n": spec["n"], "k": spec["k"],
                    "note": "reference CPU simulator on host cores; each step is one 128x256 output tile over "
                            f"K={chosen} of this workload"},
@@ -739,12 +796,15 @@ def main():
     tflops = flops / (ms_per_step * 1e-3) / 1e12
 
     kind = spec["kind"]
-    dtype = {"dense": spec.get("dtype", "bf16"), "ksplit": "bf16", "s8": "s8", "mx": "mxfp8_e4m3"}[kind]
-    peak_scale = {"dense": 1.0, "ksplit": 1.0, "s8": 2.0, "mx": 2.0}[kind]
+    dtype = {"dense": spec.get("dtype", "bf16"), "ksplit": "bf16", "allgather": "bf16", "s8": "s8",
+             "mx": "mxfp8_e4m3"}[kind]
+    peak_scale = {"dense": 1.0, "ksplit": 1.0, "allgather": 1.0, "s8": 2.0, "mx": 2.0}[kind]
     # a single kernel timed back to back for a short region: burst peak; the long K-split step: sustained
     peak_key = "bf16_tflops" if ms < 500.0 else "bf16_tflops_sustained"
     peak = float(peaks.get(peak_key, FALLBACK_PEAKS["bf16_tflops"])) * peak_scale
-    achieved = tflops / world
+    # K-split: the ranks share one product; all-gather: every rank computes the whole product (the reference's
+    # 2 M N K / time counts it once), so a GPU achieves the line's value
+    achieved = tflops / world if kind == "ksplit" else tflops
     line = {
         "metric": "gemm_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -753,13 +813,16 @@ def main():
                    "layout": "A row-major, B column-major, fp32 accumulate",
                    "l2": (f"rotating {sets} input/output sets, {ws_bytes / 2**20:.0f} MiB > 126 MiB L2"
                           if sets > 1 else f"working set {ws_bytes / 2**20:.0f} MiB > 126 MiB L2"),
-                   "inputs": "seeded torch.randn on device, N(0,1)/sqrt(K)" if kind in ("dense", "ksplit") else "seeded",
+                   "inputs": ("seeded torch.randn on device, N(0,1)/sqrt(K)" if kind in ("dense", "ksplit", "allgather")
+                              else "seeded"),
                    **({"parallelism": f"ksplit{world}", "panels": args.panels,
                        "reduce": getattr(step, "reduce_used", args.mode),
                        "gemm_blocks": args.gemm_blocks, "reduce_blocks": args.reduce_blocks,
                        "gemm_streams": args.gemm_streams,
                        "panel_rows": getattr(step, "panel_rows", None)}
-                      if kind == "ksplit" else {})},
+                      if kind == "ksplit" else
+                      ({"parallelism": f"allgather{world}", "reduce": getattr(step, "reduce_used", None)}
+                       if kind == "allgather" else {}))},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak, "traffic": ncu_dram_traffic(name),
                      "peak_source": f"{peaks['_source']}: {peak_key}" + (" x2 (8-bit kinds, nominal ratio)" if peak_scale > 1 else ""),
@@ -870,7 +933,7 @@ def main():
             line["cpu_baseline"]["single_thread"] = {"value": v1, "cores": info1["cores"], "sample": info1["sample"]}
         except Exception as e:  # noqa: BLE001
             line["cpu_baseline"] = {"value": None, "unit": "TFLOP/s", "cores": 0, "kind": "port", "sample": repr(e)}
-    elif world > 1:
+    elif world > 1 and kind == "ksplit":
         # end to end for the K-split step: H2D of this rank's operand slices, the step, D2H of the bf16 result
         a, b, out = step.tensors
         h_a = torch.empty(a.shape, dtype=a.dtype).pin_memory()

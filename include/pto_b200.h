@@ -82,11 +82,13 @@ int pto_b200_gemm_ex(void* stream, uint8_t* out, const uint8_t* src0, const uint
  * pto_b200_gemm_ex with an optional workspace for the last, partly filled wave of tiles. The reference assigns each
  * core a fixed sub-matrix (InitGMOffsets, gemm_performance_kernel.cpp:48-67) and has no counterpart; on 148 SMs a
  * 4096^3 problem leaves the last wave 46 % full, so with a workspace each leftover tile is cut into two K halves
- * that run on two CTA pairs at once: the first half parks its 32-bit accumulators in the workspace, the second adds
- * them to its own and stores. Results differ from the unsplit chain only by the fp32 summation order (int32: exact).
- *   workspace : device memory of pto_b200_gemm_workspace_bytes() bytes, 16-byte aligned, ZERO before its first use
- *               (the kernel leaves its counters zero again), or NULL = never split. One workspace must not be used
- *               by two launches that can overlap on the GPU (use one per stream).
+ * that run on two CTA pairs at once and then swap: each pair parks the 32-bit accumulators of the 128 columns the
+ * other pair finishes in the workspace, adds the other's half to its own and stores. Results differ from the unsplit
+ * chain only by the fp32 summation order (int32: exact).
+ *   workspace : device memory of pto_b200_gemm_workspace_bytes() bytes, 16-byte aligned, ZERO before its first use,
+ *               or NULL = never split. One workspace must not be used by two launches that can overlap on the GPU
+ *               (use one per stream). The split is skipped when launch_block_count caps the blocks: the two pairs of
+ *               a tile wait for each other inside the kernel, so all blocks of the launch must be on the GPU at once.
  */
 size_t pto_b200_gemm_workspace_bytes(void);
 int pto_b200_gemm_ws(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, int m, int n, int k,
@@ -295,6 +297,34 @@ int pto_b200_ksplit_gemm_allreduce(void* stream, const uint8_t* src0, const uint
                                    int* panel_counters_local, int* exchange_counters_local, int world, int rank,
                                    int slot0, int epoch, int panel_rows, long long ld_partial, long long ld_out,
                                    const void* multicast_partial, void* multicast_out, int launch_block_count);
+
+/*
+ * One rank's whole step of AllGather + GEMM in ONE kernel launch: every rank holds an M slice of A, B is replicated,
+ * every rank ends with the whole C = A * B. Extra warps of the GEMM kernel push this rank's slice, 256-row block by
+ * block, into every rank's copy of A (one NVSwitch multicast store per 16 bytes when a multicast address is given,
+ * else one store per peer) and publish a flag per block; the tile loop starts with this rank's own rows and waits for
+ * the flag of a remote block before its first load from it, so multiplication starts before the gather completes.
+ * Replaces: launchRingCommStreaming + launchAllGatherGemmComputeStreaming on two streams
+ * (kernels/manual/a2a3/allgather_gemm/allgather_gemm_comm_kernel.cpp:255, allgather_gemm_compute_kernel.cpp:393;
+ * pipeline described in kernels/manual/a2a3/allgather_gemm/README.md:28-110).
+ *   a_ptrs        : every rank's copy of A [m, lda] as mapped in this process; rank r owns rows [r m/world, (r+1) m/world)
+ *                   and must have written them into ITS copy before the launch; the other rows are filled by the peers
+ *   src1          : B, column-major [n, k] (ldb), the same on every rank; in_dtype F16 or BF16
+ *   out           : this rank's C [m, n] (ldc), out_dtype F32, BF16 or F16
+ *   flag_arrays   : every rank's flag array, ceil(m / 256) + PTO_B200_KSPLIT_MAX_RANKS ints, zero before the first step
+ *   block_counters_local : this rank's scratch, m / (256 world) ints, zero before the first step
+ *   done_counter_local   : this rank's scratch, one int, zero before the first step
+ *   epoch         : 1, 2, 3, ... one per step, the same on every rank
+ *   multicast_a   : NVSwitch multicast address of the A copies, or null
+ * m must be a multiple of 256 * world and k of 8. A step's pushes wait (bounded) until every rank has finished
+ * reading the previous step's rows. As for pto_b200_ksplit_gemm_allreduce, all ranks launch the same step at about the
+ * same time and the launch must be able to hold all its thread blocks on the GPU at once. TMA loads read this GPU's
+ * own copy of A only; peers are reached by plain or multimem stores.
+ */
+int pto_b200_allgather_gemm(void* stream, uint8_t* out, void* const* a_ptrs, const uint8_t* src1, int m, int n, int k,
+                            long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype,
+                            void* const* flag_arrays, int* block_counters_local, int* done_counter_local, int world,
+                            int rank, int epoch, void* multicast_a, int launch_block_count);
 
 /*
  * Cycles a kernel of this library waits on one barrier or flag before it gives up (records a code in the status

@@ -75,6 +75,11 @@ SYMBOLS = {
          ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p),
          ctypes.c_void_p, ctypes.c_void_p, _i, _i, _i, _i, _i, _ll, _ll, ctypes.c_void_p, ctypes.c_void_p, _i],
     ),
+    "pto_b200_allgather_gemm": (
+        _i,
+        [ctypes.c_void_p, _u8p, ctypes.POINTER(ctypes.c_void_p), _u8p, _i, _i, _i, _ll, _ll, _ll, _i, _i,
+         ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.c_void_p, _i, _i, _i, ctypes.c_void_p, _i],
+    ),
     "pto_b200_set_wait_limit": (_ll, [_ll]),
     "call_kernel": (None, [ctypes.c_uint32, ctypes.c_void_p, _u8p, _u8p, _u8p]),
     "pto_b200_device_status": (_i, [ctypes.POINTER(_i)]),

@@ -54,11 +54,13 @@ struct GemmParams {
     const void* bias;   // TMATMUL_BIAS: one value per output column in the accumulator's type (fp32 / int32), or null
     int* status;
     // CTA-pair kernels, last partly filled wave: each leftover tile is cut in two K halves that run on two pairs at
-    // once; the first half parks its fp32 / int32 accumulators in the workspace, the second half adds them and stores.
+    // once; each pair parks the accumulators of the columns the other pair finishes and adds the other's to its own.
     int tail_first_unit; // first work unit of the split tail (= number of tiles when nothing is split)
     int tail_tiles;      // leftover tiles that are split (0 = none)
-    uint32_t* ws_partial; // [tail_tiles][256][256] 32-bit accumulators
-    int* ws_flags;        // [2 * tail_tiles]: arrivals of the first halves' store warps, departures of the readers
+    uint32_t* ws_partial; // [tail_tiles][2 K halves][2 CTAs][128 x 128] parked 32-bit accumulators
+    int* ws_flags;        // [tail_tiles][2 K halves][8 store warps]: "my half is parked" = this launch's token
+    int tail_token;       // never 0, different for every launch that splits tiles
+    int mi_rotate;        // CTA-pair kernels: the tile raster starts at this row of tiles and wraps (0 = from the top)
     const unsigned long long* quant_words; // EPI_QUANT16, vector form: n scale words in device memory
     unsigned long long quant_word;         // EPI_QUANT16, scalar form: the scale word
     int quant_flags;                       // EPI_QUANT16: QuantFlags

@@ -20,7 +20,7 @@
 // second CTA, which issues no MMAs, copies them into tensor memory (tcgen05.cp, every stage of the ring has its own
 // scale columns) and commits to the leader, so no scale copy sits in the leader's MMA instruction stream.
 //
-// K-split form (FUSED_AR): the kernel of one rank of the reference's GEMM + AllReduce
+// K-split form (COMM_KSPLIT): the kernel of one rank of the reference's GEMM + AllReduce
 // (kernels/manual/a2a3/gemm_ar: gemm_compute_kernel.cpp:150-240 fills a ready queue tile by tile, comm_kernel.cpp
 // :165-210 reduce-scatters, :377-400 all-gathers, :528-590 waits). Here both halves are ONE kernel: the tile loop
 // walks the output row panel by row panel and counts finished tiles per panel; the warp that completes a panel
@@ -28,6 +28,14 @@
 // of a panel, sum this rank's row shard of it over the ranks' fp32 partials through peer memory (NVSwitch multimem
 // or plain peer loads), cast to bf16, store the result into every rank's output, publish done[panel][rank], and at
 // the end wait until every rank has delivered every panel here. No TMA load and no multicast load touches peer memory.
+//
+// All-gather form (COMM_GATHER): the kernel of one rank of the reference's AllGather + GEMM
+// (kernels/manual/a2a3/allgather_gemm: every rank holds an M slice of A, B is replicated, every rank computes the
+// whole C; allgather_gemm_comm_kernel.cpp pushes chunks and counts them, allgather_gemm_compute_kernel.cpp:393 waits per
+// chunk and multiplies, local rows first). Here the four extra warps per CTA push this rank's slice of A, 256-row
+// block by block, into every rank's copy of A (one NVSwitch multicast store per 16 bytes, or one store per peer) and
+// publish arrived[block] to every rank; the tile loop starts with this rank's own rows and its TLOAD role waits for a
+// remote block's flag before the first TMA load of a tile in it. TMA reads this GPU's own copy of A only.
 //
 // Every wait is bounded as in gemm_tile_loop; the pair leaves through a cluster barrier so neither CTA's shared
 // or tensor memory disappears while the other can still touch it.
@@ -45,6 +53,7 @@ constexpr int ST_TAIL_TIMEOUT = 5;
 constexpr int kExchangeThreads = 128; // four exchange warps per CTA in the K-split form
 constexpr int kExchangeBarrierId = 1;
 constexpr int ST_SCALE_TIMEOUT = 6;
+constexpr int ST_GATHER_TIMEOUT = 18; // a remote block of A never arrived, or a rank never finished the previous step
 
 __device__ __forceinline__ int ld_acquire_gpu(const int* ptr)
 {
@@ -70,6 +79,35 @@ struct KsplitFusedArgs {
     int panels;              // row panels of the output
     int panel_tile_rows;     // 256-row tiles per panel (= the raster's group height)
 };
+
+// What the extra warps of a CTA do: nothing (no extra warps), the K-split exchange, or the all-gather push.
+enum CommMode : int { COMM_NONE = 0, COMM_KSPLIT = 1, COMM_GATHER = 2 };
+
+// What the all-gather form needs besides the GEMM's own arguments.
+struct GatherArgs {
+    PeerPointers a_full;    // every rank's copy of A [m, lda] (own rank included); rank r owns rows [r m/world, (r+1) m/world)
+    PeerPointers flags;     // every rank's flag array: arrived[m_tiles] then done[kMaxRanks], epochs
+    void* mc_a;             // NVSwitch multicast address of the A copies, or null (one store per peer)
+    int* block_counter;     // local, one int per block of a slice, zero between steps: CTAs that pushed their part
+    int* done_counter;      // local, one int, zero between steps: CTAs that finished the step
+    long long lda_bytes;    // row pitch of A
+    int row_bytes;          // bytes of a row that carry data (k elements), a multiple of 16
+    int world, rank, epoch;
+    int blocks_per_rank;    // 256-row blocks in one rank's slice
+};
+
+__device__ __forceinline__ void multimem_st_b128(void* mc_ptr, const uint4& v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_ptr), "f"(__uint_as_float(v.x)),
+                 "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+                 : "memory");
+}
+
+__device__ __forceinline__ void st_relaxed_sys_b128(void* ptr, const uint4& v)
+{
+    asm volatile("st.relaxed.sys.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(ptr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
 
 template <int KIND, int STAGES, int EPI_BUFS>
 struct PairSmemLayout {
@@ -104,6 +142,9 @@ __device__ __forceinline__ bool pair_unit(int u, const GemmParams& p, PairUnit& 
 {
     if (u < p.tail_first_unit) {
         tile_coords(u, p, w.mi, w.ni);
+        if (p.mi_rotate != 0) { // all-gather form: the raster starts at this rank's own rows
+            w.mi = (w.mi + p.mi_rotate) % p.m_tiles;
+        }
         w.kb0 = 0;
         w.kb1 = p.k_blocks;
         w.role = 0;
@@ -125,21 +166,29 @@ __device__ __forceinline__ bool pair_unit(int u, const GemmParams& p, PairUnit& 
 
 constexpr int kTailWarps = 8; // store warps of a pair: four in each CTA
 
-// Parked accumulators of a split tile: per CTA of the pair 128 rows x 256 columns of 32-bit words, laid out so that a
-// warp's 16-byte accesses are contiguous: word index ((chunk * 8 + i) * 128 + row) * 4 for the i-th 16 bytes of the
-// 32-column chunk `chunk` of row `row`.
+// Parked accumulators of a split tile: per CTA and K half 128 rows x 128 columns of 32-bit words, laid out so that a
+// warp's 16-byte accesses are contiguous: 16-byte index (chunk * 8 + i) * 128 + row for the i-th 16 bytes of the
+// 32-column chunk `chunk` (0..3) of row `row`.
 __device__ __forceinline__ uint4* parked_quad(uint32_t* cta_base, int chunk, int i, int row_in_cta)
 {
     return reinterpret_cast<uint4*>(cta_base) + (chunk * 8 + i) * kBlockM + row_in_cta;
 }
 
-template <int KIND, int STAGES, int EPI, bool FUSED_AR>
+__device__ __forceinline__ void st_release_gpu(int* ptr, int v)
+{
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+
+template <int KIND, int STAGES, int EPI, int COMM>
 __global__ void __cluster_dims__(2, 1, 1)
-    __launch_bounds__(kNumThreads + (FUSED_AR ? kExchangeThreads : 0), 1)
+    __launch_bounds__(kNumThreads + (COMM != COMM_NONE ? kExchangeThreads : 0), 1)
     gemm_tile_loop_2cta(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                        const __grid_constant__ CUtensorMap tmap_c, const GemmParams p, const KsplitFusedArgs ar)
+                        const __grid_constant__ CUtensorMap tmap_c, const GemmParams p, const KsplitFusedArgs ar,
+                        const GatherArgs ga)
 {
+    constexpr bool FUSED_AR = (COMM == COMM_KSPLIT);
+    static_assert(COMM != COMM_GATHER || KIND == KIND_F16, "the all-gather form multiplies 16-bit inputs");
     constexpr int kEpiBufs = (KIND == KIND_MXF8) ? 1 : 2;
     using L = PairSmemLayout<KIND, STAGES, kEpiBufs>;
     constexpr int kNumAcc = (KIND == KIND_MXF8) ? 1 : 2;
@@ -213,6 +262,19 @@ __global__ void __cluster_dims__(2, 1, 1)
                 const int mi = w.mi, ni = w.ni;
                 const int row_a = mi * kPairBlockM + static_cast<int>(cta_rank) * kBlockM;
                 const int row_b = ni * kPairBlockN + static_cast<int>(cta_rank) * (kPairBlockN / 2);
+                if constexpr (COMM == COMM_GATHER) {
+                    // rows of another rank: wait until its push of this 256-row block has been published here, then
+                    // order the peer's (generic-proxy) writes before this thread's TMA (async-proxy) reads
+                    if (mi / ga.blocks_per_rank != ga.rank) {
+                        const int* arrived = static_cast<const int*>(ga.flags.p[ga.rank]);
+                        if (!wait_epoch(arrived + mi, ga.epoch, p.status, ST_GATHER_TIMEOUT, p.wait_limit)) {
+                            *abort_flag = 1;
+                            ok = false;
+                            break;
+                        }
+                        asm volatile("fence.proxy.async;" ::: "memory");
+                    }
+                }
                 for (int kb = w.kb0; kb < w.kb1; ++kb) {
                     ok = bounded_wait(&empty_bar[stage], phase ^ 1u, abort_flag, p.status, ST_PRODUCER_TIMEOUT,
                                       p.wait_limit);
@@ -378,71 +440,16 @@ __global__ void __cluster_dims__(2, 1, 1)
             }
             const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * kAccCols) +
                                    (static_cast<uint32_t>(quarter * 32) << 16);
-            const bool use_tma = (w.role == 0) && (p.tma_store != 0);
-            // parked accumulators of a split tile (this CTA's 128 x 256 words) and the tile's two counters
-            uint32_t* ws_cta = nullptr;
-            int* ws_arrive = nullptr;
-            if (w.role != 0) {
-                ws_cta = p.ws_partial + (static_cast<size_t>(w.tail_idx) * 2 + cta_rank) * (kBlockM * kPairBlockN);
-                ws_arrive = p.ws_flags + 2 * w.tail_idx;
-            }
-            if (w.role == 2) {
-                // second K half: wait (bounded) until every store warp of the first half has parked its rows
-                bool parked = true;
-                if (lane == 0) {
-                    const long long t0 = clock64();
-                    while (ld_acquire_gpu(ws_arrive) < kTailWarps) {
-                        __nanosleep(32);
-                        if (*abort_flag != 0 || clock64() - t0 > p.wait_limit) {
-                            *abort_flag = 1;
-                            atomicCAS(p.status, 0, ST_TAIL_TIMEOUT);
-                            parked = false;
-                            break;
-                        }
-                    }
-                }
-                parked = __all_sync(0xFFFFFFFFu, parked);
-                if (!parked) {
-                    ok = false;
-                    break;
-                }
-            }
-            // One 32-column chunk of this thread's row. Whole tiles: convert and either write the words into the
-            // warp's swizzled store box (a box is one chunk of 32-bit outputs or two chunks of 16-bit outputs; the
-            // box leaves with one TMA store when it is full) or store them from registers. Split tiles: park the raw
-            // accumulators (first K half) or add the parked half and store from registers (second K half).
+            const bool use_tma = (p.tma_store != 0);
+            // One finished 32-column chunk of this thread's row: convert and either write the words into the warp's
+            // swizzled store box (a box is one chunk of 32-bit outputs or two chunks of 16-bit outputs; the box leaves
+            // with one TMA store when it is full) or store them from registers.
             auto finish_chunk = [&](uint32_t (&v)[32], int chunk) {
                 constexpr int kChunksPerBox = kOut32 ? 1 : 2;
                 const int col0 = ni * kPairBlockN + chunk * 32;
                 // nothing to do past N; a store box that starts before N is still filled and sent whole (TMA clips it)
                 if ((use_tma ? col0 - (chunk % kChunksPerBox) * 32 : col0) >= p.n) {
                     return;
-                }
-                if (w.role == 1) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        *parked_quad(ws_cta, chunk, i, row_in_cta) = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                    }
-                    return;
-                }
-                if (w.role == 2) {
-                    uint4 q[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        q[i] = __ldcg(parked_quad(ws_cta, chunk, i, row_in_cta));
-                    }
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const uint32_t qa[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if constexpr (EPI == EPI_S32 || EPI == EPI_DEQ_BF16) {
-                                v[4 * i + j] += qa[j]; // int32 accumulators: exact
-                            } else {
-                                v[4 * i + j] = __float_as_uint(__uint_as_float(qa[j]) + __uint_as_float(v[4 * i + j]));
-                            }
-                        }
-                    }
                 }
                 if (!use_tma) {
                     store_chunk<EPI>(v, p, row, col0, vec_ok, s_row);
@@ -477,10 +484,21 @@ __global__ void __cluster_dims__(2, 1, 1)
                     ++boxes;
                 }
             };
-            // Accumulator read-back, software-pipelined over 32-column chunks: the TMEM load of the next chunk is in
-            // flight while the current one is converted and stored (columns past N are loaded but never stored).
-            // The accumulator is handed back to the MMA role as soon as its last chunk is in registers.
-            {
+            auto release_accumulator = [&]() {
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if (leader) {
+                        ptx::mbar_arrive(&acc_empty_bar[acc]);
+                    } else {
+                        ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&acc_empty_bar[acc]), 0));
+                    }
+                }
+            };
+            if (w.role == 0) {
+                // Accumulator read-back, software-pipelined over 32-column chunks: the TMEM load of the next chunk is
+                // in flight while the current one is converted and stored (columns past N are loaded but never
+                // stored). The accumulator is handed back to the MMA role as soon as its last chunk is in registers.
                 uint32_t va[32], vb[32];
                 ptx::tmem_ld_32x32b_x32(t_row + 0u, va);
 #pragma unroll
@@ -492,33 +510,105 @@ __global__ void __cluster_dims__(2, 1, 1)
                     if (g + 1 < kPairBlockN / 64) {
                         ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(g * 64 + 64), va);
                     } else {
-                        ptx::tc_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) {
-                            if (leader) {
-                                ptx::mbar_arrive(&acc_empty_bar[acc]);
-                            } else {
-                                ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&acc_empty_bar[acc]), 0));
-                            }
-                        }
+                        release_accumulator();
                     }
                     finish_chunk(vb, g * 2 + 1);
                 }
-            }
-            if (w.role == 1) {
+            } else {
+                // A tile of the last, partly filled wave, cut into two K halves on two pairs. The halves swap: each
+                // pair parks the accumulators of the 128 columns the OTHER pair will finish (role 1 finishes columns
+                // 0..127, role 2 columns 128..255), tells the other, waits for the other's half, adds it to its own
+                // accumulators and stores. Both pairs do the same amount of work and neither waits for a whole
+                // read-back of the other. Flags carry this launch's token, so nothing is counted and nothing needs
+                // resetting, whatever an earlier launch left behind.
+                const int keep0 = (w.role == 1) ? 0 : 4;   // first of the four chunks this pair finishes
+                const int give0 = 4 - keep0;
+                const size_t half_words = static_cast<size_t>(kBlockM) * (kPairBlockN / 2);
+                uint32_t* mine_parked = p.ws_partial + ((static_cast<size_t>(w.tail_idx) * 2 + (w.role - 1)) * 2 + cta_rank) * half_words;
+                uint32_t* theirs_parked = p.ws_partial + ((static_cast<size_t>(w.tail_idx) * 2 + (2 - w.role)) * 2 + cta_rank) * half_words;
+                int* my_flags = p.ws_flags + (w.tail_idx * 2 + (w.role - 1)) * kTailWarps;
+                const int* their_flags = p.ws_flags + (w.tail_idx * 2 + (2 - w.role)) * kTailWarps;
+                uint32_t v[32];
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>((give0 + c) * 32), v);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        *parked_quad(mine_parked, c, i, row_in_cta) = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    }
+                }
                 __threadfence();
                 __syncwarp();
                 if (lane == 0) {
-                    atomicAdd(ws_arrive, 1);
+                    st_release_gpu(my_flags + static_cast<int>(cta_rank) * 4 + quarter, p.tail_token);
                 }
-            } else if (w.role == 2) {
-                __syncwarp();
-                if (lane == 0) {
-                    // the last reader to leave clears both counters for the next launch
-                    if (atomicAdd(ws_arrive + 1, 1) == kTailWarps - 1) {
-                        ws_arrive[0] = 0;
-                        ws_arrive[1] = 0;
+                // wait (bounded) until all eight store warps of the other pair have parked their half
+                bool parked = true;
+                if (lane < kTailWarps) {
+                    const long long t0 = clock64();
+                    while (ld_acquire_gpu(their_flags + lane) != p.tail_token) {
+                        __nanosleep(32);
+                        if (*abort_flag != 0 || clock64() - t0 > p.wait_limit) {
+                            *abort_flag = 1;
+                            atomicCAS(p.status, 0, ST_TAIL_TIMEOUT);
+                            parked = false;
+                            break;
+                        }
                     }
+                }
+                parked = __all_sync(0xFFFFFFFFu, parked);
+                if (!parked) {
+                    ok = false;
+                    break;
+                }
+                // finish this pair's four chunks; the parked values of the next chunk are in flight meanwhile
+                uint4 qa[8], qb[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    qa[i] = __ldcg(parked_quad(theirs_parked, 0, i, row_in_cta));
+                }
+                auto add_parked = [&](const uint4 (&q)[8]) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const uint32_t qv[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if constexpr (EPI == EPI_S32 || EPI == EPI_DEQ_BF16 || EPI == EPI_QUANT16) {
+                                if (EPI != EPI_QUANT16 || (p.quant_flags & QUANT_ACC_S32) != 0) {
+                                    v[4 * i + j] += qv[j]; // int32 accumulators: exact
+                                } else {
+                                    v[4 * i + j] = __float_as_uint(__uint_as_float(qv[j]) + __uint_as_float(v[4 * i + j]));
+                                }
+                            } else {
+                                v[4 * i + j] = __float_as_uint(__uint_as_float(qv[j]) + __uint_as_float(v[4 * i + j]));
+                            }
+                        }
+                    }
+                };
+#pragma unroll
+                for (int c = 0; c < 4; c += 2) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        qb[i] = __ldcg(parked_quad(theirs_parked, c + 1, i, row_in_cta));
+                    }
+                    ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>((keep0 + c) * 32), v);
+                    ptx::tmem_ld_wait();
+                    add_parked(qa);
+                    finish_chunk(v, keep0 + c);
+                    if (c + 2 < 4) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            qa[i] = __ldcg(parked_quad(theirs_parked, c + 2, i, row_in_cta));
+                        }
+                    }
+                    ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>((keep0 + c + 1) * 32), v);
+                    ptx::tmem_ld_wait();
+                    if (c + 2 >= 4) {
+                        release_accumulator();
+                    }
+                    add_parked(qb);
+                    finish_chunk(v, keep0 + c + 1);
                 }
             }
             if constexpr (FUSED_AR) {
@@ -553,6 +643,77 @@ __global__ void __cluster_dims__(2, 1, 1)
         // shared memory must outlive the reads of the last store boxes
         if (lane == 0) {
             ptx::bulk_wait_group_read<0>();
+        }
+    } else if constexpr (COMM == COMM_GATHER) {
+        // ---------------------------------------------------------------- gather role (both CTAs, all-gather form)
+        const int tid = static_cast<int>(threadIdx.x) - kNumThreads;
+        const int* my_flags = static_cast<const int*>(ga.flags.p[ga.rank]);
+        // Nobody may still be reading the previous step's rows: every rank published done[r] = epoch - 1 when its
+        // last tile was loaded (flags start at zero, so the first step passes at once).
+        if (tid < ga.world) {
+            if (!wait_epoch(my_flags + p.m_tiles + tid, ga.epoch - 1, p.status, ST_GATHER_TIMEOUT, p.wait_limit)) {
+                *exchange_ok = 0;
+            }
+        }
+        ptx::named_barrier_sync(kExchangeBarrierId, kExchangeThreads);
+        const bool ok = (*exchange_ok != 0);
+        const int items_per_row = ga.row_bytes / 16;
+        const uint8_t* mine = static_cast<const uint8_t*>(ga.a_full.p[ga.rank]);
+        // The CTAs of the launch form up to four groups; group g pushes blocks g, g + groups, ... of the slice, so
+        // several blocks are in flight at once and the wait for one block's stores to be acknowledged by the peers
+        // (the system-scope fence before its flag) overlaps the next blocks' stores. Blocks still complete roughly
+        // in the order the peers consume them.
+        const int groups = min(ga.blocks_per_rank, min(4, static_cast<int>(gridDim.x)));
+        const int group = static_cast<int>(blockIdx.x) % groups;
+        const int group_ctas = (static_cast<int>(gridDim.x) - group + groups - 1) / groups;
+        const long long first = static_cast<long long>(blockIdx.x / groups) * kExchangeThreads + tid;
+        const long long stride = static_cast<long long>(group_ctas) * kExchangeThreads;
+        for (int b = group; ok && ga.world > 1 && b < ga.blocks_per_rank; b += groups) {
+            const int block = ga.rank * ga.blocks_per_rank + b;
+            const int row0 = block * kPairBlockM;
+            const int rows = min(kPairBlockM, p.m - row0);
+            const long long total = static_cast<long long>(rows) * items_per_row;
+            constexpr int kUnroll = 4;
+            for (long long i0 = first; i0 < total; i0 += stride * kUnroll) {
+                uint4 v[kUnroll];
+                long long off[kUnroll];
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) {
+                    const long long i = i0 + u * stride;
+                    off[u] = -1;
+                    if (i < total) {
+                        off[u] = (row0 + i / items_per_row) * ga.lda_bytes + (i % items_per_row) * 16;
+                        v[u] = __ldg(reinterpret_cast<const uint4*>(mine + off[u]));
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) {
+                    if (off[u] < 0) {
+                        continue;
+                    }
+                    if (ga.mc_a != nullptr) {
+                        multimem_st_b128(static_cast<uint8_t*>(ga.mc_a) + off[u], v[u]);
+                    } else {
+                        for (int r = 0; r < ga.world; ++r) {
+                            if (r != ga.rank) {
+                                st_relaxed_sys_b128(static_cast<uint8_t*>(ga.a_full.p[r]) + off[u], v[u]);
+                            }
+                        }
+                    }
+                }
+            }
+            // the last CTA of the group to finish its part of the block publishes it to every rank
+            __threadfence_system();
+            ptx::named_barrier_sync(kExchangeBarrierId, kExchangeThreads);
+            if (tid == 0) {
+                if (atomicAdd(ga.block_counter + b, 1) == group_ctas - 1) {
+                    ga.block_counter[b] = 0;
+                    __threadfence_system();
+                    for (int r = 0; r < ga.world; ++r) {
+                        st_release_sys(static_cast<int*>(ga.flags.p[r]) + block, ga.epoch);
+                    }
+                }
+            }
         }
     } else if constexpr (FUSED_AR) {
         // ---------------------------------------------------------------- exchange role (both CTAs, K-split form)
@@ -630,6 +791,19 @@ __global__ void __cluster_dims__(2, 1, 1)
     if (*abort_flag != 0) {
         for (int i = 0; i < 2000; ++i) {
             __nanosleep(1000);
+        }
+    }
+    if constexpr (COMM == COMM_GATHER) {
+        // every load of this CTA has landed: the last CTA of the launch tells every rank that this rank is done with
+        // the step's rows, so the next step's pushes may overwrite them
+        if (threadIdx.x == 0) {
+            if (atomicAdd(ga.done_counter, 1) == static_cast<int>(gridDim.x) - 1) {
+                *ga.done_counter = 0;
+                __threadfence_system();
+                for (int r = 0; r < ga.world; ++r) {
+                    st_release_sys(static_cast<int*>(ga.flags.p[r]) + p.m_tiles + ga.rank, ga.epoch);
+                }
+            }
         }
     }
     // Both CTAs are past every access to the other's shared memory, barriers and tensor memory.

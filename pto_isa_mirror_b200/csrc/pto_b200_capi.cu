@@ -238,10 +238,11 @@ struct PairLaunch {
     size_t workspace_bytes = 0;
     int out_dtype = PTO_B200_F32;         // element type of C (for the store map)
     const KsplitFusedArgs* fused = nullptr; // K-split form: exchange arguments (group height = its panel height)
+    const GatherArgs* gather = nullptr;     // all-gather form: push arguments
     bool no_tma_store = false;
 };
 
-template <int KIND, int EPI, bool FUSED_AR = false>
+template <int KIND, int EPI, int COMM = COMM_NONE>
 int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, const Problem& q,
                 const PairLaunch& o)
 {
@@ -250,9 +251,10 @@ int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& t
 #endif
     constexpr int STAGES = (KIND == KIND_MXF8) ? 6 : PTO_B200_PAIR_STAGES;
     constexpr int kEpiBufs = (KIND == KIND_MXF8) ? 1 : 2;
-    constexpr int kThreads = kNumThreads + (FUSED_AR ? kExchangeThreads : 0);
+    constexpr bool FUSED_AR = (COMM == COMM_KSPLIT);
+    constexpr int kThreads = kNumThreads + (COMM != COMM_NONE ? kExchangeThreads : 0);
     using L = PairSmemLayout<KIND, STAGES, kEpiBufs>;
-    auto kernel = gemm_tile_loop_2cta<KIND, STAGES, EPI, FUSED_AR>;
+    auto kernel = gemm_tile_loop_2cta<KIND, STAGES, EPI, COMM>;
     static std::atomic<int> max_clusters[kMaxDevices];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -288,8 +290,11 @@ int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& t
     p.n_tiles = (q.n + kPairBlockN - 1) / kPairBlockN;
     p.group_m = FUSED_AR ? o.fused->panel_tile_rows : 8;
     const int tiles = p.m_tiles * p.n_tiles;
-    if (tiles < clusters && !FUSED_AR) {
+    if (tiles < clusters && COMM == COMM_NONE) {
         return -1;
+    }
+    if (COMM == COMM_GATHER) {
+        p.mi_rotate = (o.gather->rank * o.gather->blocks_per_rank) % p.m_tiles;
     }
     int pairs = tiles < clusters ? tiles : clusters;
     if (o.block_limit > 0 && o.block_limit / 2 < pairs) {
@@ -297,22 +302,22 @@ int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& t
     }
     cfg.gridDim = dim3(2 * pairs, 1, 1);
     // Last wave: when the leftover tiles would occupy at most half of the pairs, cut each of them into two K halves
-    // that run on two pairs at once (accumulators of the first half parked in the caller's workspace). The second
-    // half waits in the kernel for the first, so the split is only used when this launch may take every SM (no block
-    // cap) and is never combined with the K-split form.
+    // that run on two pairs at once and swap halves of their accumulators through the caller's workspace. The two
+    // pairs wait for each other in the kernel, so the split is only used when this launch may take every SM (no
+    // block cap) and is never combined with the K-split form.
     const int leftover = tiles % pairs;
     p.tail_first_unit = tiles;
     p.tail_tiles = 0;
-    if (!FUSED_AR && o.workspace != nullptr && o.workspace_bytes >= kGemmWorkspaceBytes && o.block_limit == 0 &&
+    if (COMM == COMM_NONE && o.workspace != nullptr && o.workspace_bytes >= kGemmWorkspaceBytes && o.block_limit == 0 &&
         leftover > 0 && 2 * leftover <= pairs && leftover <= kGemmWorkspaceTiles && p.k_blocks >= 2) {
         p.tail_first_unit = tiles - leftover;
         p.tail_tiles = leftover;
         p.ws_flags = reinterpret_cast<int*>(o.workspace);
         p.ws_partial = reinterpret_cast<uint32_t*>(o.workspace + kGemmWorkspaceFlagBytes);
-        // counters start from zero whatever an earlier launch that gave up left behind
-        if (int rc = note_cuda(cudaMemsetAsync(o.workspace, 0, kGemmWorkspaceFlagBytes, stream), "workspace flags")) {
-            return rc;
-        }
+        // the pairs' "parked" flags carry a token no earlier launch used, so the flag area never needs clearing
+        static std::atomic<unsigned> token{0};
+        unsigned t = token.fetch_add(1, std::memory_order_relaxed) + 1;
+        p.tail_token = static_cast<int>((t % 0x7FFFFFFEu) + 1);
     }
     // C leaves through TMA stores when it is 16-byte aligned with a 16-byte row pitch (the rule for any TMA copy)
     constexpr int esize = (EPI == EPI_F32 || EPI == EPI_S32) ? 4 : 2;
@@ -334,7 +339,10 @@ int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& t
     KsplitFusedArgs none;
     std::memset(&none, 0, sizeof(none));
     const KsplitFusedArgs& fa = o.fused ? *o.fused : none;
-    return note_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, ma, mb, tc, p, fa), "gemm_tile_loop_2cta launch");
+    GatherArgs no_gather;
+    std::memset(&no_gather, 0, sizeof(no_gather));
+    const GatherArgs& gargs = o.gather ? *o.gather : no_gather;
+    return note_cuda(cudaLaunchKernelEx(&cfg, kernel, ta, tb, ma, mb, tc, p, fa, gargs), "gemm_tile_loop_2cta launch");
 }
 
 // 128-wide tiles when 256-wide ones would leave SMs without work and the narrower split fills more of them.
@@ -1116,7 +1124,93 @@ extern "C" int pto_b200_ksplit_gemm_allreduce(void* stream, const uint8_t* src0,
     o.out_dtype = PTO_B200_F32;
     o.fused = &fa;
     o.no_tma_store = dev->no_tma_store;
-    const int rc = launch_pair<KIND_F16, EPI_F32, true>(static_cast<cudaStream_t>(stream), ta, tb_half, p, q, o);
+    const int rc = launch_pair<KIND_F16, EPI_F32, COMM_KSPLIT>(static_cast<cudaStream_t>(stream), ta, tb_half, p, q, o);
+    return rc == -1 ? PTO_B200_EDEVICE : rc;
+}
+
+extern "C" int pto_b200_allgather_gemm(void* stream, uint8_t* out, void* const* a_ptrs, const uint8_t* src1, int m, int n,
+                                       int k, long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype,
+                                       void* const* flag_arrays, int* block_counters_local, int* done_counter_local,
+                                       int world, int rank, int epoch, void* multicast_a, int launch_block_count)
+{
+    if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || epoch < 1 || block_counters_local == nullptr ||
+        done_counter_local == nullptr || launch_block_count < 0 || m <= 0) {
+        return PTO_B200_EINVAL;
+    }
+    if (in_dtype != PTO_B200_F16 && in_dtype != PTO_B200_BF16) {
+        return PTO_B200_EDTYPE;
+    }
+    if (!(out_dtype == PTO_B200_F32 || out_dtype == PTO_B200_BF16 || out_dtype == PTO_B200_F16)) {
+        return PTO_B200_EDTYPE;
+    }
+    // every rank's slice is a whole number of 256-row blocks: a block is the unit that is pushed, flagged and waited for
+    if (m % (kPairBlockM * world) != 0) {
+        return PTO_B200_EINVAL;
+    }
+    GatherArgs g;
+    std::memset(&g, 0, sizeof(g));
+    if (int rc = fill_peers(g.a_full, a_ptrs, world)) {
+        return rc;
+    }
+    if (int rc = fill_peers(g.flags, flag_arrays, world)) {
+        return rc;
+    }
+    const uint8_t* a_local = static_cast<const uint8_t*>(a_ptrs[rank]);
+    const Problem q{m, n, k, lda, ldb, ldc};
+    if (int rc = check_common(out, a_local, src1, q, 2, 2, false)) {
+        return rc;
+    }
+    for (int r = 0; r < world; ++r) {
+        if (reinterpret_cast<uintptr_t>(a_ptrs[r]) & 15u) {
+            return PTO_B200_EALIGN;
+        }
+    }
+    if ((k & 7) || (reinterpret_cast<uintptr_t>(multicast_a) & 15u)) { // rows are pushed in 16-byte pieces
+        return PTO_B200_EALIGN;
+    }
+    DeviceInfo* dev = nullptr;
+    if (int rc = device_info(&dev)) {
+        return rc;
+    }
+    g.mc_a = multicast_a;
+    g.block_counter = block_counters_local;
+    g.done_counter = done_counter_local;
+    g.lda_bytes = lda * 2;
+    g.row_bytes = k * 2;
+    g.world = world;
+    g.rank = rank;
+    g.epoch = epoch;
+    g.blocks_per_rank = m / (kPairBlockM * world);
+    const int kelems = kBlockKBytes / 2;
+    GemmParams p;
+    fill_params(p, out, q, kPairBlockN, kelems, dev->status_ptr);
+    const int fmt = (in_dtype == PTO_B200_BF16) ? 1 : 0;
+    p.idesc = make_idesc(1, fmt, fmt, false, kPairBlockN, false, kPairBlockM);
+    CUtensorMap ta, tb_half;
+    if (int rc = make_tensor_map(&ta, in_dtype, a_local, m, k, lda, kelems, kBlockM)) {
+        return rc;
+    }
+    if (int rc = make_tensor_map(&tb_half, in_dtype, src1, n, k, ldb, kelems, kPairBlockN / 2)) {
+        return rc;
+    }
+    PairLaunch o;
+    o.block_limit = launch_block_count;
+    o.out_dtype = out_dtype;
+    o.gather = &g;
+    o.no_tma_store = dev->no_tma_store;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int rc;
+    switch (out_dtype) {
+        case PTO_B200_F32:
+            rc = launch_pair<KIND_F16, EPI_F32, COMM_GATHER>(s, ta, tb_half, p, q, o);
+            break;
+        case PTO_B200_BF16:
+            rc = launch_pair<KIND_F16, EPI_BF16, COMM_GATHER>(s, ta, tb_half, p, q, o);
+            break;
+        default:
+            rc = launch_pair<KIND_F16, EPI_F16, COMM_GATHER>(s, ta, tb_half, p, q, o);
+            break;
+    }
     return rc == -1 ? PTO_B200_EDEVICE : rc;
 }
 
