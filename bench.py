@@ -54,6 +54,13 @@ WORKLOADS = {
     # the largest shape of the reference's AllGather + GEMM table (kernels/manual/a2a3/allgather_gemm/README.md:112-125):
     # A split along M over the ranks, B replicated, every rank computes the whole C; run with --workload at any N
     "allgather_bf16_8192x4096x4096": dict(kind="allgather", m=8192, n=4096, k=4096),
+    # one rank's share of the 8-GPU K-split step on one GPU: the fused kernel with its exchange warps reducing this GPU's
+    # own partial (no peers), the form that can be profiled on a single GPU
+    "ksplit_rank_share_bf16_8192x8192x8192": dict(kind="ksplit1", m=8192, n=8192, k=8192),
+    "bf16_8192": dict(kind="dense", m=8192, n=8192, k=8192, dtype="bf16", out="bf16"),
+    # HBM-bound neighbours of the tile loop (metric GB/s of algorithmic bytes)
+    "gemv_bf16_8192x8192": dict(kind="gemv", m=1, n=8192, k=8192),
+    "mx_quantize_8192x8192": dict(kind="quant", m=8192, n=1, k=8192),
 }
 
 
@@ -433,6 +440,76 @@ def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=8, 
         step.reduce_used = reduce_used
         step.tensors = (a, b, out)
         return step, flops, (m + n) * kr * 2 + m * n * 6, 1
+    if kind == "ksplit1":
+        from pto_isa_mirror_b200.ksplit import KSplitGemmFused
+
+        a = _randn_scaled((m, k), k, torch.bfloat16, gen, dev)
+        b = _randn_scaled((n, k), k, torch.bfloat16, gen, dev)
+        op = KSplitGemmFused(m, n, panels=panels, device=dev)
+
+        def step(i):
+            op.step(a, b)
+
+        def parity():
+            import oracle
+
+            step(0)
+            want = pto.cast_f32_to_bf16(pto.gemm(a, b, torch.float32))
+            torch.cuda.synchronize(dev)
+            same = bool(torch.equal(op.out.view(torch.int16), want.view(torch.int16)))
+            acc, out16, refs = [], [], []
+            for r0, c0 in _tile_origins(m, n, 1, 106):
+                refs.append(oracle.gemm_f32acc(_bits16(a[r0:r0 + 128]), _bits16(b[c0:c0 + 256]), oracle.BF16))
+                acc.append(op.partial[op.epoch & 1][r0:r0 + 128, c0:c0 + 256].cpu().numpy())
+                out16.append(_bits16(op.out[r0:r0 + 128, c0:c0 + 256]))
+            rep = _dense_tile_report(acc, out16, refs, 1e-3)
+            rep["equals_plain_gemm_then_cast"] = same
+            rep["ok"] = bool(rep["ok"] and same)
+            return rep
+
+        step.parity = parity
+        step.reduce_used = "fused_one_kernel_single_rank"
+        return step, flops, (m + n) * k * 2 + m * n * 6, 1
+    if kind == "gemv":
+        mats = [_randn_scaled((n, k), k, torch.bfloat16, gen, dev) for _ in range(4)]      # 512 MiB > L2
+        x = _randn_scaled((k,), k, torch.bfloat16, gen, dev)
+        y = torch.empty((n,), dtype=torch.float32, device=dev)
+
+        def step(i):
+            pto.gemv(x, mats[i % 4], out=y)
+
+        def parity():
+            import oracle
+
+            pto.gemv(x, mats[0], out=y)
+            torch.cuda.synchronize(dev)
+            ref = oracle.gemm_f32acc(_bits16(x.view(1, k)), _bits16(mats[0][:2048]), oracle.BF16)[0]
+            err = float(np.abs(y[:2048].cpu().numpy() - ref).max() / np.abs(ref).max())
+            return {"rows": 2048, "max_rel_err": err, "tol": 1e-3, "ok": bool(err <= 1e-3)}
+
+        step.parity = parity
+        step.bytes = n * k * 2 + k * 2 + n * 4
+        return step, 2.0 * n * k, 4 * n * k * 2, 4
+    if kind == "quant":
+        srcs = [torch.randn((m, k), generator=gen, device=dev) for _ in range(2)]             # 512 MiB > L2
+        q_data = torch.empty((m, k), dtype=torch.uint8, device=dev)
+        q_scales = torch.empty((m, k // 32), dtype=torch.uint8, device=dev)
+
+        def step(i):
+            pto.mx_quantize_e4m3(srcs[i % 2], data=q_data, scales=q_scales)
+
+        def parity():
+            import oracle
+
+            pto.mx_quantize_e4m3(srcs[0], data=q_data, scales=q_scales)
+            torch.cuda.synchronize(dev)
+            rd, rs = oracle.mx_quantize_e4m3(srcs[0][:256].cpu().numpy())
+            exact = bool(np.array_equal(q_data[:256].cpu().numpy(), rd) and np.array_equal(q_scales[:256].cpu().numpy(), rs))
+            return {"rows": 256, "bit_exact": exact, "ok": exact}
+
+        step.parity = parity
+        step.bytes = int(m * k * (4 + 1 + 1 / 32))
+        return step, 0.0, 2 * m * k * 4, 2
     if kind == "allgather":
         import torch.distributed as dist
 
@@ -796,9 +873,9 @@ def main():
     tflops = flops / (ms_per_step * 1e-3) / 1e12
 
     kind = spec["kind"]
-    dtype = {"dense": spec.get("dtype", "bf16"), "ksplit": "bf16", "allgather": "bf16", "s8": "s8",
-             "mx": "mxfp8_e4m3"}[kind]
-    peak_scale = {"dense": 1.0, "ksplit": 1.0, "allgather": 1.0, "s8": 2.0, "mx": 2.0}[kind]
+    dtype = {"dense": spec.get("dtype", "bf16"), "ksplit": "bf16", "ksplit1": "bf16", "allgather": "bf16", "s8": "s8",
+             "mx": "mxfp8_e4m3", "gemv": "bf16", "quant": "f32"}[kind]
+    peak_scale = {"s8": 2.0, "mx": 2.0}.get(kind, 1.0)
     # a single kernel timed back to back for a short region: burst peak; the long K-split step: sustained
     peak_key = "bf16_tflops" if ms < 500.0 else "bf16_tflops_sustained"
     peak = float(peaks.get(peak_key, FALLBACK_PEAKS["bf16_tflops"])) * peak_scale
@@ -845,6 +922,14 @@ def main():
     if par is not None:
         line["parity"] = par
 
+    if kind in ("gemv", "quant"):
+        # HBM-bound neighbours: GB/s of algorithmic bytes against the measured copy bandwidth
+        gbs = step.bytes / (ms_per_step * 1e-3) / 1e9
+        hbm = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+        line.update({"metric": "hbm_gbs", "value": gbs, "unit": "GB/s"})
+        line["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm,
+                            "traffic": ncu_dram_traffic(name), "peak_source": f"{peaks['_source']}: hbm_gbs",
+                            "algorithmic_bytes": step.bytes, "per": "GPU"}
     if rank == 0 and world == 1 and not args.no_extras:
         # end to end through the host-buffer API: H2D of A and B, one launch, D2H of C, every step
         if kind == "dense":
