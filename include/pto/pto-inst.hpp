@@ -456,6 +456,39 @@ PTO_INST RecordEvent TMATMUL_MX(TileRes& cOutMatrix, TileRes& cInMatrix, TileLef
     return {};
 }
 
+// TGEMV_MX (include/pto/common/pto_instr.hpp:797-862): the block-scaled forms with a one-row left tile; TSTORE then
+// streams B and its scales once (pto_b200_gemv_mx) instead of running 128-row tensor-core tiles.
+template <AccPhase Phase = AccPhase::Unspecified, typename TileRes, typename TileLeft_, typename TileLeftScale_,
+          typename TileRight_, typename TileRightScale_>
+PTO_INST RecordEvent TGEMV_MX(TileRes& cMatrix, TileLeft_& aMatrix, TileLeftScale_& aScaleMatrix, TileRight_& bMatrix,
+                              TileRightScale_& bScaleMatrix)
+{
+    TMATMUL_MX<Phase>(cMatrix, aMatrix, aScaleMatrix, bMatrix, bScaleMatrix);
+    cMatrix.one_row = true;
+    return {};
+}
+
+template <AccPhase Phase = AccPhase::Unspecified, typename TileRes, typename TileLeft_, typename TileLeftScale_,
+          typename TileRight_, typename TileRightScale_, std::enable_if_t<TileRight_::Loc == TileType::Right, int> = 0>
+PTO_INST RecordEvent TGEMV_MX(TileRes& cOutMatrix, TileRes& cInMatrix, TileLeft_& aMatrix, TileLeftScale_& aScaleMatrix,
+                              TileRight_& bMatrix, TileRightScale_& bScaleMatrix)
+{
+    TMATMUL_MX<Phase>(cOutMatrix, cInMatrix, aMatrix, aScaleMatrix, bMatrix, bScaleMatrix);
+    cOutMatrix.one_row = (&cOutMatrix == &cInMatrix) ? cOutMatrix.one_row : cInMatrix.one_row;
+    return {};
+}
+
+template <AccPhase Phase = AccPhase::Unspecified, typename TileRes, typename TileLeft_, typename TileLeftScale_,
+          typename TileRight_, typename TileRightScale_, typename TileBias_,
+          std::enable_if_t<TileBias_::Loc == TileType::Bias, int> = 0>
+PTO_INST RecordEvent TGEMV_MX(TileRes& cMatrix, TileLeft_& aMatrix, TileLeftScale_& aScaleMatrix, TileRight_& bMatrix,
+                              TileRightScale_& bScaleMatrix, TileBias_& biasData)
+{
+    TMATMUL_MX<Phase>(cMatrix, aMatrix, aScaleMatrix, bMatrix, bScaleMatrix, biasData);
+    cMatrix.one_row = true;
+    return {};
+}
+
 namespace b200 {
 // true if `next` continues `prev` along K: A windows side by side in a row-major matrix.
 inline bool a_continues(const View& prev, const View& next)
@@ -551,7 +584,14 @@ inline void store_chain(GlobalData& dst, TileAcc_& src, const StoreQuant& quant)
         }
         const long long ld_sfa = sa.row_stride, ld_sfb = sb.col_stride;
         const Workspace& ws = current_workspace();
-        if (src.bias.bound()) {
+        rc = PTO_B200_EALIGN;
+        if (src.one_row && m == 1) { // TGEMV_MX: no workspace, no tensor-core tile
+            rc = pto_b200_gemv_mx(stream, out, a.ptr, b.ptr, sa.ptr, sb.ptr, src.bias.ptr, n, k, ldb, ld_sfb, first.a_dtype,
+                                  first.b_dtype, dtype_of<OutT>::value);
+        }
+        if (rc != PTO_B200_EALIGN) {
+            // launched (or rejected for a reason other than the row's alignment)
+        } else if (src.bias.bound()) {
             if (ws.ptr == nullptr) {
                 fail("TSTORE: the bias form of TMATMUL_MX needs scratch: call pto::b200::set_workspace first", 0);
                 return;

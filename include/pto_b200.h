@@ -164,6 +164,22 @@ int pto_b200_gemm_mx(void* stream, uint8_t* out, const uint8_t* src0, const uint
 size_t pto_b200_gemm_mx_workspace_bytes(int m, int n, int k);
 
 /*
+ * pto_b200_gemm_mx in two steps, for scales that do not change between calls (the weights' scales) or that a producer
+ * can write in the tiled form directly: pto_b200_mx_retile_scales fills the workspace from the reference-layout scale
+ * tensors (the two small re-tile kernels, 3.6 % of a 16384 x 8192 x 8192 call), pto_b200_gemm_mx_pretiled multiplies
+ * with a workspace that was filled earlier for the same m, n, k. The reference's counterpart are its pre-tiled scale
+ * layouts, Layout::MX_A_ZZ / Layout::MX_B_NN (include/pto/common/pto_tile.hpp:849-881,943-975), whose fractal order
+ * belongs to its L0 scale buffers; here the order is the one tcgen05.cp copies into tensor memory: 512-byte atoms
+ * (k_block of 128, 128-row block), byte (r % 32) * 16 + (r / 32) * 4 + j for row r and K group j; all A atoms first
+ * (2 * ceil(m / 256) row blocks per k_block), then B's (2 * ceil(n / 256)); rows and groups past the end hold 127.
+ */
+int pto_b200_mx_retile_scales(void* stream, uint8_t* workspace, size_t workspace_bytes, const uint8_t* src2,
+                              const uint8_t* src3, int m, int n, int k, long long ld_sfa, long long ld_sfb);
+int pto_b200_gemm_mx_pretiled(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1,
+                              const uint8_t* tiled_scales, size_t tiled_bytes, int m, int n, int k, long long lda,
+                              long long ldb, long long ldc, int a_dtype, int b_dtype, int out_dtype);
+
+/*
  * pto_b200_gemm_mx with an fp32 bias row added to the finished accumulator: the six-operand TMATMUL_MX
  * (c, a, a_scale, b, b_scale, bias), include/pto/common/pto_instr.hpp:918-942, include/pto/cpu/TMatmul.hpp:271-292.
  * bias : n floats in device memory.
@@ -222,6 +238,20 @@ int pto_b200_gemv(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t
                   int k, long long ldb, int in_dtype, int out_dtype);
 
 /*
+ * One left row against a block-scaled fp8 matrix:
+ *   out[j] = sum_k a[k] * B[k][j] * 2^(SA[k/32] - 127) * 2^(SB[j][k/32] - 127)  (+ bias[j]).
+ * Replaces: TGEMV_MX (include/pto/common/pto_instr.hpp:797-862: plain, accumulating and bias forms;
+ * include/pto/cpu/TMatmul.hpp:294-326, the TMATMUL_MX arithmetic with a one-row left tile).
+ *   src0 : the left row, k fp8 bytes, 16-byte aligned;      src2 : its k / 32 e8m0 scales
+ *   src1 : B column-major (n runs of k bytes, leading dimension ldb, a multiple of 16); src3 : its scales [n][ld_sfb]
+ *   bias : n floats or null; a_dtype / b_dtype E4M3 or E5M2 (any mix); out_dtype F32 or BF16; k % 32 == 0.
+ * Bandwidth-bound like pto_b200_gemv: B and its scales are streamed once, no tensor-core tile.
+ */
+int pto_b200_gemv_mx(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, const uint8_t* src2,
+                     const uint8_t* src3, const uint8_t* bias, int n, int k, long long ldb, long long ld_sfb, int a_dtype,
+                     int b_dtype, int out_dtype);
+
+/*
  * OCP MX quantisation of fp32 rows into e4m3 bytes and e8m0 block scales (one per 32 elements along k): the
  * producer of pto_b200_gemm_mx's src0 / src2 (or src1 / src3) operands.
  * Replaces: TQUANT<QuantType::MXFP8> with the OCP scale rule (include/pto/common/pto_instr.hpp:2981-3035;
@@ -233,6 +263,17 @@ int pto_b200_gemv(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t
  */
 int pto_b200_mx_quantize_e4m3(void* stream, uint8_t* data, uint8_t* scales, const uint8_t* src, int rows, int k,
                               long long ld_src, long long ld_data, long long ld_scales);
+
+/*
+ * The same with the scale rule as an argument: QuantScaleAlg::OCP or QuantScaleAlg::NV (include/pto/common/type.hpp:205-208).
+ * NV (include/pto/cpu/TQuant.hpp:33-37,194-211,239-248, the NV form of EncodeE4M3Fn :118-131): the block scale is the
+ * smallest power of two that brings absmax to at most 448 (e8m0 = biased exponent of absmax / 448, rounded up), and
+ * scaled values below 2^-10 in magnitude are stored as zeros that keep their sign. Bit-identical to the reference for
+ * finite input.
+ */
+typedef enum { PTO_B200_SCALE_OCP = 0, PTO_B200_SCALE_NV = 1 } pto_b200_scale_alg;
+int pto_b200_mx_quantize_e4m3_ex(void* stream, uint8_t* data, uint8_t* scales, const uint8_t* src, int rows, int k,
+                                 long long ld_src, long long ld_data, long long ld_scales, int scale_alg);
 
 /*
  * K-split reduction over peer memory: the reduce-scatter / all-gather half of the reference's GEMM + AllReduce

@@ -590,7 +590,11 @@ static uint8_t encode_e4m3fn(float v)
     return (uint8_t)(code | (signbit(c) ? 0x80u : 0u));
 }
 
-void pto_oracle_mx_quantize_e4m3(const float* src, uint8_t* data, uint8_t* scales, int rows, int k, long long ld)
+/* scale_alg 0: OCP rule (ComputeSharedExponent, cpu/TQuant.hpp:178-190); 1: NV rule (ComputeNvSharedExponent with the
+   e4m3 spec, :33-37,:194-211: e8m0 = ceil(log2(amax / 448)) as a biased exponent; scaling :239-248; the NV form of the
+   element encoder keeps the sign of values below 2^-10, :118-131). */
+void pto_oracle_mx_quantize_e4m3_alg(const float* src, uint8_t* data, uint8_t* scales, int rows, int k, long long ld,
+                                     int scale_alg)
 {
     const int groups = k / 32;
     for (int r = 0; r < rows; ++r) {
@@ -603,19 +607,58 @@ void pto_oracle_mx_quantize_e4m3(const float* src, uint8_t* data, uint8_t* scale
                     amax = ax;
                 }
             }
-            /* ComputeSharedExponent: biased exponent of the block maximum minus 8, floored at 0 */
-            const uint32_t bits = float_to_bits(amax);
-            const uint32_t exponent = (bits & 0x7F800000u) >> 23;
-            const uint8_t e8m0 = (exponent <= 8u) ? 0u : (uint8_t)(exponent - 8u);
-            /* ComputeMxScalingFromExponent: 2^(127 - e8m0), with the zero bit pattern replaced by 2^-127 */
-            float scaling = bits_to_float((254u - (uint32_t)e8m0) << 23);
-            if (scaling == 0.0f) {
-                scaling = ldexpf(1.0f, -127);
+            uint8_t e8m0;
+            float scaling;
+            if (scale_alg == 0) {
+                /* ComputeSharedExponent: biased exponent of the block maximum minus 8, floored at 0 */
+                const uint32_t bits = float_to_bits(amax);
+                const uint32_t exponent = (bits & 0x7F800000u) >> 23;
+                e8m0 = (exponent <= 8u) ? 0u : (uint8_t)(exponent - 8u);
+                /* ComputeMxScalingFromExponent: 2^(127 - e8m0), with the zero bit pattern replaced by 2^-127 */
+                scaling = bits_to_float((254u - (uint32_t)e8m0) << 23);
+                if (scaling == 0.0f) {
+                    scaling = ldexpf(1.0f, -127);
+                }
+            } else {
+                e8m0 = 0;
+                if (amax != 0.0f) {
+                    volatile float descale = amax * (1.0f / 448.0f);
+                    const uint32_t bits = float_to_bits(descale);
+                    const uint32_t exponent = (bits & 0x7F800000u) >> 23;
+                    const uint32_t mantissa = bits & 0x007FFFFFu;
+                    if (exponent == 0xFFu) {
+                        e8m0 = mantissa == 0u ? 0xFEu : 0xFFu;
+                    } else {
+                        const int round_up = mantissa > 0u && exponent != 0xFEu && !(exponent == 0u && mantissa <= 0x00400000u);
+                        e8m0 = (uint8_t)(exponent + (round_up ? 1u : 0u));
+                    }
+                }
+                if (e8m0 == 0xFFu) {
+                    scaling = amax; /* NaN block */
+                } else if (e8m0 == 0xFEu) {
+                    scaling = ldexpf(1.0f, -127);
+                } else {
+                    scaling = bits_to_float((254u - (uint32_t)e8m0) << 23);
+                    if (scaling == 0.0f) {
+                        scaling = ldexpf(1.0f, -127);
+                    }
+                }
             }
             scales[(size_t)r * groups + g] = e8m0;
             for (int i = 0; i < 32; ++i) {
-                data[(size_t)r * k + (size_t)g * 32 + i] = encode_e4m3fn(x[i] * scaling);
+                volatile float y = x[i] * scaling;
+                const float yv = y;
+                if (scale_alg != 0 && !isnan(yv) && fabsf(yv) < 0.0009765625f) {
+                    data[(size_t)r * k + (size_t)g * 32 + i] = signbit(yv) ? 0x80u : 0x00u;
+                } else {
+                    data[(size_t)r * k + (size_t)g * 32 + i] = encode_e4m3fn(yv);
+                }
             }
         }
     }
+}
+
+void pto_oracle_mx_quantize_e4m3(const float* src, uint8_t* data, uint8_t* scales, int rows, int k, long long ld)
+{
+    pto_oracle_mx_quantize_e4m3_alg(src, data, scales, rows, k, ld, 0);
 }

@@ -356,6 +356,29 @@ void ref_mx_quantize_e4m3(const float* src, uint8_t* data, uint8_t* scales, int 
     }
 }
 
+// The same with the NV scale rule (include/pto/cpu/TQuant.hpp:194-211 ComputeNvSharedExponent with the e4m3 spec
+// :33-37, :239-248 ComputeNvScalingFromExponent, :118-131 EncodeE4M3Fn<NV>).
+void ref_mx_quantize_e4m3_nv(const float* src, uint8_t* data, uint8_t* scales, int rows, int k)
+{
+    using namespace pto::cpu_quant;
+    const int groups = k / 32;
+    for (int r = 0; r < rows; ++r) {
+        for (int g = 0; g < groups; ++g) {
+            const float* x = src + static_cast<size_t>(r) * k + g * 32;
+            float amax = 0.0f;
+            for (int i = 0; i < 32; ++i) {
+                amax = std::max(amax, std::fabs(x[i]));
+            }
+            const uint8_t e = ComputeMxSharedExponent<QuantType::MXFP8, QuantScaleAlg::NV>(amax);
+            const float scaling = ComputeMxGroupScaling<QuantType::MXFP8, QuantScaleAlg::NV>(amax, e);
+            scales[static_cast<size_t>(r) * groups + g] = e;
+            for (int i = 0; i < 32; ++i) {
+                data[static_cast<size_t>(r) * k + g * 32 + i] = EncodeE4M3Fn<QuantScaleAlg::NV>(x[i] * scaling);
+            }
+        }
+    }
+}
+
 double ref_fp8_to_double(uint8_t raw, int fmt)
 {
     return fmt == 6 ? static_cast<double>(float8_e5m2_t::FromRaw(raw)) : static_cast<double>(float8_e4m3_t::FromRaw(raw));

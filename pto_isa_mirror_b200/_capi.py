@@ -18,6 +18,8 @@ B_DN, B_ND = 0, 1
 # return codes
 OK, EINVAL, EALIGN, EDTYPE, EWORKSPACE, ECUDA, EDEVICE, ETIMEOUT, ESCRATCH = range(9)
 MX_STATIC_SCRATCH_BYTES = 8 * 1024 * 1024
+# pto_b200_scale_alg
+SCALE_OCP, SCALE_NV = 0, 1
 
 # every symbol include/pto_b200.h declares: name -> (restype, argtypes)
 _u8p = ctypes.c_void_p
@@ -54,8 +56,15 @@ SYMBOLS = {
          _ll, _i, _i, _i],
     ),
     "pto_b200_gemm_mx_workspace_bytes": (ctypes.c_size_t, [_i, _i, _i]),
+    "pto_b200_mx_retile_scales": (_i, [ctypes.c_void_p, _u8p, ctypes.c_size_t, _u8p, _u8p, _i, _i, _i, _ll, _ll]),
+    "pto_b200_gemm_mx_pretiled": (
+        _i,
+        [ctypes.c_void_p, _u8p, _u8p, _u8p, _u8p, ctypes.c_size_t, _i, _i, _i, _ll, _ll, _ll, _i, _i, _i],
+    ),
     "pto_b200_gemv": (_i, [ctypes.c_void_p, _u8p, _u8p, _u8p, _u8p, _i, _i, _ll, _i, _i]),
+    "pto_b200_gemv_mx": (_i, [ctypes.c_void_p, _u8p, _u8p, _u8p, _u8p, _u8p, _u8p, _i, _i, _ll, _ll, _i, _i, _i]),
     "pto_b200_mx_quantize_e4m3": (_i, [ctypes.c_void_p, _u8p, _u8p, _u8p, _i, _i, _ll, _ll, _ll]),
+    "pto_b200_mx_quantize_e4m3_ex": (_i, [ctypes.c_void_p, _u8p, _u8p, _u8p, _i, _i, _ll, _ll, _ll, _i]),
     "pto_b200_gemm_mx_static": (
         _i,
         [ctypes.c_void_p, _u8p, _u8p, _u8p, _u8p, _u8p, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _i, _i, _i],

@@ -14,7 +14,7 @@ CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_DIR = os.path.join(PKG_DIR, "lib")
 LIB = os.path.join(LIB_DIR, "libpto_b200.so")
 SOURCES = ["pto_b200_capi.cu"]
-HEADERS = ["gemm_tile_loop.cuh", "gemm_tile_loop_2cta.cuh", "gemv.cuh", "ksplit_reduce.cuh", "mx_quantize.cuh",
+HEADERS = ["gemm_tile_loop.cuh", "gemm_tile_loop_2cta.cuh", "gemv.cuh", "gemv_mx.cuh", "ksplit_reduce.cuh", "mx_quantize.cuh",
            "sm100_ptx.cuh", os.path.join("..", "..", "include", "pto_b200.h")]
 
 NVCC_FLAGS = [

@@ -49,8 +49,10 @@ struct GemmParams {
     uint32_t idesc;
     const float* s_row;
     const float* s_col;
-    const uint8_t* sfa; // scale factors re-tiled to 512-byte atoms, index (k_block, m_block)
-    const uint8_t* sfb; // same, index (k_block, n_block)
+    const uint8_t* sfa; // scale factors re-tiled to 512-byte atoms, index (k_block, 128-row block of A)
+    const uint8_t* sfb; // same, index (k_block, 128-column block of B)
+    int sf_a_blocks;    // 128-row blocks per k_block in sfa (the same for every kernel: 2 * ceil(m / 256))
+    int sf_b_blocks;    // 128-column blocks per k_block in sfb (2 * ceil(n / 256))
     const void* bias;   // TMATMUL_BIAS: one value per output column in the accumulator's type (fp32 / int32), or null
     int* status;
     // CTA-pair kernels, last partly filled wave: each leftover tile is cut in two K halves that run on two pairs at
@@ -388,9 +390,9 @@ __global__ void __launch_bounds__(kNumThreads, 1)
                     }
                     if constexpr (KIND == KIND_MXF8) {
                         constexpr int kNB = L::kSfbBytes / 512;
-                        const uint8_t* sfa_src = p.sfa + (static_cast<size_t>(kb) * p.m_tiles + mi) * 512;
+                        const uint8_t* sfa_src = p.sfa + (static_cast<size_t>(kb) * p.sf_a_blocks + mi) * 512;
                         const uint8_t* sfb_src =
-                            p.sfb + (static_cast<size_t>(kb) * p.n_tiles + ni) * static_cast<size_t>(kNB) * 512;
+                            p.sfb + (static_cast<size_t>(kb) * p.sf_b_blocks + static_cast<size_t>(ni) * kNB) * 512;
                         ptx::bulk_load_1d(smem + L::kSfaOff + stage * L::kSfaBytes, sfa_src, L::kSfaBytes,
                                           &full_bar[stage]);
                         ptx::bulk_load_1d(smem + L::kSfbOff + stage * L::kSfbBytes, sfb_src, L::kSfbBytes,

@@ -8,6 +8,10 @@
 //   scaling = 2^(127 - e8m0)
 //   byte    = nearest e4m3fn code of clamp(x * scaling, +-448), ties to the even code; a result that rounds to zero
 //             is stored as +0 (0x00) whatever its sign.
+// With the NV scale rule (ComputeNvSharedExponent with the e4m3 spec, TQuant.hpp:33-37,194-211; scaling :239-248; the
+// NV form of EncodeE4M3Fn :118-131):
+//   e8m0    = biased exponent of absmax / 448, plus one unless absmax / 448 is a power of two (0 for an all-zero block)
+//   byte    = as above, except that a scaled value below 2^-10 in magnitude is stored as a zero WITH its sign.
 // Inputs must be finite (a NaN or infinity in a block is outside the supported domain).
 //
 // HBM-bound: 4 bytes read and 1 + 1/32 bytes written per element. Eight consecutive lanes own one block of 32
@@ -42,6 +46,9 @@ constexpr int kQuantItems = 4; // 16-byte loads in flight per thread
 
 // src: [rows][ld_src] floats (16-byte aligned rows); data: [rows][ld_data] bytes (4-byte aligned rows);
 // scales: [rows][ld_scales] bytes. k % 32 == 0.
+enum MxScaleAlg : int { MX_SCALE_OCP = 0, MX_SCALE_NV = 1 };
+
+template <int ALG>
 __global__ void __launch_bounds__(kQuantThreads) mx_quantize_e4m3_kernel(const float* __restrict__ src,
                                                                           uint8_t* __restrict__ data,
                                                                           uint8_t* __restrict__ scales, int rows, int k,
@@ -89,12 +96,32 @@ __global__ void __launch_bounds__(kQuantThreads) mx_quantize_e4m3_kernel(const f
             amax = fmaxf(amax, __shfl_xor_sync(group_mask, amax, 1));
             amax = fmaxf(amax, __shfl_xor_sync(group_mask, amax, 2));
             amax = fmaxf(amax, __shfl_xor_sync(group_mask, amax, 4));
-            const uint32_t exponent = (__float_as_uint(amax) & 0x7F800000u) >> 23;
-            const uint32_t e8m0 = exponent <= 8u ? 0u : exponent - 8u;
+            uint32_t e8m0;
+            if constexpr (ALG == MX_SCALE_OCP) {
+                const uint32_t exponent = (__float_as_uint(amax) & 0x7F800000u) >> 23;
+                e8m0 = exponent <= 8u ? 0u : exponent - 8u;
+            } else {
+                const uint32_t bits = __float_as_uint(__fmul_rn(amax, 1.0f / 448.0f));
+                const uint32_t exponent = (bits & 0x7F800000u) >> 23;
+                const uint32_t mantissa = bits & 0x007FFFFFu;
+                const bool round_up = mantissa > 0u && !(exponent == 0u && mantissa <= 0x00400000u);
+                e8m0 = (amax == 0.0f) ? 0u : exponent + (round_up ? 1u : 0u);
+            }
             const float scaling = __uint_as_float((254u - e8m0) << 23); // e8m0 <= 246 for finite input: never zero
-            const uint32_t lo = cvt_e4m3x2(__fmul_rn(v[u].x, scaling), __fmul_rn(v[u].y, scaling));
-            const uint32_t hi = cvt_e4m3x2(__fmul_rn(v[u].z, scaling), __fmul_rn(v[u].w, scaling));
-            const uint32_t packed = drop_negative_zero(lo | (hi << 16));
+            const float y0 = __fmul_rn(v[u].x, scaling), y1 = __fmul_rn(v[u].y, scaling);
+            const float y2 = __fmul_rn(v[u].z, scaling), y3 = __fmul_rn(v[u].w, scaling);
+            const uint32_t lo = cvt_e4m3x2(y0, y1);
+            const uint32_t hi = cvt_e4m3x2(y2, y3);
+            uint32_t packed = lo | (hi << 16);
+            if constexpr (ALG == MX_SCALE_OCP) {
+                packed = drop_negative_zero(packed);
+            } else {
+                // values below 2^-10 keep their sign as +-0 (what the conversion gives); a value of exactly -2^-10 is a
+                // tie that the reference's search resolves to +0
+                constexpr float kTie = -0.0009765625f;
+                packed &= ~((y0 == kTie ? 0x80u : 0u) | (y1 == kTie ? 0x8000u : 0u) | (y2 == kTie ? 0x800000u : 0u) |
+                            (y3 == kTie ? 0x80000000u : 0u));
+            }
             *reinterpret_cast<uint32_t*>(data + row[u] * ld_data + static_cast<long long>(c4[u]) * 4) = packed;
             if ((c4[u] & 7) == 0) {
                 scales[row[u] * ld_scales + (c4[u] >> 3)] = static_cast<uint8_t>(e8m0);

@@ -14,6 +14,7 @@
 #include "gemm_tile_loop.cuh"
 #include "gemm_tile_loop_2cta.cuh"
 #include "gemv.cuh"
+#include "gemv_mx.cuh"
 #include "ksplit_reduce.cuh"
 #include "mx_quantize.cuh"
 
@@ -697,10 +698,13 @@ static int mx_check_args(const uint8_t* out, const uint8_t* src0, const uint8_t*
     return PTO_B200_OK;
 }
 
+// What a call of the block-scaled path does: re-tile the scales into the workspace, multiply, or both.
+enum MxSteps : int { MX_RETILE = 1, MX_MULTIPLY = 2 };
+
 static int gemm_mx_impl(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, const uint8_t* src2,
                         const uint8_t* src3, uint8_t* workspace, size_t workspace_bytes, int m, int n, int k,
                         long long lda, long long ldb, long long ldc, long long ld_sfa, long long ld_sfb, int a_dtype,
-                        int b_dtype, int out_dtype, const void* bias)
+                        int b_dtype, int out_dtype, const void* bias, int steps = MX_RETILE | MX_MULTIPLY)
 {
     if (int rc = mx_check_args(out, src0, src1, src2, src3, m, n, k, lda, ldb, ldc, ld_sfa, ld_sfb, a_dtype, b_dtype,
                                out_dtype, bias)) {
@@ -723,19 +727,20 @@ static int gemm_mx_impl(void* stream, uint8_t* out, const uint8_t* src0, const u
     auto run = [&](bool pairs, int block_n) -> int {
         GemmParams p;
         fill_params(p, out, q, block_n, kBlockKBytes, dev->status_ptr);
-        int a_blocks = p.m_tiles;
-        int b_blocks = p.n_tiles * (block_n / 128);
+        // one layout of the re-tiled scales whatever kernel reads them: 128-row blocks counted in pairs
+        const int a_blocks = 2 * ((m + kPairBlockM - 1) / kPairBlockM);
+        const int b_blocks = 2 * ((n + kPairBlockN - 1) / kPairBlockN);
         if (pairs) {
             p.m_tiles = (m + kPairBlockM - 1) / kPairBlockM;
             p.n_tiles = (n + kPairBlockN - 1) / kPairBlockN;
-            a_blocks = 2 * p.m_tiles;
-            b_blocks = 2 * p.n_tiles;
         }
         uint8_t* sfa_ws = workspace;
         uint8_t* sfb_ws = workspace + static_cast<size_t>(p.k_blocks) * a_blocks * 512;
         p.bias = bias;
         p.sfa = sfa_ws;
         p.sfb = sfb_ws;
+        p.sf_a_blocks = a_blocks;
+        p.sf_b_blocks = b_blocks;
         CUtensorMap ta, tb, tsa, tsb;
         if (int rc = make_tensor_map(&ta, a_dtype, src0, m, k, lda, kBlockKBytes, kBlockM)) {
             return rc;
@@ -761,11 +766,16 @@ static int gemm_mx_impl(void* stream, uint8_t* out, const uint8_t* src0, const u
         const long long tb_items = static_cast<long long>(b_blocks) * p.k_blocks * 128;
         const int ga = static_cast<int>((ta_items + 255) / 256 < 4096 ? (ta_items + 255) / 256 : 4096);
         const int gb = static_cast<int>((tb_items + 255) / 256 < 4096 ? (tb_items + 255) / 256 : 4096);
-        retile_scales_kernel<<<ga, 256, 0, s>>>(src2, sfa_ws, m, k / 32, ld_sfa, a_blocks, p.k_blocks);
-        retile_scales_kernel<<<gb, 256, 0, s>>>(src3, sfb_ws, n, k / 32, ld_sfb, b_blocks, p.k_blocks);
-        g_launches.fetch_add(2, std::memory_order_relaxed);
-        if (int rc = note_cuda(cudaGetLastError(), "retile_scales launch")) {
-            return rc;
+        if (steps & MX_RETILE) {
+            retile_scales_kernel<<<ga, 256, 0, s>>>(src2, sfa_ws, m, k / 32, ld_sfa, a_blocks, p.k_blocks);
+            retile_scales_kernel<<<gb, 256, 0, s>>>(src3, sfb_ws, n, k / 32, ld_sfb, b_blocks, p.k_blocks);
+            g_launches.fetch_add(2, std::memory_order_relaxed);
+            if (int rc = note_cuda(cudaGetLastError(), "retile_scales launch")) {
+                return rc;
+            }
+        }
+        if (!(steps & MX_MULTIPLY)) {
+            return PTO_B200_OK;
         }
         if (pairs) {
             PairLaunch o;
@@ -801,6 +811,26 @@ extern "C" int pto_b200_gemm_mx(void* stream, uint8_t* out, const uint8_t* src0,
 {
     return gemm_mx_impl(stream, out, src0, src1, src2, src3, workspace, workspace_bytes, m, n, k, lda, ldb, ldc, ld_sfa,
                         ld_sfb, a_dtype, b_dtype, out_dtype, nullptr);
+}
+
+extern "C" int pto_b200_mx_retile_scales(void* stream, uint8_t* workspace, size_t workspace_bytes, const uint8_t* src2,
+                                         const uint8_t* src3, int m, int n, int k, long long ld_sfa, long long ld_sfb)
+{
+    // the operand pointers are not touched by this step: any aligned non-null value passes the shared checks
+    const uint8_t* aligned = reinterpret_cast<const uint8_t*>(static_cast<uintptr_t>(16));
+    return gemm_mx_impl(stream, const_cast<uint8_t*>(aligned), aligned, aligned, src2, src3, workspace, workspace_bytes, m,
+                        n, k, k, k, n, ld_sfa, ld_sfb, PTO_B200_E4M3, PTO_B200_E4M3, PTO_B200_BF16, nullptr, MX_RETILE);
+}
+
+extern "C" int pto_b200_gemm_mx_pretiled(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1,
+                                         const uint8_t* tiled_scales, size_t tiled_bytes, int m, int n, int k,
+                                         long long lda, long long ldb, long long ldc, int a_dtype, int b_dtype,
+                                         int out_dtype)
+{
+    // the scale tensors themselves are not read: the workspace already holds them re-tiled
+    const uint8_t* unused = reinterpret_cast<const uint8_t*>(static_cast<uintptr_t>(16));
+    return gemm_mx_impl(stream, out, src0, src1, unused, unused, const_cast<uint8_t*>(tiled_scales), tiled_bytes, m, n, k,
+                        lda, ldb, ldc, k / 32, k / 32, a_dtype, b_dtype, out_dtype, nullptr, MX_MULTIPLY);
 }
 
 extern "C" int pto_b200_gemm_mx_bias(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1,
@@ -907,12 +937,70 @@ extern "C" int pto_b200_gemv(void* stream, uint8_t* out, const uint8_t* src0, co
     return launch_gemv<GEMV_F16>(s, grid, out_dtype, src0, src1, bias, out, n, k, ldb);
 }
 
-extern "C" int pto_b200_mx_quantize_e4m3(void* stream, uint8_t* data, uint8_t* scales, const uint8_t* src, int rows,
-                                         int k, long long ld_src, long long ld_data, long long ld_scales)
+template <bool A52, bool B52>
+static int launch_gemv_mx(cudaStream_t s, int grid, int out_dtype, const uint8_t* a, const uint8_t* sa, const uint8_t* b,
+                          const uint8_t* sb, const float* bias, void* out, int n, int k, long long ldb, long long ld_sfb)
+{
+    if (out_dtype == PTO_B200_F32) {
+        gemv_mx_kernel<A52, B52, GEMV_OUT_F32><<<grid, kGemvThreads, 0, s>>>(a, sa, b, sb, bias, out, n, k, ldb, ld_sfb);
+    } else {
+        gemv_mx_kernel<A52, B52, GEMV_OUT_BF16><<<grid, kGemvThreads, 0, s>>>(a, sa, b, sb, bias, out, n, k, ldb, ld_sfb);
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return note_cuda(cudaGetLastError(), "gemv_mx launch");
+}
+
+extern "C" int pto_b200_gemv_mx(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, const uint8_t* src2,
+                                const uint8_t* src3, const uint8_t* bias, int n, int k, long long ldb, long long ld_sfb,
+                                int a_dtype, int b_dtype, int out_dtype)
+{
+    const bool a_ok = (a_dtype == PTO_B200_E4M3 || a_dtype == PTO_B200_E5M2);
+    const bool b_ok = (b_dtype == PTO_B200_E4M3 || b_dtype == PTO_B200_E5M2);
+    if (!a_ok || !b_ok || !(out_dtype == PTO_B200_F32 || out_dtype == PTO_B200_BF16)) {
+        return PTO_B200_EDTYPE;
+    }
+    if (out == nullptr || src0 == nullptr || src1 == nullptr || src2 == nullptr || src3 == nullptr || n <= 0 || k <= 0 ||
+        k % 32 != 0 || ldb < k || ld_sfb < k / 32) {
+        return PTO_B200_EINVAL;
+    }
+    const int out_es = (out_dtype == PTO_B200_F32) ? 4 : 2;
+    if ((reinterpret_cast<uintptr_t>(src0) & 15u) || (reinterpret_cast<uintptr_t>(src1) & 15u) || (ldb & 15) != 0 ||
+        (reinterpret_cast<uintptr_t>(out) & static_cast<uintptr_t>(out_es - 1)) ||
+        (reinterpret_cast<uintptr_t>(bias) & 3u)) {
+        return PTO_B200_EALIGN;
+    }
+    DeviceInfo* dev = nullptr;
+    if (int rc = device_info(&dev)) {
+        return rc;
+    }
+    const int warps_per_block = kGemvThreads / 32;
+    const long long want = (static_cast<long long>(n) + warps_per_block - 1) / warps_per_block;
+    const long long cap = static_cast<long long>(dev->sm_count) * 8;
+    const int grid = static_cast<int>(want < cap ? want : cap);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const float* fb = reinterpret_cast<const float*>(bias);
+    const bool a52 = (a_dtype == PTO_B200_E5M2), b52 = (b_dtype == PTO_B200_E5M2);
+    if (a52 && b52) {
+        return launch_gemv_mx<true, true>(s, grid, out_dtype, src0, src2, src1, src3, fb, out, n, k, ldb, ld_sfb);
+    }
+    if (a52) {
+        return launch_gemv_mx<true, false>(s, grid, out_dtype, src0, src2, src1, src3, fb, out, n, k, ldb, ld_sfb);
+    }
+    if (b52) {
+        return launch_gemv_mx<false, true>(s, grid, out_dtype, src0, src2, src1, src3, fb, out, n, k, ldb, ld_sfb);
+    }
+    return launch_gemv_mx<false, false>(s, grid, out_dtype, src0, src2, src1, src3, fb, out, n, k, ldb, ld_sfb);
+}
+
+extern "C" int pto_b200_mx_quantize_e4m3_ex(void* stream, uint8_t* data, uint8_t* scales, const uint8_t* src, int rows,
+                                            int k, long long ld_src, long long ld_data, long long ld_scales, int scale_alg)
 {
     if (data == nullptr || scales == nullptr || src == nullptr || rows <= 0 || k <= 0 || k % 32 != 0 || ld_src < k ||
         ld_data < k || ld_scales < k / 32) {
         return PTO_B200_EINVAL;
+    }
+    if (scale_alg != PTO_B200_SCALE_OCP && scale_alg != PTO_B200_SCALE_NV) {
+        return PTO_B200_EDTYPE;
     }
     if ((reinterpret_cast<uintptr_t>(src) & 15u) || (ld_src & 3) != 0 || (reinterpret_cast<uintptr_t>(data) & 3u) ||
         (ld_data & 3) != 0) {
@@ -922,10 +1010,10 @@ extern "C" int pto_b200_mx_quantize_e4m3(void* stream, uint8_t* data, uint8_t* s
     if (int rc = device_info(&dev)) {
         return rc;
     }
+    auto kernel = scale_alg == PTO_B200_SCALE_NV ? mx_quantize_e4m3_kernel<MX_SCALE_NV> : mx_quantize_e4m3_kernel<MX_SCALE_OCP>;
     // one resident wave of blocks walking the matrix with a grid stride: no partly filled second wave
     int blocks_per_sm = 0;
-    if (int rc = note_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, mx_quantize_e4m3_kernel,
-                                                                         kQuantThreads, 0),
+    if (int rc = note_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, kernel, kQuantThreads, 0),
                            "mx_quantize occupancy")) {
         return rc;
     }
@@ -933,10 +1021,17 @@ extern "C" int pto_b200_mx_quantize_e4m3(void* stream, uint8_t* data, uint8_t* s
     const long long want = (items + kQuantThreads - 1) / kQuantThreads;
     const long long cap = static_cast<long long>(dev->sm_count) * (blocks_per_sm > 0 ? blocks_per_sm : 1);
     const int grid = static_cast<int>(want < cap ? want : cap);
-    mx_quantize_e4m3_kernel<<<grid, kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const float*>(src), data, scales, rows, k, ld_src, ld_data, ld_scales);
+    kernel<<<grid, kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const float*>(src), data, scales,
+                                                                          rows, k, ld_src, ld_data, ld_scales);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return note_cuda(cudaGetLastError(), "mx_quantize launch");
+}
+
+extern "C" int pto_b200_mx_quantize_e4m3(void* stream, uint8_t* data, uint8_t* scales, const uint8_t* src, int rows,
+                                         int k, long long ld_src, long long ld_data, long long ld_scales)
+{
+    return pto_b200_mx_quantize_e4m3_ex(stream, data, scales, src, rows, k, ld_src, ld_data, ld_scales,
+                                        PTO_B200_SCALE_OCP);
 }
 
 // ---------------------------------------------------------------- K-split reduction over peer memory

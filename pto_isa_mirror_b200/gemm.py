@@ -217,6 +217,44 @@ def gemm_mx(a: torch.Tensor, b_dn: torch.Tensor, sfa: torch.Tensor, sfb: torch.T
     return out
 
 
+def mx_retile_scales(sfa: torch.Tensor, sfb: torch.Tensor, k: int, workspace: Optional[torch.Tensor] = None,
+                     stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """Re-tile the e8m0 scales sfa [M, K/32] and sfb [N, K/32] into the layout the block-scaled kernels read
+    (``pto_b200_mx_retile_scales``) and return the workspace, for use with :func:`gemm_mx_pretiled`."""
+    lib = _capi.load()
+    for t, name in ((sfa, "sfa"), (sfb, "sfb")):
+        _require_cuda_2d(t, name)
+        if t.element_size() != 1 or t.shape[1] != k // 32:
+            raise ValueError(f"{name} must be [rows, K/32] bytes")
+    m, n = sfa.shape[0], sfb.shape[0]
+    if workspace is None:
+        workspace = torch.empty(gemm_mx_workspace_bytes(m, n, k), dtype=torch.uint8, device=sfa.device)
+    rc = lib.pto_b200_mx_retile_scales(_stream_ptr(stream), workspace.data_ptr(), workspace.numel(), sfa.data_ptr(),
+                                       sfb.data_ptr(), m, n, k, sfa.stride(0), sfb.stride(0))
+    _capi.check(rc, "pto_b200_mx_retile_scales")
+    return workspace
+
+
+def gemm_mx_pretiled(a: torch.Tensor, b_dn: torch.Tensor, tiled_scales: torch.Tensor,
+                     out_dtype: torch.dtype = torch.bfloat16, a_fmt: int = E4M3, b_fmt: int = E4M3,
+                     out: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """:func:`gemm_mx` with scales that :func:`mx_retile_scales` already re-tiled for the same m, n, k: one kernel launch."""
+    lib = _capi.load()
+    _require_cuda_2d(a, "a")
+    _require_cuda_2d(b_dn, "b_dn")
+    m, k = a.shape
+    n = b_dn.shape[0]
+    if b_dn.shape[1] != k or a.element_size() != 1 or b_dn.element_size() != 1:
+        raise ValueError("a [M, K] and b_dn [N, K] must be fp8 bytes with the same K")
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    rc = lib.pto_b200_gemm_mx_pretiled(_stream_ptr(stream), out.data_ptr(), a.data_ptr(), b_dn.data_ptr(),
+                                       tiled_scales.data_ptr(), tiled_scales.numel(), m, n, k, a.stride(0),
+                                       b_dn.stride(0), out.stride(0), a_fmt, b_fmt, _TORCH_TO_PTO[out.dtype])
+    _capi.check(rc, "pto_b200_gemm_mx_pretiled")
+    return out
+
+
 def gemv(x: torch.Tensor, b_dn: torch.Tensor, out_dtype: torch.dtype = torch.float32,
          bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
          stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
@@ -247,11 +285,42 @@ def gemv(x: torch.Tensor, b_dn: torch.Tensor, out_dtype: torch.dtype = torch.flo
     return out
 
 
+def gemv_mx(x: torch.Tensor, b_dn: torch.Tensor, sfx: torch.Tensor, sfb: torch.Tensor,
+            out_dtype: torch.dtype = torch.float32, a_fmt: int = E4M3, b_fmt: int = E4M3,
+            bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+            stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """TGEMV_MX: out[j] = sum_k x[k] * b_dn[j, k] * 2^(sfx[k/32]-127) * 2^(sfb[j, k/32]-127) (+ bias[j]) for one left
+    row x [K] of fp8 bytes with its K/32 e8m0 scales sfx, and column-major b_dn [N, K] with scales sfb [N, K/32]."""
+    lib = _capi.load()
+    _require_cuda_2d(b_dn, "b_dn")
+    _require_cuda_2d(sfb, "sfb")
+    n, k = b_dn.shape
+    if (not x.is_cuda or x.element_size() != 1 or b_dn.element_size() != 1 or x.numel() != k or not x.is_contiguous()
+            or k % 32):
+        raise ValueError("x must be K contiguous fp8 bytes, b_dn [N, K] fp8 bytes, K a multiple of 32")
+    if sfx.numel() != k // 32 or not sfx.is_contiguous() or tuple(sfb.shape) != (n, k // 32):
+        raise ValueError("scales must be [K/32] and [N, K/32] bytes")
+    if out is None:
+        out = torch.empty((n,), dtype=out_dtype, device=x.device)
+    bias_ptr = None
+    if bias is not None:
+        if bias.dtype != torch.float32 or not bias.is_cuda or bias.numel() != n or not bias.is_contiguous():
+            raise ValueError(f"bias must be a contiguous CUDA float32 tensor with {n} elements")
+        bias_ptr = bias.data_ptr()
+    rc = lib.pto_b200_gemv_mx(_stream_ptr(stream), out.data_ptr(), x.data_ptr(), b_dn.data_ptr(), sfx.data_ptr(),
+                              sfb.data_ptr(), bias_ptr, n, k, b_dn.stride(0), sfb.stride(0), a_fmt, b_fmt,
+                              _TORCH_TO_PTO[out.dtype])
+    _capi.check(rc, "pto_b200_gemv_mx")
+    return out
+
+
 def mx_quantize_e4m3(src: torch.Tensor, stream: Optional[torch.cuda.Stream] = None,
-                     data: Optional[torch.Tensor] = None, scales: Optional[torch.Tensor] = None):
+                     data: Optional[torch.Tensor] = None, scales: Optional[torch.Tensor] = None,
+                     scale_alg: int = _capi.SCALE_OCP):
     """OCP MX quantisation (TQUANT, MXFP8): float32 src [rows, K] -> (e4m3 bytes [rows, K] uint8, e8m0 scales
     [rows, K/32] uint8), one scale per 32 elements along K. Finite input only. ``data`` / ``scales``: caller's output
-    buffers of those shapes (allocated when omitted)."""
+    buffers of those shapes (allocated when omitted). ``scale_alg``: ``_capi.SCALE_OCP`` (default) or ``_capi.SCALE_NV``,
+    the reference's QuantScaleAlg."""
     lib = _capi.load()
     _require_cuda_2d(src, "src")
     if src.dtype != torch.float32:
@@ -267,9 +336,9 @@ def mx_quantize_e4m3(src: torch.Tensor, stream: Optional[torch.cuda.Stream] = No
         _require_cuda_2d(t, name)
         if t.dtype != torch.uint8 or tuple(t.shape) != shape:
             raise ValueError(f"{name} must be a uint8 CUDA tensor of shape {shape}")
-    rc = lib.pto_b200_mx_quantize_e4m3(_stream_ptr(stream), data.data_ptr(), scales.data_ptr(), src.data_ptr(), rows,
-                                       k, src.stride(0), data.stride(0), scales.stride(0))
-    _capi.check(rc, "pto_b200_mx_quantize_e4m3")
+    rc = lib.pto_b200_mx_quantize_e4m3_ex(_stream_ptr(stream), data.data_ptr(), scales.data_ptr(), src.data_ptr(), rows,
+                                          k, src.stride(0), data.stride(0), scales.stride(0), scale_alg)
+    _capi.check(rc, "pto_b200_mx_quantize_e4m3_ex")
     return data, scales
 
 

@@ -141,6 +141,23 @@ def main():
     src[3, 5] = -1e-9
     d, s = ref.mx_quantize_e4m3(src)
     save("mx_quantize", src=src, data=d, scales=s)
+    # the NV scale rule (QuantScaleAlg::NV): power-of-two maxima (no round-up), the -2^-10 tie, tiny negatives that keep
+    # their sign, a range of block magnitudes
+    if wanted("mx_quantize_nv"):
+        src = gd.normal((64, 256), 16)
+        src[0, :32] = 0
+        src[1, :32] *= 1e-30
+        src[2, :32] *= 1e30
+        src[3, 5] = -1e-9
+        src[4, :32] = np.float32(448.0) * np.float32(2.0) ** np.arange(-16, 16)
+        src[5, :32] = np.float32(-(2.0 ** -10))
+        src[5, 0] = np.float32(1.0)
+        src[6, :32] = np.linspace(-1, 1, 32).astype(np.float32) * np.float32(2.0 ** -12)
+        src[6, 31] = np.float32(448.0)
+        for i in range(8, 40):
+            src[i, :32] *= np.float32(2.0) ** (i - 24)
+        d, s = ref.mx_quantize_e4m3(src, 1)
+        save("mx_quantize_nv", src=src, data=d, scales=s)
 
 
 if __name__ == "__main__":

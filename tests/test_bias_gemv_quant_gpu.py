@@ -282,3 +282,60 @@ def test_quant_store_rejects_bad_arguments():
     assert e.value.code == 3
     with pytest.raises(ValueError):
         pto.gemm_quant(a, a, torch.bfloat16, fp_words=torch.zeros(5, dtype=torch.int64, device=DEV))
+
+
+def test_mx_quantiser_nv_rule_bit_exact():
+    """pto_b200_mx_quantize_e4m3_ex with QuantScaleAlg::NV against the simulator's fixture and, on a larger matrix,
+    against the oracle."""
+    from pto_isa_mirror_b200 import _capi
+
+    g = golden("mx_quantize_nv")
+    d, s = pto.mx_quantize_e4m3(dev(g["src"]), scale_alg=_capi.SCALE_NV)
+    assert np.array_equal(host(s), g["scales"])
+    assert np.array_equal(host(d), g["data"])
+    x = gd.normal((777, 1056), 17) * np.float32(5.0)
+    x[::7] *= np.float32(1e-6)
+    d, s = pto.mx_quantize_e4m3(dev(x), scale_alg=_capi.SCALE_NV)
+    rd, rs = oracle.mx_quantize_e4m3(x, oracle.NV)
+    assert np.array_equal(host(s), rs) and np.array_equal(host(d), rd)
+    with pytest.raises(pto.PtoB200Error):
+        pto.mx_quantize_e4m3(dev(x), scale_alg=5)
+
+
+# ------------------------------------------------------------------ TGEMV_MX (one left row, block-scaled)
+
+@pytest.mark.parametrize("fa,fb", [(pto.E4M3, pto.E4M3), (pto.E4M3, pto.E5M2), (pto.E5M2, pto.E5M2)])
+def test_gemv_mx_integer_cases_exact(fa, fb):
+    """Integers in [-10, 10] with scales 2^0..2^2 (tests/cpu/st/testcase/tmatmul_mx/gen_data.py:113-138): exact."""
+    import ml_dtypes
+
+    n, k = 300, 1056
+    enc = {pto.E4M3: ml_dtypes.float8_e4m3fn, pto.E5M2: ml_dtypes.float8_e5m2}
+    xi = gd.randint((1, k), -10, 10, 23, 0).astype(np.float32)
+    bi = gd.randint((n, k), -10, 10, 23, 1).astype(np.float32)
+    # (e5m2 cannot hold 9: the encoder rounds it; the expected values are computed from the encoded bytes)
+    x8 = xi.astype(enc[fa]).view(np.uint8)
+    b8 = bi.astype(enc[fb]).view(np.uint8)
+    sfx = gd.randint((1, k // 32), 127, 129, 23, 2).astype(np.uint8)
+    sfb = gd.randint((n, k // 32), 127, 129, 23, 3).astype(np.uint8)
+    exact = oracle.gemm_mx(x8, b8, sfx, sfb, fa, fb)[0]
+    bias = gd.normal((n,), 24).astype(np.float32).round()
+    out = pto.gemv_mx(dev(x8[0]), dev(b8), dev(sfx[0]), dev(sfb), torch.float32, fa, fb)
+    assert np.array_equal(host(out), exact)
+    outb = pto.gemv_mx(dev(x8[0]), dev(b8), dev(sfx[0]), dev(sfb), torch.float32, fa, fb, bias=dev(bias))
+    assert np.array_equal(host(outb), exact + bias)
+
+
+def test_gemv_mx_against_the_oracle_and_the_tile_kernel():
+    """Quantised N(0, 1) data: within the MX tolerance of the oracle's chain, and of row 0 of the block-scaled GEMM."""
+    n, k = 2048, 4096
+    a, b, sfa, sfb = gd.mx_inputs(128, n, k, 25)
+    ref = oracle.gemm_mx(a[:1], b, sfa[:1], sfb)[0]
+    out = pto.gemv_mx(dev(a[0]), dev(b), dev(sfa[0]), dev(sfb), torch.float32)
+    assert max_rel_err(host(out), ref) <= MX_TOL
+    full = pto.gemm_mx(dev(a), dev(b), dev(sfa), dev(sfb), torch.float32)
+    assert max_rel_err(host(out), host(full)[0]) <= MX_TOL
+    out16 = pto.gemv_mx(dev(a[0]), dev(b), dev(sfa[0]), dev(sfb), torch.bfloat16)
+    assert np.array_equal(host(out16), gd.f32_to_bf16_bits(host(out)))
+    with pytest.raises(pto.PtoB200Error):
+        pto.gemv_mx(dev(a[0]), dev(b), dev(sfa[0]), dev(sfb), torch.float16)

@@ -78,6 +78,14 @@ def test_argument_errors_come_before_any_launch(lib):
     assert gv(None, p, p, p, None, 16, 12, 12, BF16, F32) == _capi.EALIGN                       # 24-byte column pitch
     assert gv(None, p, p, p, None, 16, 16, 16, S8, F32) == _capi.EDTYPE                         # int8 -> float
     assert gv(None, p, p, p, None, 16, 16, 16, F32, F32) == _capi.EDTYPE
+    gvm = lib.pto_b200_gemv_mx
+    assert gvm(None, p, p, p, p, p, None, 16, 48, 48, 2, E4M3, E4M3, F32) == _capi.EINVAL          # k % 32
+    assert gvm(None, p, p, p, None, p, None, 16, 64, 64, 2, E4M3, E4M3, F32) == _capi.EINVAL      # row scales missing
+    assert gvm(None, p, p, p, p, p, None, 16, 64, 64, 2, S8, E4M3, F32) == _capi.EDTYPE
+    assert gvm(None, p, p, p, p, p, None, 16, 64, 64, 2, E4M3, E5M2, F16) == _capi.EDTYPE
+    assert gvm(None, p, p + 4, p, p, p, None, 16, 64, 64, 2, E4M3, E4M3, F32) == _capi.EALIGN
+    qx = lib.pto_b200_mx_quantize_e4m3_ex
+    assert qx(None, p, p, p, 4, 64, 64, 64, 2, 7) == _capi.EDTYPE                                  # unknown scale rule
     q = lib.pto_b200_mx_quantize_e4m3
     assert q(None, p, p, None, 4, 64, 64, 64, 2) == _capi.EINVAL
     assert q(None, p, p, p, 4, 48, 48, 48, 2) == _capi.EINVAL                                   # k % 32

@@ -476,3 +476,19 @@ def test_bounded_wait_expires_and_reports():
     a, b = gd.dense_inputs(256, 256, 256, "bf16", 43)
     out = host(pto.gemm(dev16(a, torch.bfloat16), dev16(b, torch.bfloat16), torch.float32))
     assert max_rel_err(out, oracle.gemm_f32acc(a, b, oracle.BF16)) <= DENSE_TOL
+
+
+@pytest.mark.parametrize("m,n,k", [(2560, 2560, 512), (130, 260, 160), (384, 128, 1056)])
+def test_mx_pretiled_scales_match_the_one_call_form(m, n, k):
+    """pto_b200_mx_retile_scales + pto_b200_gemm_mx_pretiled give the bits of pto_b200_gemm_mx, on the two-CTA kernel and
+    on both tile widths of the one-CTA kernel (the re-tiled layout does not depend on the kernel that reads it)."""
+    a, b, sfa, sfb = gd.mx_inputs(m, n, k, 91)
+    ta, tb, tsa, tsb = dev8(a), dev8(b), dev8(sfa), dev8(sfb)
+    want = pto.gemm_mx(ta, tb, tsa, tsb, torch.float32)
+    tiled = pto.mx_retile_scales(tsa, tsb, k)
+    before = pto.launch_count()
+    got = pto.gemm_mx_pretiled(ta, tb, tiled, torch.float32)
+    assert pto.launch_count() == before + 1
+    assert torch.equal(got.view(torch.int32), want.view(torch.int32))
+    ref = oracle.gemm_mx(a[:128], b[:128], sfa[:128], sfb[:128])
+    assert max_rel_err(host(got)[:128, :128], ref) <= MX_TOL

@@ -47,7 +47,11 @@ def test_one_row_and_bias_forms_compile(tmp_path):
                     "  TileLeft<half, 1, 64> a; TileRight<half, 64, 256> b; TileAcc<float, 1, 256> c;\n"
                     "  Tile<TileType::Bias, float, 1, 256, BLayout::RowMajor, 1, 256> bias;\n"
                     "  if (false) { TGEMV(c, a, b); TGEMV_ACC(c, c, a, b); TGEMV_BIAS(c, a, b, bias); "
-                    "TMATMUL_BIAS(c, a, b, bias); }\n  return 0;\n}\n")
+                    "TMATMUL_BIAS(c, a, b, bias); }\n"
+                    "  TileLeft<float8_e4m3_t, 1, 128> xa; TileRight<float8_e5m2_t, 128, 256> xb;\n"
+                    "  TileLeftScale<float8_e8m0_t, 1, 4> xsa; TileRightScale<float8_e8m0_t, 4, 256> xsb;\n"
+                    "  if (false) { TGEMV_MX(c, xa, xsa, xb, xsb); TGEMV_MX(c, c, xa, xsa, xb, xsb); "
+                    "TGEMV_MX(c, xa, xsa, xb, xsb, bias); }\n  return 0;\n}\n")
     inc = ["-I", os.path.join(ROOT, "include"), "-I", os.path.join(CUDA, "include")]
     proc = subprocess.run(["g++", "-std=c++17", "-Wall", "-Werror", "-fsyntax-only", *inc, str(good)],
                           capture_output=True, text=True)
