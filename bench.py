@@ -50,6 +50,9 @@ WORKLOADS = {
     "bf16_4096": dict(kind="dense", m=4096, n=4096, k=4096, dtype="bf16", out="bf16"),
     "s8_8192_dequant": dict(kind="s8", m=8192, n=8192, k=8192),
     "mxfp8_16384x8192x8192": dict(kind="mx", m=16384, n=8192, k=8192),
+    # the shape of the reference's MXFP4 kernel (kernels/manual/a5/matmul_mxfp4_performance/mxmatmul_performance_kernel.cpp:
+    # 446-463): float4_e2m1x2_t operands, e8m0 scales, bf16 out, ragged M and N
+    "mxfp4_2040x8100x8192": dict(kind="mx", m=2040, n=8100, k=8192, fmt="e2m1"),
     "ksplit_bf16_8192x65536x8192": dict(kind="ksplit", m=8192, n=8192, k=65536),
     # the largest shape of the reference's AllGather + GEMM table (kernels/manual/a2a3/allgather_gemm/README.md:112-125):
     # A split along M over the ranks, B replicated, every rank computes the whole C; run with --workload at any N
@@ -294,6 +297,49 @@ def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=8, 
                 exact = exact and bool(np.array_equal(_bits16(c[r0:r0 + 128, c0:c0 + 256]), want))
             return {"tiles": len(origins), "bit_exact": exact, "ok": exact,
                     "what": "bf16((float(int32 acc) * s_col) * s_row) against the oracle's int32 chain and store"}
+
+        step.parity = parity
+        return step, flops, per_set * sets, sets
+    if kind == "mx" and spec.get("fmt") == "e2m1":
+        # inputs as the reference's generator draws them (matmul_mxfp4_performance/scripts/gen_data.py:46-52): values
+        # -1, 0, 1 (codes 0xA, 0x0, 0x2), two per byte with the even element in the low nibble, scales 2^0..2^2
+        codes = torch.tensor([0xA, 0x0, 0x2], dtype=torch.uint8, device=dev)
+
+        def draw(rows):
+            v = codes[torch.randint(0, 3, (rows, k), generator=gen, device=dev)]
+            return (v[:, 0::2] | (v[:, 1::2] << 4)).contiguous()
+
+        per_set = (m * k + n * k) // 2 + (m + n) * (k // 32) + m * n * 2
+        sets = min(16, max(2, -(-3 * L2_BYTES // per_set))) if per_set < 3 * L2_BYTES else 1
+        bufs = []
+        for _ in range(sets):
+            bufs.append((draw(m), draw(n),
+                         torch.randint(127, 130, (m, k // 32), generator=gen, device=dev, dtype=torch.uint8),
+                         torch.randint(127, 130, (n, k // 32), generator=gen, device=dev, dtype=torch.uint8),
+                         torch.empty((m, n), dtype=torch.bfloat16, device=dev)))
+        ws = torch.empty(pto.gemm_mx_workspace_bytes(m, n, k), dtype=torch.uint8, device=dev)
+
+        def step(i):
+            a, b, sfa, sfb, c = bufs[i % sets]
+            pto.gemm_mx(a, b, sfa, sfb, torch.bfloat16, pto.E2M1, pto.E2M1, workspace=ws, out=c)
+
+        def parity():
+            import oracle
+
+            a, b, sfa, sfb, c = bufs[0]
+            step(0)
+            torch.cuda.synchronize(dev)
+            ok, tiles = True, []
+            for r0, c0 in _tile_origins(m, n, 2, 103):
+                ref = oracle.gemm_mx(a[r0:r0 + 128].cpu().numpy(), b[c0:c0 + 256].cpu().numpy(),
+                                     sfa[r0:r0 + 128].cpu().numpy(), sfb[c0:c0 + 256].cpu().numpy(), oracle.E2M1,
+                                     oracle.E2M1)
+                same = np.array_equal(_bits16(c[r0:r0 + 128, c0:c0 + 256]), oracle.f32_to_bf16_bits(ref))
+                ok = ok and same
+                tiles.append([r0, c0])
+            return {"ok": bool(ok), "tiles": tiles,
+                    "what": "bf16 store against the RNE cast of the oracle's chain: every sum is an integer below 2^18, "
+                            "so the comparison is exact"}
 
         step.parity = parity
         return step, flops, per_set * sets, sets
@@ -713,6 +759,8 @@ def time_steps(step, steps, warmup, dev, world):
 def cpu_tile_runner(kind: str, k: int, single_thread=False):
     """A closure that runs ONE 128 x 256 x k output tile of the workload through the reference CPU simulator
     (or, where it was never built, the C restatement), plus a description of what runs."""
+    import numpy as np
+
     import oracle
     from pto_isa_mirror_b200 import gen_data as gd
 
@@ -722,6 +770,13 @@ def cpu_tile_runner(kind: str, k: int, single_thread=False):
     if kind == "s8":
         a, b, _, _ = gd.s8_inputs(128, 256, k, 2)
         run = (lambda: sim.tile_s8(a, b)) if use_ref else (lambda: oracle.gemm_s8(a, b, cores))
+    elif kind == "mx4":
+        a = gd.randint((128, k // 2), 0, 255, 5, 0).astype(np.uint8)
+        b = gd.randint((256, k // 2), 0, 255, 5, 1).astype(np.uint8)
+        sfa = gd.randint((128, k // 32), 127, 129, 5, 2).astype(np.uint8)
+        sfb = gd.randint((256, k // 32), 127, 129, 5, 3).astype(np.uint8)
+        run = (lambda: sim.tile_mx(a, b, sfa, sfb, oracle.E2M1, oracle.E2M1)) if use_ref else (
+            lambda: oracle.gemm_mx(a, b, sfa, sfb, oracle.E2M1, oracle.E2M1, threads=cores))
     elif kind == "mx":
         a, b, sfa, sfb = gd.mx_inputs(128, 256, k, 3)
         run = (lambda: sim.tile_mx(a, b, sfa, sfb)) if use_ref else (
@@ -770,7 +825,7 @@ def reference_arm(args, world, rank):
         oracle.build()
     # one step = one 128 x 256 output tile over a K that keeps the whole run within a few minutes
     full_k = spec["k"] if kind != "ksplit" else spec["k"] // max(args.gpus, 1)
-    sk = "dense" if kind in ("ksplit", "allgather") else kind
+    sk = "dense" if kind in ("ksplit", "allgather") else ("mx4" if spec.get("fmt") == "e2m1" else kind)
     depths = (8192, 4096, 1024, 256) if sk == "dense" else (8192, 1024, 256)
     candidates = [kk for kk in depths if kk <= full_k] or [256]
     total_steps = args.steps + args.warmup
@@ -794,7 +849,8 @@ def reference_arm(args, world, rank):
         "impl": "reference", "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": el / max(args.steps, 1) * 1e3,
         "higher_is_better": True, "scaling": "strong" if kind == "ksplit" else "weak", "vs_baseline": None,
-        "dtype": {"dense": "bf16", "ksplit": "bf16", "allgather": "bf16", "s8": "s8", "mx": "mxfp8_e4m3"}[kind],
+        "dtype": "mxfp4_e2m1" if spec.get("fmt") == "e2m1" else
+                 {"dense": "bf16", "ksplit": "bf16", "allgather": "bf16", "s8": "s8", "mx": "mxfp8_e4m3"}[kind],
         "data": "synthetic",
         "config": {"workload": name, "m": spec["m"], "n": spec["n"], "k": spec["k"],
                    "note": "reference CPU simulator on host cores; each step is one 128x256 output tile over "
@@ -888,6 +944,8 @@ def main():
     kind = spec["kind"]
     dtype = {"dense": spec.get("dtype", "bf16"), "ksplit": "bf16", "ksplit1": "bf16", "allgather": "bf16", "s8": "s8",
              "mx": "mxfp8_e4m3", "gemv": "bf16", "quant": "f32"}[kind]
+    if spec.get("fmt") == "e2m1":
+        dtype = "mxfp4_e2m1"   # through kind::mxf8f6f4: 4-bit operands in memory, the 8-bit kinds' tensor rate
     peak_scale = {"s8": 2.0, "mx": 2.0}.get(kind, 1.0)
     # a single kernel timed back to back for a short region: burst peak; the long K-split step: sustained
     peak_key = "bf16_tflops" if ms < 500.0 else "bf16_tflops_sustained"

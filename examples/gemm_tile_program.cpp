@@ -6,8 +6,8 @@
 // tmatmul_kernel.cpp:86-96), (5) a one-row TGEMV_BIAS, (6) the int8 K loop stored with a per-column scaling tile
 // (TSTORE_FP) and with one pre-quant scalar plus ReLU (kernels/manual/a2a3/dispatch_mega_combine/op_kernel/utils/
 // pto_gmm_preload_async_fixpipe_quant.hpp:75-124), (7) the block-scaled K loop with MX_A_ND / MX_B_DN scale tensors
-// (kernels/manual/a5/matmul_mxfp8_performance/mxmatmul_performance_kernel.cpp:153-344) and (8) LaunchMxMatmul on e5m2
-// operands. Inputs are small integers so the fp32 results are exact; the program checks them against host loops and
+// (kernels/manual/a5/matmul_mxfp8_performance/mxmatmul_performance_kernel.cpp:153-344), (8) LaunchMxMatmul on e5m2
+// operands and (9) on float4_e2m1x2_t operands, two per byte (kernels/manual/a5/matmul_mxfp4_performance). Inputs are small integers so the fp32 results are exact; the program checks them against host loops and
 // prints "tile programs ok".
 //
 // Build (one line): g++ -std=c++17 -I include -I /usr/local/cuda/include examples/gemm_tile_program.cpp
@@ -52,6 +52,11 @@ static uint8_t int_to_e5m2(int v)
 {
     static const uint8_t mag[5] = {0x00, 0x3C, 0x40, 0x42, 0x44};
     return static_cast<uint8_t>((v < 0 ? 0x80 : 0) | mag[v < 0 ? -v : v]);
+}
+static uint8_t int_to_e2m1(int v)
+{ // 4-bit codes of 0, 1, 2, 3, 4
+    static const uint8_t mag[5] = {0x0, 0x2, 0x4, 0x5, 0x6};
+    return static_cast<uint8_t>((v < 0 ? 0x8 : 0) | mag[v < 0 ? -v : v]);
 }
 
 template <typename T>
@@ -375,6 +380,26 @@ int main()
         for (int i = 0; i < M * N; ++i) n8 += (out16[i] != f32_to_bf16_rne(ref[i]));
         std::printf("LaunchMxMatmul (e5m2, bf16 out): %d mismatches\n", n8);
         bad += n8;
+        // (9) the same launcher on packed 4-bit operands: element 2i in the low nibble of byte i, element 2i+1 high
+        std::vector<uint8_t> a4(M * K / 2), b4(N * K / 2);
+        for (int i = 0; i < M * K / 2; ++i)
+            a4[i] = static_cast<uint8_t>(int_to_e2m1(ai[2 * i]) | (int_to_e2m1(ai[2 * i + 1]) << 4));
+        for (int j = 0; j < N; ++j)
+            for (int k = 0; k < K; k += 2)
+                b4[(j * K + k) / 2] = static_cast<uint8_t>(int_to_e2m1(bi[k * N + j]) | (int_to_e2m1(bi[(k + 1) * N + j]) << 4));
+        uint8_t* dA4 = to_device(a4);
+        uint8_t* dB4 = to_device(b4);
+        cudaMemset(dOut16, 0xFF, M * N * sizeof(uint16_t));
+        LaunchMxMatmul(reinterpret_cast<uint8_t*>(dOut16), dA4, dB4, reinterpret_cast<uint8_t*>(dSfa),
+                       reinterpret_cast<uint8_t*>(dSfb), nullptr, {M, N, K}, PTO_B200_E2M1);
+        cudaDeviceSynchronize();
+        cudaMemcpy(out16.data(), dOut16, out16.size() * 2, cudaMemcpyDeviceToHost);
+        int n9 = 0;
+        for (int i = 0; i < M * N; ++i) n9 += (out16[i] != f32_to_bf16_rne(ref[i]));
+        std::printf("LaunchMxMatmul (float4_e2m1x2, bf16 out): %d mismatches\n", n9);
+        bad += n9;
+        cudaFree(dA4);
+        cudaFree(dB4);
         ref.swap(ref_mx);
         cudaFree(dA43);
         cudaFree(dB43);

@@ -33,12 +33,14 @@ inline void LaunchGEMME2E(uint8_t* out, uint8_t* src0, uint8_t* src1, void* stre
 }
 
 // e5m2 x e5m2 with e8m0 scales (src2: [m, k/32], src3: [n, k/32]) -> bf16. Six arguments as in the reference:
-// the scale re-tiling scratch is the library's built-in array (pto_b200_gemm_mx_static).
+// the scale re-tiling scratch is the library's built-in array (pto_b200_gemm_mx_static). The MXFP4 kernel of the same
+// name (kernels/manual/a5/matmul_mxfp4_performance/mxmatmul_performance_kernel.cpp:446-463: float4_e2m1x2_t operands,
+// two per byte, 2040 x 8100 x 8192) is this call with operand_dtype = PTO_B200_E2M1 and shape {2040, 8100, 8192}.
 inline void LaunchMxMatmul(uint8_t* out, uint8_t* src0, uint8_t* src1, uint8_t* src2, uint8_t* src3, void* stream,
-                           pto::b200::GemmShape shape = {6144, 6144, 6144}, int fp8_dtype = PTO_B200_E5M2)
+                           pto::b200::GemmShape shape = {6144, 6144, 6144}, int operand_dtype = PTO_B200_E5M2)
 {
     const int rc = pto_b200_gemm_mx_static(stream, out, src0, src1, src2, src3, shape.m, shape.n, shape.k, shape.k,
-                                           shape.k, shape.n, shape.k / 32, shape.k / 32, fp8_dtype, fp8_dtype,
+                                           shape.k, shape.n, shape.k / 32, shape.k / 32, operand_dtype, operand_dtype,
                                            PTO_B200_BF16);
     if (rc != PTO_B200_OK) {
         pto::b200::fail("LaunchMxMatmul", rc);

@@ -34,7 +34,8 @@ typedef enum {
     PTO_B200_S8 = 3,   /* int8_t                                             */
     PTO_B200_S32 = 4,  /* int32_t                                            */
     PTO_B200_E4M3 = 5, /* float8_e4m3_t (fn variant: no inf, 0x7f NaN)      */
-    PTO_B200_E5M2 = 6  /* float8_e5m2_t                                      */
+    PTO_B200_E5M2 = 6, /* float8_e5m2_t                                      */
+    PTO_B200_E2M1 = 7  /* float4_e2m1x2_t: two 4-bit values per byte, the even element in the low nibble */
 } pto_b200_dtype;
 
 typedef enum {
@@ -151,7 +152,10 @@ int pto_b200_gemm_quant(void* stream, uint8_t* out, const uint8_t* src0, const u
  * TMATMUL_MX, include/pto/cpu/TMatmul.hpp:169-205.
  *   src2 : e8m0 scales of A, M x K/32 row-major (Layout::MX_A_ND), leading dimension ld_sfa bytes
  *   src3 : e8m0 scales of B, N x K/32 row-major (Layout::MX_B_DN), leading dimension ld_sfb bytes
- *   a_dtype / b_dtype : E4M3 or E5M2 (any mix); out_dtype BF16 or F32; B is PTO_B200_B_DN; k % 32 == 0.
+ *   a_dtype / b_dtype : E4M3 or E5M2 (any mix), or both E2M1 (MXFP4: kernels/manual/a5/matmul_mxfp4_performance,
+ *                       float4_e2m1x2_t of include/pto/cpu/MXTypes.hpp:316-359; lda / ldb still count ELEMENTS, a row
+ *                       holds k / 2 bytes; bases 32-byte aligned, lda and ldb multiples of 64, k a multiple of 128);
+ *                       out_dtype BF16 or F32; B is PTO_B200_B_DN; k % 32 == 0.
  *   workspace : device scratch of at least pto_b200_gemm_mx_workspace_bytes(m, n, k) bytes, 16-byte aligned;
  *               the scales are re-tiled into it by a small kernel on the same stream before the GEMM.
  * Scale byte 0xFF (NaN in the e8m0 encoding) is outside the supported input domain.

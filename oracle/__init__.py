@@ -26,7 +26,7 @@ REF_LIB_1T = os.path.join(HERE, "_ref", "libpto_ref_1t.so")
 
 F16, BF16, F32 = 0, 1, 2
 B_DN, B_ND = 0, 1
-E4M3, E5M2 = 5, 6
+E4M3, E5M2, E2M1 = 5, 6, 7
 
 _ll = ctypes.c_longlong
 _i = ctypes.c_int
@@ -136,9 +136,10 @@ def gemm_mx(a: np.ndarray, b_dn: np.ndarray, sfa: np.ndarray, sfb: np.ndarray, a
     b_dn = _c(b_dn, np.uint8)
     sfa = _c(sfa, np.uint8)
     sfb = _c(sfb, np.uint8)
-    m, k = a.shape
+    m = a.shape[0]
+    k = a.shape[1] * (2 if a_fmt == E2M1 else 1)          # E2M1: two elements per byte
     n = b_dn.shape[0]
-    assert b_dn.shape[1] == k and sfa.shape == (m, k // 32) and sfb.shape == (n, k // 32)
+    assert b_dn.shape[1] * (2 if b_fmt == E2M1 else 1) == k and sfa.shape == (m, k // 32) and sfb.shape == (n, k // 32)
     c = np.empty((m, n), dtype=np.float32)
     if bias is not None:
         bias = _c(bias, np.float32)
@@ -294,8 +295,8 @@ class Ref:
         b_dn = _c(b_dn, np.uint8)
         sfa = _c(sfa, np.uint8)
         sfb = _c(sfb, np.uint8)
-        k = a.shape[1]
-        assert a.shape[0] == self.TILE_M and b_dn.shape == (self.TILE_N, k)
+        k = a.shape[1] * (2 if a_fmt == E2M1 else 1)
+        assert a.shape[0] == self.TILE_M and b_dn.shape[0] == self.TILE_N
         assert sfa.shape == (self.TILE_M, k // 32) and sfb.shape == (self.TILE_N, k // 32)
         out = np.empty((self.TILE_M, self.TILE_N), dtype=np.float32)
         rc = self.lib.ref_tile_mx(_ptr(out), _ptr(a), _ptr(b_dn), _ptr(sfa), _ptr(sfb), k, a_fmt, b_fmt)

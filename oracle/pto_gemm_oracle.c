@@ -99,9 +99,34 @@ uint16_t pto_oracle_float_to_half(float f)
     return (uint16_t)(sign | (base + q)); /* a mantissa carry walks into the exponent, up to inf */
 }
 
+double pto_oracle_fp8_to_double(uint8_t raw, int fmt);
+
+/* float4_e2m1x2_t (include/pto/cpu/MXTypes.hpp:316-332, decode :254-274): one sign, two exponent (bias 1) and one
+   mantissa bit per 4-bit code: 0, 0.5, 1, 1.5, 2, 3, 4, 6 and their negatives. */
+static double e2m1_to_double(unsigned nibble)
+{
+    static const double mag[8] = {0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0};
+    const double v = mag[nibble & 7u];
+    return (nibble & 8u) ? -v : v;
+}
+
+/* Element kk of row `row` of an MX operand: one byte per element for fp8; for ORACLE_E2M1 two elements per byte, the
+   even one in the low nibble (GetProperDataPart, include/pto/cpu/MXTypes.hpp:351-359), ld counted in elements. */
+static double mx_element(const uint8_t* base, long long row, long long ld, int kk, int fmt)
+{
+    if (fmt == ORACLE_E2M1) {
+        const uint8_t byte = base[(size_t)row * (size_t)(ld / 2) + (size_t)(kk / 2)];
+        return e2m1_to_double((kk & 1) ? (unsigned)(byte >> 4) : (unsigned)(byte & 0xFu));
+    }
+    return pto_oracle_fp8_to_double(base[(size_t)row * (size_t)ld + (size_t)kk], fmt);
+}
+
 /* include/pto/cpu/MXTypes.hpp:232-252 */
 double pto_oracle_fp8_to_double(uint8_t raw, int fmt)
 {
+    if (fmt == ORACLE_E2M1) {
+        return e2m1_to_double(raw & 0xFu);
+    }
     const int sign = raw >> 7;
     const int mag = raw & 0x7F;
     double v;
@@ -413,7 +438,7 @@ static void mx_rows(void* vctx, int r0, int r1)
     }
     for (int i = r0; i < r1; ++i) {
         for (int kk = 0; kk < x->k; ++kk) {
-            arow[kk] = pto_oracle_fp8_to_double(x->a[(size_t)i * x->lda + kk], x->a_fmt) *
+            arow[kk] = mx_element(x->a, i, x->lda, kk, x->a_fmt) *
                        pto_oracle_e8m0_to_double(x->sfa[(size_t)i * x->ld_sfa + kk / 32]);
         }
         for (int j0 = 0; j0 < x->n; j0 += JBLOCK) {
@@ -467,7 +492,7 @@ void pto_oracle_gemm_mx_bias(const uint8_t* a, const uint8_t* b, const uint8_t* 
     }
     for (int j = 0; j < n; ++j) {
         for (int kk = 0; kk < k; ++kk) {
-            bt[(size_t)kk * n + j] = pto_oracle_fp8_to_double(b[(size_t)j * ldb + kk], b_fmt) *
+            bt[(size_t)kk * n + j] = mx_element(b, j, ldb, kk, b_fmt) *
                                      pto_oracle_e8m0_to_double(sfb[(size_t)j * ld_sfb + kk / 32]);
         }
     }

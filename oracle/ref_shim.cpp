@@ -50,6 +50,19 @@ void run_s8_tile(int32_t* out, const int8_t* a, const int8_t* b_dn)
         out, const_cast<int8_t*>(a), const_cast<int8_t*>(b_dn));
 }
 
+// Raw code of element idx of a row of k elements: a byte for the fp8 types; for the packed 4-bit types two elements
+// share a byte, the even one in the low nibble (GetProperDataPart, include/pto/cpu/MXTypes.hpp:351-359).
+template <typename T>
+uint8_t mx_raw_code(const uint8_t* base, size_t row, int k, int idx)
+{
+    if constexpr (IsTwinType<T>()) {
+        const uint8_t byte = base[row * static_cast<size_t>(k / 2) + static_cast<size_t>(idx / 2)];
+        return (idx & 1) ? static_cast<uint8_t>(byte >> 4) : static_cast<uint8_t>(byte & 0xF);
+    } else {
+        return base[row * static_cast<size_t>(k) + static_cast<size_t>(idx)];
+    }
+}
+
 template <typename AT, typename BT>
 void run_mx_tile(float* out, const uint8_t* a, const uint8_t* b_dn, const uint8_t* sfa, const uint8_t* sfb, int k,
                  const float* bias = nullptr)
@@ -83,7 +96,7 @@ void run_mx_tile(float* out, const uint8_t* a, const uint8_t* b_dn, const uint8_
     for (int k0 = 0; k0 < k; k0 += KC) {
         for (int i = 0; i < M; ++i) {
             for (int kk = 0; kk < KC; ++kk) {
-                aTile.SetElement(i, kk, AT::FromRaw(a[static_cast<size_t>(i) * k + k0 + kk]));
+                aTile.SetElement(i, kk, AT::FromRaw(mx_raw_code<AT>(a, i, k, k0 + kk)));
             }
             for (int g = 0; g < KS; ++g) {
                 saTile.SetElement(i, g, float8_e8m0_t::FromRaw(sfa[static_cast<size_t>(i) * kg + k0 / 32 + g]));
@@ -91,7 +104,7 @@ void run_mx_tile(float* out, const uint8_t* a, const uint8_t* b_dn, const uint8_
         }
         for (int j = 0; j < N; ++j) {
             for (int kk = 0; kk < KC; ++kk) {
-                bTile.SetElement(kk, j, BT::FromRaw(b_dn[static_cast<size_t>(j) * k + k0 + kk]));
+                bTile.SetElement(kk, j, BT::FromRaw(mx_raw_code<BT>(b_dn, j, k, k0 + kk)));
             }
             for (int g = 0; g < KS; ++g) {
                 sbTile.SetElement(g, j, float8_e8m0_t::FromRaw(sfb[static_cast<size_t>(j) * kg + k0 / 32 + g]));
@@ -237,7 +250,7 @@ int ref_tile_s8(int32_t* out, const int8_t* a, const int8_t* b_dn, int k)
     }
 }
 
-// fmt: 5 = e4m3, 6 = e5m2 (the pto_b200_dtype values). k must be a multiple of 128.
+// fmt: 5 = e4m3, 6 = e5m2, 7 = e2m1 packed two per byte (the pto_b200_dtype values). k must be a multiple of 128.
 int ref_tile_mx(float* out, const uint8_t* a, const uint8_t* b_dn, const uint8_t* sfa, const uint8_t* sfb, int k,
                 int a_fmt, int b_fmt)
 {
@@ -252,6 +265,8 @@ int ref_tile_mx(float* out, const uint8_t* a, const uint8_t* b_dn, const uint8_t
         run_mx_tile<float8_e4m3_t, float8_e5m2_t>(out, a, b_dn, sfa, sfb, k);
     } else if (a_fmt == 6 && b_fmt == 5) {
         run_mx_tile<float8_e5m2_t, float8_e4m3_t>(out, a, b_dn, sfa, sfb, k);
+    } else if (a_fmt == 7 && b_fmt == 7) { // MXFP4: float4_e2m1x2_t operands, two per byte
+        run_mx_tile<float4_e2m1x2_t, float4_e2m1x2_t>(out, a, b_dn, sfa, sfb, k);
     } else {
         return -1;
     }

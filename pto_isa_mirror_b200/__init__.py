@@ -9,7 +9,7 @@ and the K-split GEMM + allreduce (``ksplit``). PyTorch is used for device memory
 torch.distributed only; all arithmetic runs in the CUDA library.
 """
 from . import _capi
-from ._capi import B_DN, B_ND, BF16, E4M3, E5M2, F16, F32, S8, S32, PtoB200Error
+from ._capi import B_DN, B_ND, BF16, E2M1, E4M3, E5M2, F16, F32, S8, S32, PtoB200Error
 from .gemm import (
     cast_f32_to_bf16,
     device_status,
@@ -31,5 +31,5 @@ __all__ = [
     "gemm", "gemm_s8_dequant", "gemm_quant", "gemm_mx", "gemm_mx_pretiled", "mx_retile_scales", "gemm_mx_workspace_bytes", "gemv", "gemv_mx", "mx_quantize_e4m3", "cast_f32_to_bf16",
     "pto_gemm_basic",
     "device_status", "launch_count", "PtoB200Error",
-    "F16", "BF16", "F32", "S8", "S32", "E4M3", "E5M2", "B_DN", "B_ND",
+    "F16", "BF16", "F32", "S8", "S32", "E4M3", "E5M2", "E2M1", "B_DN", "B_ND",
 ]

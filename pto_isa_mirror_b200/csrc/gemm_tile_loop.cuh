@@ -69,6 +69,8 @@ struct GemmParams {
     long long wait_limit; // cycles one bounded wait may take before the kernel gives up (kWaitLimitCycles by default)
     int tma_store;        // CTA-pair kernels: C is 16-byte aligned with a 16-byte row pitch, so finished tiles leave
                           // through shared memory and TMA stores; 0 = per-thread global stores
+    int packed4;          // 1 when the operand tensor maps unpack 4-bit values (two per byte in memory, one per byte
+                          // in shared memory): a load then completes half the bytes it writes on its barrier
 };
 
 constexpr int kBlockM = 128;
@@ -285,9 +287,29 @@ __device__ __forceinline__ void store_words(const uint32_t (&o)[OutWords<EPI>::k
                 d4[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
             }
         } else {
+            // Rows that start off a 16-byte boundary (an odd pitch such as 8100 bf16) or the ragged last chunk: the
+            // widest pieces the address allows - 8 bytes, 4 bytes, else single values - and single values at the end.
+            const uintptr_t addr = reinterpret_cast<uintptr_t>(dst);
+            const int piece = (addr & 7u) == 0 ? 4 : ((addr & 3u) == 0 ? 2 : 1); // 16-bit values per store
+            if (piece == 4) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    if (4 * i + 4 <= n_left) {
+                        reinterpret_cast<uint2*>(dst)[i] = make_uint2(o[2 * i], o[2 * i + 1]);
+                    }
+                }
+            } else if (piece == 2) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    if (2 * i + 2 <= n_left) {
+                        reinterpret_cast<uint32_t*>(dst)[i] = o[i];
+                    }
+                }
+            }
+            const int done = piece == 1 ? 0 : (n_left >= 32 ? 32 : n_left / piece * piece);
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-                if (i < n_left) {
+                if (i >= done && i < n_left) {
                     dst[i] = static_cast<uint16_t>((o[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu);
                 }
             }
@@ -373,7 +395,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
                     if (!ok) {
                         break;
                     }
-                    ptx::mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
+                    ptx::mbar_arrive_expect_tx(&full_bar[stage], ((L::kABytes + L::kBBytes) >> p.packed4) + L::kSfaBytes + L::kSfbBytes);
                     uint8_t* a_dst = smem + L::kAOff + stage * L::kABytes;
                     uint8_t* b_dst = smem + L::kBOff + stage * L::kBBytes;
                     ptx::tma_load_2d(a_dst, &tmap_a, &full_bar[stage], kb * kBlockKElems, mi * kBlockM);

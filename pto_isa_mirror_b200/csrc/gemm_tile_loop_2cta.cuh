@@ -282,7 +282,7 @@ __global__ void __cluster_dims__(2, 1, 1)
                         break;
                     }
                     if (leader) {
-                        ptx::mbar_arrive_expect_tx(&full_bar[stage], 2u * L::kStageBytes);
+                        ptx::mbar_arrive_expect_tx(&full_bar[stage], (2u * L::kStageBytes) >> p.packed4);
                     }
                     const uint32_t full_addr = ptx::map_to_cta(ptx::smem_u32(&full_bar[stage]), 0);
                     ptx::tma_load_2d_pair(smem + L::kAOff + stage * L::kABytes, &tmap_a, full_addr, kb * kBlockKElems,

@@ -162,6 +162,29 @@ int make_tensor_map(CUtensorMap* map, int dtype, const void* base, long long row
     return PTO_B200_OK;
 }
 
+// Packed 4-bit operand (PTO_B200_E2M1, two elements per byte) as the block-scaled MMA of kind::mxf8f6f4 wants it in
+// shared memory: the TMA type 16U4_ALIGN16B expands every 8 bytes of 16 packed values to a 16-byte piece, so a row of
+// 128 elements (64 bytes in memory) fills one 128-byte swizzle row, exactly like 128 fp8 elements. rows x k_elems
+// elements, leading dimension ld_elems elements (the driver wants a 32-byte aligned base, a 32-byte pitch and k a
+// multiple of 128).
+int make_tensor_map_fp4(CUtensorMap* map, const void* base, long long rows, long long k_elems, long long ld_elems,
+                        int box_rows)
+{
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(k_elems), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_elems / 2)};
+    cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        std::snprintf(t_cuda_error, sizeof(t_cuda_error), "cuTensorMapEncodeTiled (4-bit) failed with CUresult %d",
+                      static_cast<int>(r));
+        return PTO_B200_ECUDA;
+    }
+    return PTO_B200_OK;
+}
+
 // tcgen05 instruction descriptor (dense kinds): D format [4,6), A format [7,10), B format [10,13),
 // A/B major bits 15/16 (0 = K-major), N >> 3 at [17,23), M >> 4 at [24,29).
 uint32_t make_idesc(int c_fmt, int a_fmt, int b_fmt, bool b_mn_major, int n, bool block_scaled_e8m0,
@@ -682,7 +705,9 @@ static int mx_check_args(const uint8_t* out, const uint8_t* src0, const uint8_t*
     }
     const bool a_ok = (a_dtype == PTO_B200_E4M3 || a_dtype == PTO_B200_E5M2);
     const bool b_ok = (b_dtype == PTO_B200_E4M3 || b_dtype == PTO_B200_E5M2);
-    if (!a_ok || !b_ok || !(out_dtype == PTO_B200_BF16 || out_dtype == PTO_B200_F32)) {
+    // CheckMadMxValid (include/pto/cpu/TMatmul.hpp:113-131): any mix of the fp8 types, or both operands fp4
+    const bool fp4 = (a_dtype == PTO_B200_E2M1 && b_dtype == PTO_B200_E2M1);
+    if (!((a_ok && b_ok) || fp4) || !(out_dtype == PTO_B200_BF16 || out_dtype == PTO_B200_F32)) {
         return PTO_B200_EDTYPE;
     }
     if (src2 == nullptr || src3 == nullptr) {
@@ -694,6 +719,16 @@ static int mx_check_args(const uint8_t* out, const uint8_t* src0, const uint8_t*
     }
     if (k % 32 != 0 || ld_sfa < k / 32 || ld_sfb < k / 32) {
         return PTO_B200_EINVAL;
+    }
+    if (fp4) {
+        // two elements per byte: the 4-bit TMA type wants k a multiple of 128, 32-byte aligned bases and pitches
+        if (k % 128 != 0) {
+            return PTO_B200_EINVAL;
+        }
+        if ((reinterpret_cast<uintptr_t>(src0) & 31u) || (reinterpret_cast<uintptr_t>(src1) & 31u) || (lda & 63) ||
+            (ldb & 63)) {
+            return PTO_B200_EALIGN;
+        }
     }
     return PTO_B200_OK;
 }
@@ -720,8 +755,10 @@ static int gemm_mx_impl(void* stream, uint8_t* out, const uint8_t* src0, const u
         return rc;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int a_fmt = a_dtype == PTO_B200_E5M2 ? 1 : 0;
-    const int b_fmt = b_dtype == PTO_B200_E5M2 ? 1 : 0;
+    // operand format codes of kind::mxf8f6f4: e4m3 0, e5m2 1, e2m1 5
+    const bool fp4 = (a_dtype == PTO_B200_E2M1);
+    const int a_fmt = fp4 ? 5 : (a_dtype == PTO_B200_E5M2 ? 1 : 0);
+    const int b_fmt = fp4 ? 5 : (b_dtype == PTO_B200_E5M2 ? 1 : 0);
     // Re-tile the scales, then the GEMM. `pairs` picks the two-CTA kernel (256 x 256 tiles, scale row blocks in
     // units of 128 rows: 2 per row-tile of A, 2 per column-tile of B) when the problem has enough tiles for it.
     auto run = [&](bool pairs, int block_n) -> int {
@@ -741,12 +778,23 @@ static int gemm_mx_impl(void* stream, uint8_t* out, const uint8_t* src0, const u
         p.sfb = sfb_ws;
         p.sf_a_blocks = a_blocks;
         p.sf_b_blocks = b_blocks;
+        p.packed4 = fp4 ? 1 : 0;
         CUtensorMap ta, tb, tsa, tsb;
-        if (int rc = make_tensor_map(&ta, a_dtype, src0, m, k, lda, kBlockKBytes, kBlockM)) {
-            return rc;
-        }
-        if (int rc = make_tensor_map(&tb, b_dtype, src1, n, k, ldb, kBlockKBytes, pairs ? kPairBlockN / 2 : block_n)) {
-            return rc;
+        const int b_box_rows = pairs ? kPairBlockN / 2 : block_n;
+        if (fp4) {
+            if (int rc = make_tensor_map_fp4(&ta, src0, m, k, lda, kBlockM)) {
+                return rc;
+            }
+            if (int rc = make_tensor_map_fp4(&tb, src1, n, k, ldb, b_box_rows)) {
+                return rc;
+            }
+        } else {
+            if (int rc = make_tensor_map(&ta, a_dtype, src0, m, k, lda, kBlockKBytes, kBlockM)) {
+                return rc;
+            }
+            if (int rc = make_tensor_map(&tb, b_dtype, src1, n, k, ldb, kBlockKBytes, b_box_rows)) {
+                return rc;
+            }
         }
         if (pairs) {
             const long long rows_a = static_cast<long long>(p.k_blocks) * a_blocks * 2;

@@ -12,7 +12,7 @@ from typing import Optional
 import torch
 
 from . import _capi
-from ._capi import B_DN, B_ND, BF16, E4M3, E5M2, F16, F32, S8, S32
+from ._capi import B_DN, B_ND, BF16, E2M1, E4M3, E5M2, F16, F32, S8, S32
 
 _TORCH_TO_PTO = {
     torch.float16: F16,
@@ -180,7 +180,8 @@ def gemm_mx(a: torch.Tensor, b_dn: torch.Tensor, sfa: torch.Tensor, sfb: torch.T
             out_dtype: torch.dtype = torch.bfloat16, a_fmt: int = E4M3, b_fmt: int = E4M3,
             workspace: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
             stream: Optional[torch.cuda.Stream] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """MX block-scaled fp8 GEMM (TMATMUL_MX): a [M, K] and b_dn [N, K] fp8 bytes (uint8 or torch fp8 dtypes),
+    """MX block-scaled GEMM (TMATMUL_MX): a [M, K] and b_dn [N, K] fp8 bytes (uint8 or torch fp8 dtypes), or with
+    ``a_fmt = b_fmt = E2M1`` (MXFP4) [M, K/2] and [N, K/2] bytes holding two 4-bit values each, the even element low;
     sfa [M, K/32] and sfb [N, K/32] e8m0 bytes (uint8). ``workspace`` is a uint8 CUDA tensor of at least
     ``gemm_mx_workspace_bytes(m, n, k)`` bytes; one is allocated through torch when omitted. ``bias``: n float32
     values added per column to the finished accumulator (the six-operand TMATMUL_MX)."""
@@ -189,8 +190,10 @@ def gemm_mx(a: torch.Tensor, b_dn: torch.Tensor, sfa: torch.Tensor, sfb: torch.T
         _require_cuda_2d(t, name)
         if t.element_size() != 1:
             raise ValueError(f"{name} must have one-byte elements")
-    m, k = a.shape
-    n, kb = b_dn.shape
+    # MXFP4 (a_fmt = b_fmt = E2M1): two elements per byte, so the byte tensors are [M, K/2] and [N, K/2]
+    per_byte = 2 if a_fmt == E2M1 else 1
+    m, k = a.shape[0], a.shape[1] * per_byte
+    n, kb = b_dn.shape[0], b_dn.shape[1] * (2 if b_fmt == E2M1 else 1)
     if kb != k:
         raise ValueError("inner dimensions differ")
     if k % 32 != 0 or tuple(sfa.shape) != (m, k // 32) or tuple(sfb.shape) != (n, k // 32):
@@ -205,13 +208,13 @@ def gemm_mx(a: torch.Tensor, b_dn: torch.Tensor, sfa: torch.Tensor, sfb: torch.T
             raise ValueError(f"bias must be a contiguous CUDA float32 tensor with {n} elements")
         rc = lib.pto_b200_gemm_mx_bias(_stream_ptr(stream), out.data_ptr(), a.data_ptr(), b_dn.data_ptr(),
                                        sfa.data_ptr(), sfb.data_ptr(), bias.data_ptr(), workspace.data_ptr(),
-                                       workspace.numel(), m, n, k, a.stride(0), b_dn.stride(0), out.stride(0),
-                                       sfa.stride(0), sfb.stride(0), a_fmt, b_fmt, _TORCH_TO_PTO[out.dtype])
+                                       workspace.numel(), m, n, k, a.stride(0) * per_byte, b_dn.stride(0) * per_byte,
+                                       out.stride(0), sfa.stride(0), sfb.stride(0), a_fmt, b_fmt, _TORCH_TO_PTO[out.dtype])
         _capi.check(rc, "pto_b200_gemm_mx_bias")
         return out
     rc = lib.pto_b200_gemm_mx(_stream_ptr(stream), out.data_ptr(), a.data_ptr(), b_dn.data_ptr(), sfa.data_ptr(),
-                              sfb.data_ptr(), workspace.data_ptr(), workspace.numel(), m, n, k, a.stride(0),
-                              b_dn.stride(0), out.stride(0), sfa.stride(0), sfb.stride(0), a_fmt, b_fmt,
+                              sfb.data_ptr(), workspace.data_ptr(), workspace.numel(), m, n, k, a.stride(0) * per_byte,
+                              b_dn.stride(0) * per_byte, out.stride(0), sfa.stride(0), sfb.stride(0), a_fmt, b_fmt,
                               _TORCH_TO_PTO[out.dtype])
     _capi.check(rc, "pto_b200_gemm_mx")
     return out

@@ -91,6 +91,15 @@ def main():
     save("mx_randint_e4m3_e5m2_k256", out=ref.tile_mx(a8, b8, sfa, sfb, oracle.E4M3, oracle.E5M2), a=a8, b=b8, sfa=sfa,
          sfb=sfb)
 
+    # MXFP4: float4_e2m1x2_t operands (every 4-bit code occurs), two per byte, e8m0 scales 2^-2..2^3
+    if wanted("mxfp4"):
+        a4 = gd.randint((128, 128), 0, 255, 29, 0).astype(np.uint8)       # [128, K/2] bytes, K = 256
+        b4 = gd.randint((256, 128), 0, 255, 29, 1).astype(np.uint8)
+        sfa4 = gd.randint((128, 8), 125, 130, 29, 2).astype(np.uint8)
+        sfb4 = gd.randint((256, 8), 125, 130, 29, 3).astype(np.uint8)
+        save("mxfp4_tile_k256", out=ref.tile_mx(a4, b4, sfa4, sfb4, oracle.E2M1, oracle.E2M1), a=a4, b=b4, sfa=sfa4,
+             sfb=sfb4)
+
     # bias forms: TMATMUL_BIAS on the first chunk then TMATMUL_ACC (fp16 and int8), six-operand TMATMUL_MX
     if wanted("bias"):
         a, b = gd.dense_inputs(128, 256, 256, "f16", 7, "uniform")

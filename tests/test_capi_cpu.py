@@ -62,6 +62,10 @@ def test_argument_errors_come_before_any_launch(lib):
     assert mx(None, p, p, p, p, p, p, 1 << 20, 16, 16, 48, 48, 48, 16, 2, 2, E4M3, E4M3, BF16) == _capi.EINVAL   # k % 32
     assert mx(None, p, p, p, p, p, p, 1 << 20, 16, 16, 64, 64, 64, 16, 2, 2, S8, E4M3, BF16) == _capi.EDTYPE
     assert mx(None, p, p, p, p, p, p, 1 << 20, 16, 16, 64, 64, 64, 16, 2, 2, E4M3, E5M2, F16 + 0) == _capi.EDTYPE
+    E2M1 = _capi.E2M1
+    assert mx(None, p, p, p, p, p, p, 1 << 20, 16, 16, 128, 128, 128, 16, 4, 4, E2M1, E4M3, BF16) == _capi.EDTYPE   # fp4 x fp8
+    assert mx(None, p, p, p, p, p, p, 1 << 20, 16, 16, 64, 64, 64, 16, 2, 2, E2M1, E2M1, BF16) == _capi.EINVAL     # fp4: k % 128
+    assert mx(None, p, p, p, p, p, p, 1 << 20, 16, 16, 128, 160, 128, 16, 4, 4, E2M1, E2M1, BF16) == _capi.EALIGN  # fp4: lda % 64
     assert mx(None, p, p, p, p, p, None, 0, 16, 16, 64, 64, 64, 16, 2, 2, E4M3, E4M3, BF16) == _capi.EWORKSPACE
     assert mx(None, p, p, p, p, p, p, 16, 16, 16, 64, 64, 64, 16, 2, 2, E4M3, E4M3, BF16) == _capi.EWORKSPACE   # too small
     gb = lib.pto_b200_gemm_bias

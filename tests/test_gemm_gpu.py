@@ -441,13 +441,16 @@ def test_pair_kernel_store_paths_agree(kind):
         odt = torch.bfloat16
         run = lambda out: pto.gemm_mx(ta, tb, tsa, tsb, out=out)  # noqa: E731
     results = []
-    for pitch in (n + 12, n + 5):        # n + 12: 16-byte multiple for 2- and 4-byte elements (TMA); n + 5: odd pitch
+    # n + 12: 16-byte multiple for 2- and 4-byte elements (TMA); n + 5: odd pitch; n + 2 and n + 4: 16-bit rows that
+    # start on 4- and 8-byte boundaries (the register path's narrower pieces)
+    for pitch in (n + 12, n + 5, n + 2, n + 4):
         buf = torch.full((m + 2, pitch), fill, dtype=odt, device=DEV)
         run(buf[1:m + 1, :n])
         got = buf.cpu()
         assert (got[0] == fill).all() and (got[m + 1] == fill).all() and (got[:, n:] == fill).all()
         results.append(got[1:m + 1, :n].contiguous())
-    assert torch.equal(results[0].view(torch.uint8), results[1].view(torch.uint8))
+    for other in results[1:]:
+        assert torch.equal(results[0].view(torch.uint8), other.view(torch.uint8))
     if kind == "s32":
         assert np.array_equal(results[0].numpy()[:128, :256], oracle.gemm_s8(a[:128], b[:256]))
 
@@ -492,3 +495,40 @@ def test_mx_pretiled_scales_match_the_one_call_form(m, n, k):
     assert torch.equal(got.view(torch.int32), want.view(torch.int32))
     ref = oracle.gemm_mx(a[:128], b[:128], sfa[:128], sfb[:128])
     assert max_rel_err(host(got)[:128, :128], ref) <= MX_TOL
+
+
+# ------------------------------------------------------------------ MXFP4 (float4_e2m1x2_t operands, e8m0 block scales)
+
+def test_mxfp4_golden_tile_exact():
+    """The reference's own outputs for a 128 x 256 x 256 fp4 tile: every sum is exact in fp32, so the bits must match."""
+    g = golden("mxfp4_tile_k256")
+    out = pto.gemm_mx(dev8(g["a"]), dev8(g["b"]), dev8(g["sfa"]), dev8(g["sfb"]), torch.float32, pto.E2M1, pto.E2M1)
+    assert np.array_equal(host(out), g["out"])
+
+
+@pytest.mark.parametrize("m,n,k", [(2560, 2560, 512), (2040, 2500, 384), (300, 520, 1152)])
+def test_mxfp4_against_the_oracle(m, n, k):
+    """Random 4-bit codes with scales 2^-1..2^1 on the two-CTA kernel (100 tiles; 80 ragged ones) and on a ragged one-CTA shape: exact
+    against the oracle's chain on sampled rows; the bf16 store is the RNE cast of the fp32 result."""
+    a = gd.randint((m, k // 2), 0, 255, 31, 0).astype(np.uint8)
+    b = gd.randint((n, k // 2), 0, 255, 31, 1).astype(np.uint8)
+    sfa = gd.randint((m, k // 32), 126, 128, 31, 2).astype(np.uint8)
+    sfb = gd.randint((n, k // 32), 126, 128, 31, 3).astype(np.uint8)
+    out = host(pto.gemm_mx(dev8(a), dev8(b), dev8(sfa), dev8(sfb), torch.float32, pto.E2M1, pto.E2M1))
+    for r0 in (0, m - 128):
+        ref = oracle.gemm_mx(a[r0:r0 + 128], b, sfa[r0:r0 + 128], sfb, oracle.E2M1, oracle.E2M1)
+        assert np.array_equal(out[r0:r0 + 128], ref)
+    out16 = host(pto.gemm_mx(dev8(a), dev8(b), dev8(sfa), dev8(sfb), torch.bfloat16, pto.E2M1, pto.E2M1))
+    assert np.array_equal(out16, gd.f32_to_bf16_bits(out))
+
+
+def test_mxfp4_rejects_mixed_and_misaligned_operands():
+    a = torch.zeros((128, 64), dtype=torch.uint8, device=DEV)
+    s = torch.full((128, 4), 127, dtype=torch.uint8, device=DEV)
+    with pytest.raises(pto.PtoB200Error) as e:
+        b8 = torch.zeros((128, 128), dtype=torch.uint8, device=DEV)
+        pto.gemm_mx(a, b8, s, s, torch.float32, pto.E2M1, pto.E4M3)      # fp4 x fp8 is not in CheckMadMxValid's table
+    assert e.value.code == 3
+    with pytest.raises(pto.PtoB200Error) as e:
+        pto.gemm_mx(a[:, :48], a[:, :48], s[:, :3], s[:, :3], torch.float32, pto.E2M1, pto.E2M1)   # K = 96
+    assert e.value.code in (1, 2)
