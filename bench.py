@@ -50,6 +50,9 @@ WORKLOADS = {
     "bf16_4096": dict(kind="dense", m=4096, n=4096, k=4096, dtype="bf16", out="bf16"),
     "s8_8192_dequant": dict(kind="s8", m=8192, n=8192, k=8192),
     "mxfp8_16384x8192x8192": dict(kind="mx", m=16384, n=8192, k=8192),
+    # the reference's MXFP8 kernel as it ships: e5m2 x e5m2, bf16 out, 6144^3
+    # (kernels/manual/a5/matmul_mxfp8_performance/mxmatmul_performance_kernel.cpp:354-380)
+    "mxfp8_e5m2_6144cubed": dict(kind="mx", m=6144, n=6144, k=6144, fmt="e5m2"),
     # the shape of the reference's MXFP4 kernel (kernels/manual/a5/matmul_mxfp4_performance/mxmatmul_performance_kernel.cpp:
     # 446-463): float4_e2m1x2_t operands, e8m0 scales, bf16 out, ragged M and N
     "mxfp4_2040x8100x8192": dict(kind="mx", m=2040, n=8100, k=8192, fmt="e2m1"),
@@ -64,6 +67,9 @@ WORKLOADS = {
     # HBM-bound neighbours of the tile loop (metric GB/s of algorithmic bytes)
     "gemv_bf16_8192x8192": dict(kind="gemv", m=1, n=8192, k=8192),
     "mx_quantize_8192x8192": dict(kind="quant", m=8192, n=1, k=8192),
+    # the same two kernels on four times the bytes: start-up and the last blocks weigh less
+    "gemv_bf16_8192x32768": dict(kind="gemv", m=1, n=32768, k=8192),
+    "mx_quantize_32768x8192": dict(kind="quant", m=32768, n=1, k=8192),
 }
 
 
@@ -160,10 +166,13 @@ def _randn_scaled(shape, k, dtype, gen, dev):
     return (torch.randn(shape, generator=gen, device=dev, dtype=torch.float32) / (k ** 0.5)).to(dtype)
 
 
-def mx_quantize_torch(x):
+def mx_quantize_torch(x, fp8=None):
     """OCP MX quantisation along K in blocks of 32 (include/pto/cpu/TQuant.hpp:178-190,226-237,461-494), as data
-    preparation on the device: e8m0 = max(biased_exp(absmax) - 8, 0), element = e4m3fn(x * 2^(127 - e8m0))."""
+    preparation on the device: e8m0 = max(biased_exp(absmax) - 8, 0), element = e4m3fn(x * 2^(127 - e8m0)); with
+    ``fp8 = torch.float8_e5m2`` the scaled values (at most 448 in magnitude) are stored as e5m2 instead."""
     import torch
+
+    fp8 = fp8 or torch.float8_e4m3fn
 
     rows, k = x.shape
     g = x.view(rows, k // 32, 32)
@@ -172,7 +181,7 @@ def mx_quantize_torch(x):
     e8m0 = torch.clamp(exp - 8, min=0)
     scaling = ((254 - e8m0) << 23).view(torch.float32)
     y = (g * scaling.unsqueeze(-1)).clamp(-448.0, 448.0)
-    return y.to(torch.float8_e4m3fn).view(torch.uint8).view(rows, k), e8m0.to(torch.uint8)
+    return y.to(fp8).view(torch.uint8).view(rows, k), e8m0.to(torch.uint8)
 
 
 # --------------------------------------------------------------------------------------- parity (outside timed regions)
@@ -344,13 +353,16 @@ def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=8, 
         step.parity = parity
         return step, flops, per_set * sets, sets
     if kind == "mx":
-        a, sfa = mx_quantize_torch(torch.randn((m, k), generator=gen, device=dev))
-        b, sfb = mx_quantize_torch(torch.randn((n, k), generator=gen, device=dev))
+        e5m2 = spec.get("fmt") == "e5m2"
+        fp8 = torch.float8_e5m2 if e5m2 else torch.float8_e4m3fn
+        fmt = pto.E5M2 if e5m2 else pto.E4M3
+        a, sfa = mx_quantize_torch(torch.randn((m, k), generator=gen, device=dev), fp8)
+        b, sfb = mx_quantize_torch(torch.randn((n, k), generator=gen, device=dev), fp8)
         c = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
         ws = torch.empty(pto.gemm_mx_workspace_bytes(m, n, k), dtype=torch.uint8, device=dev)
 
         def step(i):
-            pto.gemm_mx(a, b, sfa, sfb, workspace=ws, out=c)
+            pto.gemm_mx(a, b, sfa, sfb, torch.bfloat16, fmt, fmt, workspace=ws, out=c)
 
         # the same product with the scales re-tiled once beforehand (weights' scales, or a producer that writes the
         # tiled form): one kernel launch per step
@@ -358,7 +370,7 @@ def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=8, 
         c2 = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
 
         def pretiled(i):
-            pto.gemm_mx_pretiled(a, b, ws_tiled, out=c2)
+            pto.gemm_mx_pretiled(a, b, ws_tiled, torch.bfloat16, fmt, fmt, out=c2)
 
         step.pretiled = pretiled
         step.pretiled_matches = lambda: bool(torch.equal(c.view(torch.int16), c2.view(torch.int16)))
@@ -366,13 +378,14 @@ def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=8, 
         def parity():
             import oracle
 
-            pto.gemm_mx(a, b, sfa, sfb, workspace=ws, out=c)
-            c32 = pto.gemm_mx(a, b, sfa, sfb, torch.float32, workspace=ws)
+            step(0)
+            c32 = pto.gemm_mx(a, b, sfa, sfb, torch.float32, fmt, fmt, workspace=ws)
             torch.cuda.synchronize(dev)
+            ofmt = oracle.E5M2 if e5m2 else oracle.E4M3
             acc, out16, refs = [], [], []
             for r0, c0 in _tile_origins(m, n, 2, 103):
                 refs.append(oracle.gemm_mx(a[r0:r0 + 128].cpu().numpy(), b[c0:c0 + 256].cpu().numpy(),
-                                           sfa[r0:r0 + 128].cpu().numpy(), sfb[c0:c0 + 256].cpu().numpy()))
+                                           sfa[r0:r0 + 128].cpu().numpy(), sfb[c0:c0 + 256].cpu().numpy(), ofmt, ofmt))
                 acc.append(c32[r0:r0 + 128, c0:c0 + 256].cpu().numpy())
                 out16.append(_bits16(c[r0:r0 + 128, c0:c0 + 256]))
             rep = _dense_tile_report(acc, None, refs, 1e-2)
@@ -668,28 +681,32 @@ def aux_configs(dev, peaks):
         out[f"f16_f32_{size}cubed"] = entry
         del step
         torch.cuda.empty_cache()
-    # TGEMV: bf16 8192 x 8192 B per launch, 4 rotating matrices (512 MiB > L2)
-    n = k = 8192
-    mats = [_randn_scaled((n, k), k, torch.bfloat16, gen, dev) for _ in range(4)]
-    x = _randn_scaled((k,), k, torch.bfloat16, gen, dev)
-    y = torch.empty((n,), dtype=torch.float32, device=dev)
-    ms = time_steps(lambda i: pto.gemv(x, mats[i % 4], out=y), 40, 5, dev, 1) / 40
-    gbytes = (n * k * 2 + k * 2 + n * 4) / 1e9
-    out["gemv_bf16_8192x8192"] = {"gbs": gbytes / (ms * 1e-3), "ms": ms, "bytes": int(gbytes * 1e9),
-                                  "frac_of_hbm_peak": gbytes / (ms * 1e-3) / peak_gbs, "peak_gbs": peak_gbs}
-    del mats
-    torch.cuda.empty_cache()
-    # MX quantiser: fp32 8192 x 8192 per launch (256 MiB read + 66 MiB written), 2 rotating sources
-    rows = kq = 8192
-    srcs = [torch.randn((rows, kq), generator=gen, device=dev) for _ in range(2)]
-    q_data = torch.empty((rows, kq), dtype=torch.uint8, device=dev)
-    q_scales = torch.empty((rows, kq // 32), dtype=torch.uint8, device=dev)
-    ms = time_steps(lambda i: pto.mx_quantize_e4m3(srcs[i % 2], data=q_data, scales=q_scales), 20, 3, dev, 1) / 20
-    gbytes = rows * kq * (4 + 1 + 1 / 32) / 1e9
-    out["mx_quantize_8192x8192"] = {"gbs": gbytes / (ms * 1e-3), "ms": ms, "bytes": int(gbytes * 1e9),
-                                    "frac_of_hbm_peak": gbytes / (ms * 1e-3) / peak_gbs, "peak_gbs": peak_gbs}
-    del srcs, q_data, q_scales
-    torch.cuda.empty_cache()
+    # TGEMV: bf16 n x 8192 matrix per launch, rotating matrices (at least 512 MiB > L2); the larger one shows how
+    # much of the small one's gap is start-up and the last blocks
+    k = 8192
+    for n in (8192, 32768):
+        count = 4 if n == 8192 else 2
+        mats = [_randn_scaled((n, k), k, torch.bfloat16, gen, dev) for _ in range(count)]
+        x = _randn_scaled((k,), k, torch.bfloat16, gen, dev)
+        y = torch.empty((n,), dtype=torch.float32, device=dev)
+        ms = time_steps(lambda i: pto.gemv(x, mats[i % count], out=y), 40, 5, dev, 1) / 40
+        gbytes = (n * k * 2 + k * 2 + n * 4) / 1e9
+        out[f"gemv_bf16_8192x{n}"] = {"gbs": gbytes / (ms * 1e-3), "ms": ms, "bytes": int(gbytes * 1e9),
+                                      "frac_of_hbm_peak": gbytes / (ms * 1e-3) / peak_gbs, "peak_gbs": peak_gbs}
+        del mats
+        torch.cuda.empty_cache()
+    # MX quantiser: fp32 rows x 8192 per launch (4 bytes read + 1 1/32 written per element), 2 rotating sources
+    kq = 8192
+    for rows in (8192, 32768):
+        srcs = [torch.randn((rows, kq), generator=gen, device=dev) for _ in range(2)]
+        q_data = torch.empty((rows, kq), dtype=torch.uint8, device=dev)
+        q_scales = torch.empty((rows, kq // 32), dtype=torch.uint8, device=dev)
+        ms = time_steps(lambda i: pto.mx_quantize_e4m3(srcs[i % 2], data=q_data, scales=q_scales), 20, 3, dev, 1) / 20
+        gbytes = rows * kq * (4 + 1 + 1 / 32) / 1e9
+        out[f"mx_quantize_{rows}x8192"] = {"gbs": gbytes / (ms * 1e-3), "ms": ms, "bytes": int(gbytes * 1e9),
+                                           "frac_of_hbm_peak": gbytes / (ms * 1e-3) / peak_gbs, "peak_gbs": peak_gbs}
+        del srcs, q_data, q_scales
+        torch.cuda.empty_cache()
     return out
 
 
@@ -849,7 +866,7 @@ def reference_arm(args, world, rank):
         "impl": "reference", "metric": "gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": el / max(args.steps, 1) * 1e3,
         "higher_is_better": True, "scaling": "strong" if kind == "ksplit" else "weak", "vs_baseline": None,
-        "dtype": "mxfp4_e2m1" if spec.get("fmt") == "e2m1" else
+        "dtype": "mxfp4_e2m1" if spec.get("fmt") == "e2m1" else "mxfp8_e5m2" if spec.get("fmt") == "e5m2" else
                  {"dense": "bf16", "ksplit": "bf16", "allgather": "bf16", "s8": "s8", "mx": "mxfp8_e4m3"}[kind],
         "data": "synthetic",
         "config": {"workload": name, "m": spec["m"], "n": spec["n"], "k": spec["k"],
@@ -946,6 +963,8 @@ def main():
              "mx": "mxfp8_e4m3", "gemv": "bf16", "quant": "f32"}[kind]
     if spec.get("fmt") == "e2m1":
         dtype = "mxfp4_e2m1"   # through kind::mxf8f6f4: 4-bit operands in memory, the 8-bit kinds' tensor rate
+    elif spec.get("fmt") == "e5m2":
+        dtype = "mxfp8_e5m2"
     peak_scale = {"s8": 2.0, "mx": 2.0}.get(kind, 1.0)
     # a single kernel timed back to back for a short region: burst peak; the long K-split step: sustained
     peak_key = "bf16_tflops" if ms < 500.0 else "bf16_tflops_sustained"
@@ -1051,7 +1070,8 @@ def main():
                 line["e2e"]["pipeline_error"] = repr(e)
         # the other single-GPU configurations, briefly
         others = {}
-        for oname in ("c1_f16_128x256x256", "s8_8192_dequant", "mxfp8_16384x8192x8192", "ksplit_bf16_8192x65536x8192"):
+        for oname in ("c1_f16_128x256x256", "s8_8192_dequant", "mxfp8_16384x8192x8192", "mxfp8_e5m2_6144cubed",
+                      "mxfp4_2040x8100x8192", "ksplit_bf16_8192x65536x8192"):
             if oname == name:
                 continue
             try:

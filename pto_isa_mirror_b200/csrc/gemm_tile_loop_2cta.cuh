@@ -109,6 +109,18 @@ __device__ __forceinline__ void st_relaxed_sys_b128(void* ptr, const uint4& v)
                  : "memory");
 }
 
+// Ring stages and store boxes per TSTORE warp of the block-scaled instantiations (one accumulator, so the read-back
+// is not hidden behind the next tile's MMAs). Measured on 16384 x 8192 x 8192: 6 stages + 1 box, 5 + 2, 5 + 3 and
+// 4 + 4 all take 0.886-0.895 ms, so neither the ring depth nor a wait for a store box limits this kernel.
+#ifndef PTO_B200_MX_PAIR_STAGES
+#define PTO_B200_MX_PAIR_STAGES 6
+#endif
+#ifndef PTO_B200_MX_EPI_BUFS
+#define PTO_B200_MX_EPI_BUFS 1
+#endif
+template <int KIND>
+inline constexpr int kPairEpiBufs = (KIND == KIND_MXF8) ? PTO_B200_MX_EPI_BUFS : 2;
+
 template <int KIND, int STAGES, int EPI_BUFS>
 struct PairSmemLayout {
     static constexpr int kABytes = kBlockM * kBlockKBytes;        // this CTA's 128 rows of A
@@ -189,7 +201,7 @@ __global__ void __cluster_dims__(2, 1, 1)
 {
     constexpr bool FUSED_AR = (COMM == COMM_KSPLIT);
     static_assert(COMM != COMM_GATHER || KIND == KIND_F16, "the all-gather form multiplies 16-bit inputs");
-    constexpr int kEpiBufs = (KIND == KIND_MXF8) ? 1 : 2;
+    constexpr int kEpiBufs = kPairEpiBufs<KIND>;
     using L = PairSmemLayout<KIND, STAGES, kEpiBufs>;
     constexpr int kNumAcc = (KIND == KIND_MXF8) ? 1 : 2;
     constexpr int kAccCols = 256;

@@ -273,8 +273,8 @@ int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& t
 #ifndef PTO_B200_PAIR_STAGES
 #define PTO_B200_PAIR_STAGES 6
 #endif
-    constexpr int STAGES = (KIND == KIND_MXF8) ? 6 : PTO_B200_PAIR_STAGES;
-    constexpr int kEpiBufs = (KIND == KIND_MXF8) ? 1 : 2;
+    constexpr int STAGES = (KIND == KIND_MXF8) ? PTO_B200_MX_PAIR_STAGES : PTO_B200_PAIR_STAGES;
+    constexpr int kEpiBufs = kPairEpiBufs<KIND>;
     constexpr bool FUSED_AR = (COMM == COMM_KSPLIT);
     constexpr int kThreads = kNumThreads + (COMM != COMM_NONE ? kExchangeThreads : 0);
     using L = PairSmemLayout<KIND, STAGES, kEpiBufs>;
