@@ -17,6 +17,28 @@ import torch
 import torch.distributed as dist
 
 
+BLOCK_ROWS = 256   # rows of A one arrival flag covers: one row of 256 x 256 output tiles
+
+
+def slice_rows(m: int, world: int, rank: int) -> tuple[int, int]:
+    """Rows [r0, r1) of A that rank ``rank`` owns: m / world consecutive rows, a whole number of 256-row blocks."""
+    if world < 1 or not 0 <= rank < world or m % (BLOCK_ROWS * world):
+        raise ValueError("m must be a multiple of 256 * ranks")
+    rows = m // world
+    return rank * rows, (rank + 1) * rows
+
+
+def block_schedule(m: int, world: int, rank: int) -> list[tuple[int, int]]:
+    """The order in which rank ``rank``'s tile loop visits the 256-row blocks of A, as (block, owner) pairs: the raster
+    is rotated so that the rank's own blocks come first (they need no arrival flag) and the remote ones follow in the
+    order their owners push them."""
+    r0, _ = slice_rows(m, world, rank)
+    blocks = m // BLOCK_ROWS
+    per_rank = blocks // world
+    first = r0 // BLOCK_ROWS
+    return [((first + i) % blocks, ((first + i) % blocks) // per_rank) for i in range(blocks)]
+
+
 class AllGatherGemm:
     """``a_local()`` is this rank's slice of the symmetric A buffer: write the slice there, then ``step(b_dn)``.
 
@@ -81,8 +103,8 @@ class AllGatherGemm:
         torch.cuda.synchronize(self.device)
 
     def a_local(self) -> torch.Tensor:
-        rows = self.m // self.world_size
-        return self.a_full[self.rank * rows:(self.rank + 1) * rows]
+        r0, r1 = slice_rows(self.m, self.world_size, self.rank)
+        return self.a_full[r0:r1]
 
     def step(self, b_dn: torch.Tensor) -> torch.Tensor:
         """b_dn: B column-major [n, k], identical on every rank. Returns this rank's C [m, n] (rewritten by the next step)."""

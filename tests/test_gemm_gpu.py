@@ -532,3 +532,34 @@ def test_mxfp4_rejects_mixed_and_misaligned_operands():
     with pytest.raises(pto.PtoB200Error) as e:
         pto.gemm_mx(a[:, :48], a[:, :48], s[:, :3], s[:, :3], torch.float32, pto.E2M1, pto.E2M1)   # K = 96
     assert e.value.code in (1, 2)
+
+
+# ------------------------------------------------------------------ the largest index ranges
+
+@pytest.mark.parametrize("kind", ["bf16", "s8"])
+def test_output_beyond_two_to_the_31_elements(kind):
+    """49152 x 49152 outputs (2.4e9 elements, 36 864 tiles): element offsets into C pass 2^31, so every offset the
+    store path forms must be 64-bit. Small integers keep every sum exact; tiles at the far corners, in the middle and
+    around the 2^31-th element are compared with the oracle's chain."""
+    m = n = 49152
+    k = 128
+    if kind == "bf16":
+        a = gd.f32_to_bf16_bits(gd.randint((m, k), -4, 4, 81, 0).astype(np.float32))
+        b = gd.f32_to_bf16_bits(gd.randint((n, k), -4, 4, 81, 1).astype(np.float32))
+        ta, tb = dev16(a, torch.bfloat16), dev16(b, torch.bfloat16)
+        out = pto.gemm(ta, tb, torch.bfloat16)
+        ref_tile = lambda r0, c0: gd.f32_to_bf16_bits(oracle.gemm_f32acc(a[r0:r0 + 128], b[c0:c0 + 256], oracle.BF16))  # noqa: E731
+        got_tile = lambda r0, c0: host(out[r0:r0 + 128, c0:c0 + 256].contiguous())  # noqa: E731
+    else:
+        a, b, _, _ = gd.s8_inputs(m, n, k, 82)
+        ta, tb = dev8(a), dev8(b)
+        out = pto.gemm(ta, tb)                                   # int32 accumulators
+        ref_tile = lambda r0, c0: oracle.gemm_s8(a[r0:r0 + 128], b[c0:c0 + 256])  # noqa: E731
+        got_tile = lambda r0, c0: host(out[r0:r0 + 128, c0:c0 + 256].contiguous())  # noqa: E731
+    assert out.numel() > 2 ** 31
+    row_2_31 = (2 ** 31) // n                                    # the row that holds element 2^31
+    for r0, c0 in ((0, 0), (m - 128, n - 256), (m - 128, 0), (0, n - 256), (24576, 24576),
+                   (row_2_31 - 64, 33792), (row_2_31 - 64, 0)):
+        assert np.array_equal(got_tile(r0, c0), ref_tile(r0, c0)), (r0, c0)
+    del out
+    torch.cuda.empty_cache()

@@ -95,3 +95,61 @@ def test_ksplit_two_ranks_gloo(tmp_path, mode):
     unsplit = oracle.gemm_f32acc(a_bits, b_bits, oracle.BF16)
     got = gd.bf16_bits_to_f32(outs[0])
     assert np.abs(got - unsplit).max() / np.abs(unsplit).max() <= 8e-3  # bf16 output rounding dominates
+
+
+# ------------------------------------------------------------------ AllGather + GEMM: the schedule, under gloo
+
+def test_allgather_block_schedule():
+    from pto_isa_mirror_b200.allgather import block_schedule, slice_rows
+
+    assert slice_rows(8192, 2, 1) == (4096, 8192)
+    assert [slice_rows(2048, 4, r) for r in range(4)] == [(0, 512), (512, 1024), (1024, 1536), (1536, 2048)]
+    with pytest.raises(ValueError):
+        slice_rows(1000, 2, 0)
+    for world in (1, 2, 4, 8):
+        m = 256 * world * 3
+        for rank in range(world):
+            order = block_schedule(m, world, rank)
+            assert sorted(b for b, _ in order) == list(range(m // 256))          # every block exactly once
+            assert all(owner == rank for _, owner in order[:3])                   # own rows first: no waiting
+            assert all(owner == b // 3 for b, owner in order)
+    assert block_schedule(1024, 2, 1) == [(2, 1), (3, 1), (0, 0), (1, 0)]
+
+
+def _allgather_worker(rank, world, port, m, n, k, result_dir):
+    import oracle
+    from pto_isa_mirror_b200.allgather import block_schedule, slice_rows
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        a_bits, b_bits = gd.dense_inputs(m, n, k, "bf16", 9)
+        r0, r1 = slice_rows(m, world, rank)
+        mine = torch.from_numpy(a_bits[r0:r1].view(np.uint8).copy())              # this rank holds only its M slice
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)                                              # the pushes of every owner
+        gathered = torch.cat(parts).numpy().view(np.uint16)
+        out = np.zeros((m, n), dtype=np.float32)
+        for block, owner in block_schedule(m, world, rank):                       # the tile loop's order of row blocks
+            rows = slice(block * 256, (block + 1) * 256)
+            assert slice_rows(m, world, owner)[0] <= rows.start < slice_rows(m, world, owner)[1]
+            out[rows] = oracle.gemm_f32acc(gathered[rows], b_bits, oracle.BF16, threads=2)
+        np.save(os.path.join(result_dir, f"ag_out_{rank}.npy"), out)
+        np.save(os.path.join(result_dir, f"ag_a_{rank}.npy"), gathered)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_allgather_gemm_two_ranks_gloo(tmp_path):
+    """Two CPU ranks each hold half of A's rows; after the gather every rank multiplies all row blocks in its own
+    schedule order and must hold the whole product, bit-identical on both ranks and to the unsplit product."""
+    import oracle
+
+    m, n, k = 1024, 64, 128
+    mp.spawn(_allgather_worker, args=(2, _free_port(), m, n, k, str(tmp_path)), nprocs=2, join=True)
+    a_bits, b_bits = gd.dense_inputs(m, n, k, "bf16", 9)
+    ref = oracle.gemm_f32acc(a_bits, b_bits, oracle.BF16, threads=2)
+    for r in range(2):
+        assert np.array_equal(np.load(tmp_path / f"ag_a_{r}.npy"), a_bits)
+        assert np.array_equal(np.load(tmp_path / f"ag_out_{r}.npy"), ref)
