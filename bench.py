@@ -69,6 +69,7 @@ WORKLOADS = {
     "mx_quantize_8192x8192": dict(kind="quant", m=8192, n=1, k=8192),
     # the same two kernels on four times the bytes: start-up and the last blocks weigh less
     "gemv_bf16_8192x32768": dict(kind="gemv", m=1, n=32768, k=8192),
+    "gemv_mx_e4m3_8192x32768": dict(kind="gemv_mx", m=1, n=32768, k=8192),
     "mx_quantize_32768x8192": dict(kind="quant", m=32768, n=1, k=8192),
 }
 
@@ -562,6 +563,27 @@ def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=8, 
         step.parity = parity
         step.bytes = n * k * 2 + k * 2 + n * 4
         return step, 2.0 * n * k, 4 * n * k * 2, 4
+    if kind == "gemv_mx":
+        xq, sfx = mx_quantize_torch(torch.randn((1, k), generator=gen, device=dev))
+        mats = [mx_quantize_torch(torch.randn((n, k), generator=gen, device=dev)) for _ in range(2)]   # 2 x 264 MiB > L2
+        y = torch.empty((n,), dtype=torch.float32, device=dev)
+
+        def step(i):
+            pto.gemv_mx(xq[0], mats[i % 2][0], sfx[0], mats[i % 2][1], out=y)
+
+        def parity():
+            import oracle
+
+            pto.gemv_mx(xq[0], mats[0][0], sfx[0], mats[0][1], out=y)
+            torch.cuda.synchronize(dev)
+            ref = oracle.gemm_mx(xq.cpu().numpy(), mats[0][0][:256].cpu().numpy(), sfx.cpu().numpy(),
+                                 mats[0][1][:256].cpu().numpy())[0]
+            err = float(np.abs(y[:256].cpu().numpy() - ref).max() / np.abs(ref).max())
+            return {"columns": 256, "max_rel_err": err, "tol": 1e-2, "ok": bool(err <= 1e-2)}
+
+        step.parity = parity
+        step.bytes = n * k + n * k // 32 + k + k // 32 + n * 4
+        return step, 2.0 * n * k, 2 * (n * k + n * k // 32), 2
     if kind == "quant":
         srcs = [torch.randn((m, k), generator=gen, device=dev) for _ in range(2)]             # 512 MiB > L2
         q_data = torch.empty((m, k), dtype=torch.uint8, device=dev)
@@ -695,6 +717,32 @@ def aux_configs(dev, peaks):
                                       "frac_of_hbm_peak": gbytes / (ms * 1e-3) / peak_gbs, "peak_gbs": peak_gbs}
         del mats
         torch.cuda.empty_cache()
+    # TGEMV_MX: one e4m3 row against a block-scaled e4m3 matrix of 32768 x 8192 (256 MiB + 8 MiB of scales per
+    # launch, 2 rotating matrices), checked against the oracle's chain on the first 256 columns
+    n = 32768
+    xq, sfx = mx_quantize_torch(torch.randn((1, k), generator=gen, device=dev))
+    mats = [mx_quantize_torch(torch.randn((n, k), generator=gen, device=dev)) for _ in range(2)]
+    y = torch.empty((n,), dtype=torch.float32, device=dev)
+    ms = time_steps(lambda i: pto.gemv_mx(xq[0], mats[i % 2][0], sfx[0], mats[i % 2][1], out=y), 40, 5, dev, 1) / 40
+    gbytes = (n * k + n * k // 32 + k + k // 32 + n * 4) / 1e9
+    entry = {"gbs": gbytes / (ms * 1e-3), "ms": ms, "bytes": int(gbytes * 1e9),
+             "frac_of_hbm_peak": gbytes / (ms * 1e-3) / peak_gbs, "peak_gbs": peak_gbs}
+    try:
+        import numpy as np
+
+        import oracle
+
+        pto.gemv_mx(xq[0], mats[0][0], sfx[0], mats[0][1], out=y)
+        torch.cuda.synchronize(dev)
+        ref = oracle.gemm_mx(xq.cpu().numpy(), mats[0][0][:256].cpu().numpy(), sfx.cpu().numpy(),
+                             mats[0][1][:256].cpu().numpy())[0]
+        err = float(np.abs(y[:256].cpu().numpy() - ref).max() / np.abs(ref).max())
+        entry["parity"] = {"columns": 256, "max_rel_err": err, "tol": 1e-2, "ok": bool(err <= 1e-2)}
+    except Exception as e:  # noqa: BLE001
+        entry["parity"] = {"ok": False, "error": repr(e)[:300]}
+    out["gemv_mx_e4m3_8192x32768"] = entry
+    del mats
+    torch.cuda.empty_cache()
     # MX quantiser: fp32 rows x 8192 per launch (4 bytes read + 1 1/32 written per element), 2 rotating sources
     kq = 8192
     for rows in (8192, 32768):
@@ -960,7 +1008,7 @@ def main():
 
     kind = spec["kind"]
     dtype = {"dense": spec.get("dtype", "bf16"), "ksplit": "bf16", "ksplit1": "bf16", "allgather": "bf16", "s8": "s8",
-             "mx": "mxfp8_e4m3", "gemv": "bf16", "quant": "f32"}[kind]
+             "mx": "mxfp8_e4m3", "gemv": "bf16", "gemv_mx": "mxfp8_e4m3", "quant": "f32"}[kind]
     if spec.get("fmt") == "e2m1":
         dtype = "mxfp4_e2m1"   # through kind::mxf8f6f4: 4-bit operands in memory, the 8-bit kinds' tensor rate
     elif spec.get("fmt") == "e5m2":
@@ -1012,7 +1060,7 @@ def main():
     if par is not None:
         line["parity"] = par
 
-    if kind in ("gemv", "quant"):
+    if kind in ("gemv", "gemv_mx", "quant"):
         # HBM-bound neighbours: GB/s of algorithmic bytes against the measured copy bandwidth
         gbs = step.bytes / (ms_per_step * 1e-3) / 1e9
         hbm = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))

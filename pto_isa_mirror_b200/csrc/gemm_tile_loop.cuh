@@ -336,7 +336,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
                    const GemmParams p)
 {
     using L = SmemLayout<KIND, BLOCK_N, STAGES>;
-    static_assert(BLOCK_N % 32 == 0 && BLOCK_N >= 32 && BLOCK_N <= 256, "BLOCK_N");
+    static_assert((BLOCK_N == 32 || BLOCK_N % 64 == 0) && BLOCK_N <= 256, "BLOCK_N");
     static_assert(!B_MN_MAJOR || (KIND == KIND_F16 && BLOCK_N % 64 == 0), "N-major B is for 16-bit inputs");
     // Block-scaled tiles keep their scale factors in TMEM beside one accumulator; the others double-buffer.
     constexpr int kNumAcc = (KIND == KIND_MXF8) ? 1 : 2;
@@ -526,21 +526,42 @@ __global__ void __launch_bounds__(kNumThreads, 1)
             }
             const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * kAccCols) +
                                    (static_cast<uint32_t>(quarter * 32) << 16);
-#pragma unroll 1
-            for (int chunk = 0; chunk < BLOCK_N / 32; ++chunk) {
-                const int col0 = ni * BLOCK_N + chunk * 32;
-                if (col0 >= p.n) {
-                    break;
+            // Read-back software-pipelined over 32-column chunks: the TMEM load of the next chunk is in flight while
+            // the current one is converted and stored (columns past N are loaded but never stored), and the
+            // accumulator goes back to the MMA role as soon as its last chunk is in registers.
+            const int col_tile = ni * BLOCK_N;
+            auto release_accumulator = [&]() {
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(&acc_empty_bar[acc]);
                 }
-                uint32_t v[32];
-                ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(chunk * 32), v);
+            };
+            uint32_t va[32];
+            ptx::tmem_ld_32x32b_x32(t_row, va);
+            if constexpr (BLOCK_N == 32) {
                 ptx::tmem_ld_wait();
-                store_chunk<EPI>(v, p, row, col0, vec_ok, s_row);
-            }
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-                ptx::mbar_arrive(&acc_empty_bar[acc]);
+                release_accumulator();
+                store_chunk<EPI>(va, p, row, col_tile, vec_ok, s_row);
+            } else {
+                uint32_t vb[32];
+#pragma unroll
+                for (int g = 0; g < BLOCK_N / 64; ++g) {
+                    ptx::tmem_ld_wait();
+                    ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(g * 64 + 32), vb);
+                    if (col_tile + g * 64 < p.n) {
+                        store_chunk<EPI>(va, p, row, col_tile + g * 64, vec_ok, s_row);
+                    }
+                    ptx::tmem_ld_wait();
+                    if (g + 1 < BLOCK_N / 64) {
+                        ptx::tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(g * 64 + 64), va);
+                    } else {
+                        release_accumulator();
+                    }
+                    if (col_tile + g * 64 + 32 < p.n) {
+                        store_chunk<EPI>(vb, p, row, col_tile + g * 64 + 32, vec_ok, s_row);
+                    }
+                }
             }
             if (++acc == kNumAcc) {
                 acc = 0;

@@ -985,17 +985,40 @@ extern "C" int pto_b200_gemv(void* stream, uint8_t* out, const uint8_t* src0, co
     return launch_gemv<GEMV_F16>(s, grid, out_dtype, src0, src1, bias, out, n, k, ldb);
 }
 
+template <bool A52, bool B52, int OUT>
+static int launch_gemv_mx_out(cudaStream_t s, int grid, const uint8_t* a, const uint8_t* sa, const uint8_t* b,
+                              const uint8_t* sb, const float* bias, void* out, int n, int k, long long ldb,
+                              long long ld_sfb)
+{
+    if (k <= kGemvMxSmemK) {
+        // the left row as floats in slot order (whole 512-value pieces) + one float per scale block
+        const size_t smem = static_cast<size_t>((k + 511) / 512) * 512 * sizeof(float) + static_cast<size_t>(k / 32) * sizeof(float);
+        auto kernel = gemv_mx_kernel<A52, B52, OUT>;
+        if (smem > 48 * 1024) {
+            if (int rc = note_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)),
+                                   "cudaFuncSetAttribute(gemv_mx)")) {
+                return rc;
+            }
+        }
+        kernel<<<grid, kGemvThreads, smem, s>>>(a, sa, b, sb, bias, out, n, k, ldb, ld_sfb);
+    } else {
+        constexpr int cols_per_block = (kGemvThreads / 32) * kGemvMxColsPerWarp; // a warp owns two columns
+        const long long want = (static_cast<long long>(n) + cols_per_block - 1) / cols_per_block;
+        gemv_mx_mma_kernel<A52, B52, OUT><<<static_cast<int>(want < grid ? want : grid), kGemvThreads, 0, s>>>(
+            a, sa, b, sb, bias, out, n, k, ldb, ld_sfb);
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return note_cuda(cudaGetLastError(), "gemv_mx launch");
+}
+
 template <bool A52, bool B52>
 static int launch_gemv_mx(cudaStream_t s, int grid, int out_dtype, const uint8_t* a, const uint8_t* sa, const uint8_t* b,
                           const uint8_t* sb, const float* bias, void* out, int n, int k, long long ldb, long long ld_sfb)
 {
     if (out_dtype == PTO_B200_F32) {
-        gemv_mx_kernel<A52, B52, GEMV_OUT_F32><<<grid, kGemvThreads, 0, s>>>(a, sa, b, sb, bias, out, n, k, ldb, ld_sfb);
-    } else {
-        gemv_mx_kernel<A52, B52, GEMV_OUT_BF16><<<grid, kGemvThreads, 0, s>>>(a, sa, b, sb, bias, out, n, k, ldb, ld_sfb);
+        return launch_gemv_mx_out<A52, B52, GEMV_OUT_F32>(s, grid, a, sa, b, sb, bias, out, n, k, ldb, ld_sfb);
     }
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-    return note_cuda(cudaGetLastError(), "gemv_mx launch");
+    return launch_gemv_mx_out<A52, B52, GEMV_OUT_BF16>(s, grid, a, sa, b, sb, bias, out, n, k, ldb, ld_sfb);
 }
 
 extern "C" int pto_b200_gemv_mx(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, const uint8_t* src2,
@@ -1021,7 +1044,7 @@ extern "C" int pto_b200_gemv_mx(void* stream, uint8_t* out, const uint8_t* src0,
     if (int rc = device_info(&dev)) {
         return rc;
     }
-    const int warps_per_block = kGemvThreads / 32;
+    const int warps_per_block = kGemvThreads / 32;                           // one column per warp and pass
     const long long want = (static_cast<long long>(n) + warps_per_block - 1) / warps_per_block;
     const long long cap = static_cast<long long>(dev->sm_count) * 8;
     const int grid = static_cast<int>(want < cap ? want : cap);

@@ -304,7 +304,8 @@ def test_mx_quantiser_nv_rule_bit_exact():
 
 # ------------------------------------------------------------------ TGEMV_MX (one left row, block-scaled)
 
-@pytest.mark.parametrize("fa,fb", [(pto.E4M3, pto.E4M3), (pto.E4M3, pto.E5M2), (pto.E5M2, pto.E5M2)])
+@pytest.mark.parametrize("fa,fb", [(pto.E4M3, pto.E4M3), (pto.E4M3, pto.E5M2), (pto.E5M2, pto.E4M3),
+                                   (pto.E5M2, pto.E5M2)])
 def test_gemv_mx_integer_cases_exact(fa, fb):
     """Integers in [-10, 10] with scales 2^0..2^2 (tests/cpu/st/testcase/tmatmul_mx/gen_data.py:113-138): exact."""
     import ml_dtypes
@@ -339,3 +340,22 @@ def test_gemv_mx_against_the_oracle_and_the_tile_kernel():
     assert np.array_equal(host(out16), gd.f32_to_bf16_bits(host(out)))
     with pytest.raises(pto.PtoB200Error):
         pto.gemv_mx(dev(a[0]), dev(b), dev(sfa[0]), dev(sfb), torch.float16)
+
+
+@pytest.mark.parametrize("n,k", [(9, 8192), (4, 10240), (7, 12320), (3, 16384), (5, 16416), (5, 40960), (33, 41984),
+                                 (37, 65536)])
+def test_gemv_mx_long_rows_exact(n, k):
+    """Left rows up to 40960 values are kept in shared memory as floats; longer ones take the kernel that multiplies
+    whole scale blocks with the warp-level fp8 MMA. Integers with power-of-two scales: both are exact, odd column
+    counts and K that is not a multiple of 512 included."""
+    import ml_dtypes
+
+    xi = gd.randint((1, k), -6, 6, 27, 0).astype(np.float32)
+    bi = gd.randint((n, k), -6, 6, 27, 1).astype(np.float32)
+    x8 = xi.astype(ml_dtypes.float8_e4m3fn).view(np.uint8)
+    b8 = bi.astype(ml_dtypes.float8_e5m2).view(np.uint8)
+    sfx = gd.randint((1, k // 32), 126, 128, 27, 2).astype(np.uint8)
+    sfb = gd.randint((n, k // 32), 126, 128, 27, 3).astype(np.uint8)
+    exact = oracle.gemm_mx(x8, b8, sfx, sfb, pto.E4M3, pto.E5M2)[0]
+    out = pto.gemv_mx(dev(x8[0]), dev(b8), dev(sfx[0]), dev(sfb), torch.float32, pto.E4M3, pto.E5M2)
+    assert np.array_equal(host(out), exact)

@@ -553,7 +553,7 @@ def test_output_beyond_two_to_the_31_elements(kind):
     else:
         a, b, _, _ = gd.s8_inputs(m, n, k, 82)
         ta, tb = dev8(a), dev8(b)
-        out = pto.gemm(ta, tb)                                   # int32 accumulators
+        out = pto.gemm(ta, tb, torch.int32)                      # int32 accumulators
         ref_tile = lambda r0, c0: oracle.gemm_s8(a[r0:r0 + 128], b[c0:c0 + 256])  # noqa: E731
         got_tile = lambda r0, c0: host(out[r0:r0 + 128, c0:c0 + 256].contiguous())  # noqa: E731
     assert out.numel() > 2 ** 31
