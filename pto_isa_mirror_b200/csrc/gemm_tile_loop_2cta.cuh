@@ -819,7 +819,7 @@ __global__ void __cluster_dims__(2, 1, 1)
         }
     }
     // Both CTAs are past every access to the other's shared memory, barriers and tensor memory.
-    ptx::cluster_arrive();
+    ptx::cluster_arrive_relaxed();
     ptx::cluster_wait();
     if (warp == 1) {
         ptx::tc_fence_after_sync();

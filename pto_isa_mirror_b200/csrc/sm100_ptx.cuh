@@ -262,6 +262,10 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 }
 
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+// Arrival that orders no memory: for a rendezvous that only says "I no longer touch your shared memory, barriers or
+// tensor memory". (The releasing form also waits for this CTA's outstanding stores, the TMA stores of the last tile
+// among them: measured 1.0 us against 0.43 us at the end of the pair kernel.)
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
 // Arrive on an mbarrier that lives in another CTA of the cluster (address from map_to_cta).
