@@ -280,6 +280,21 @@ int pto_b200_mx_quantize_e4m3_ex(void* stream, uint8_t* data, uint8_t* scales, c
                                  long long ld_src, long long ld_data, long long ld_scales, int scale_alg);
 
 /*
+ * TQUANT to MXFP4: fp32 rows into packed float4_e2m1x2_t bytes and e8m0 block scales (one per 32 elements along k),
+ * the producer of the PTO_B200_E2M1 operands of pto_b200_gemm_mx. Replaces TQUANT<QuantType::MXFP4_E2M1> with a float
+ * source under either scale rule, include/pto/cpu/TQuant.hpp:280-372 (group maximum :280-305 - the OCP rule takes it
+ * over the values truncated to bf16 -, shared exponent :210-221 (OCP: biased exponent - 2) / :194-208 with the e2m1 spec
+ * :39-45 (NV: absmax / 6 rounded up to a power of two), scaling :226-248, element code EncodeE2M1Magic :155-176: round
+ * to nearest even on the e2m1 grid, saturating at 6, sign kept on zeros).
+ *   src    : rows x k floats, leading dimension ld_src elements (multiple of 4), 16-byte aligned, finite values
+ *   data   : rows x k/2 bytes (element 2i in the low nibble of byte i), leading dimension ld_data bytes (even), 2-byte aligned
+ *   scales : rows x k/32 bytes, leading dimension ld_scales bytes
+ *   k % 32 == 0; scale_alg PTO_B200_SCALE_OCP or PTO_B200_SCALE_NV. Bit-identical to the reference for finite input.
+ */
+int pto_b200_mx_quantize_e2m1(void* stream, uint8_t* data, uint8_t* scales, const uint8_t* src, int rows, int k,
+                              long long ld_src, long long ld_data, long long ld_scales, int scale_alg);
+
+/*
  * K-split reduction over peer memory: the reduce-scatter / all-gather half of the reference's GEMM + AllReduce
  * (kernels/manual/a2a3/gemm_ar/comm_kernel.cpp:165-210 reduce-scatter into the owner's window, :377-400 all-gather,
  * :111-123 and :528-590 the TNOTIFY / TWAIT counters), one process per GPU, buffers mapped into every rank

@@ -63,6 +63,7 @@ def _lib() -> ctypes.CDLL:
         lib.pto_oracle_dequant_bf16.argtypes = [_p, _p, _p, _p, _i, _i, _ll, _ll, _i]
         lib.pto_oracle_mx_quantize_e4m3.argtypes = [_p, _p, _p, _i, _i, _ll]
         lib.pto_oracle_mx_quantize_e4m3_alg.argtypes = [_p, _p, _p, _i, _i, _ll, _i]
+        lib.pto_oracle_mx_quantize_e2m1.argtypes = [_p, _p, _p, _i, _i, _ll, _i]
         lib.pto_oracle_quant_store.argtypes = [_p, _i, _p, _i, _i, _i, _p, _i, _i, _ll, _ll]
         lib.pto_oracle_float_to_bf16.argtypes = [ctypes.c_float]
         lib.pto_oracle_float_to_bf16.restype = ctypes.c_uint16
@@ -188,6 +189,18 @@ def quant_store(acc: np.ndarray, words, vector: bool, relu: bool = False, out_f1
 OCP, NV = 0, 1
 
 
+def mx_quantize_e2m1(src: np.ndarray, scale_alg: int = OCP):
+    """MX quantisation of fp32 [rows, k] to MXFP4 -> (packed e2m1 bytes [rows, k/2], element 2i in the low nibble;
+    e8m0 bytes [rows, k/32]), with the OCP or the NV scale rule."""
+    src = _c(src, np.float32)
+    rows, k = src.shape
+    assert k % 32 == 0
+    data = np.empty((rows, k // 2), dtype=np.uint8)
+    scales = np.empty((rows, k // 32), dtype=np.uint8)
+    _lib().pto_oracle_mx_quantize_e2m1(_ptr(src), _ptr(data), _ptr(scales), rows, k, k, scale_alg)
+    return data, scales
+
+
 def mx_quantize_e4m3(src: np.ndarray, scale_alg: int = OCP):
     """MX quantisation of fp32 [rows, k] along k in blocks of 32 -> (e4m3 bytes [rows, k], e8m0 bytes [rows, k/32]),
     with the OCP or the NV scale rule."""
@@ -238,6 +251,8 @@ class Ref:
             lib.ref_quant_store.argtypes = [_i, _i, _i, _i, ctypes.c_int32, ctypes.c_float, ctypes.c_uint64]
             lib.ref_quant_store.restype = ctypes.c_uint16
         lib.ref_mx_quantize_e4m3.argtypes = [_p, _p, _p, _i, _i]
+        if hasattr(lib, "ref_mx_quantize_e2m1"):
+            lib.ref_mx_quantize_e2m1.argtypes = [_p, _p, _p, _i, _i, _i]
         if hasattr(lib, "ref_mx_quantize_e4m3_nv"):
             lib.ref_mx_quantize_e4m3_nv.argtypes = [_p, _p, _p, _i, _i]
         lib.ref_fp8_to_double.argtypes = [ctypes.c_uint8, _i]
@@ -330,6 +345,14 @@ class Ref:
                 out[i, j] = fn(int(is_int), int(out_f16), int(vector), int(relu), int(v) if is_int else 0,
                                0.0 if is_int else float(v), w)
         return out
+
+    def mx_quantize_e2m1(self, src, scale_alg=0):
+        src = _c(src, np.float32)
+        rows, k = src.shape
+        data = np.empty((rows, k // 2), dtype=np.uint8)
+        scales = np.empty((rows, k // 32), dtype=np.uint8)
+        self.lib.ref_mx_quantize_e2m1(_ptr(src), _ptr(data), _ptr(scales), rows, k, int(scale_alg))
+        return data, scales
 
     def mx_quantize_e4m3(self, src, scale_alg=0):
         src = _c(src, np.float32)

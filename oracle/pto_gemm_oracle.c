@@ -683,6 +683,72 @@ void pto_oracle_mx_quantize_e4m3_alg(const float* src, uint8_t* data, uint8_t* s
     }
 }
 
+/* TQUANT to MXFP4 (float4_e2m1x2_t, two codes per byte, element 2i in the low nibble) with e8m0 block scales.
+   OCP rule (cpu/TQuant.hpp:280-305,210-221): the block maximum is taken over the values TRUNCATED to bf16, e8m0 =
+   max(biased exponent - 2, 0). NV rule (:194-208 with the e2m1 spec :39-45): e8m0 = biased exponent of amax / 6,
+   rounded up. Scaling 2^(127 - e8m0) (:226-248). Element code (EncodeE2M1Magic, :155-176): the magnitude is rounded to
+   nearest even on the grid of its binade - steps of 0.5 below 2, 1 below 4, 2 above - by adding a power of two, and
+   saturates at 6; the sign bit is kept, also on a zero. Inputs finite. */
+static uint8_t encode_e2m1_magic(float value)
+{
+    const uint32_t value_bits = float_to_bits(value);
+    const uint8_t sign = (uint8_t)((value_bits >> 28) & 0x8u);
+    const float abs_value = fabsf(value);
+    const uint32_t abs_bits = float_to_bits(abs_value);
+    uint32_t biased = (abs_bits & 0x7F800000u) >> 23;
+    biased = biased < 127u ? 127u : (biased > 129u ? 129u : biased);
+    const uint32_t magic_bits = (biased + 22u) << 23;
+    volatile float sum = abs_value + bits_to_float(magic_bits);
+    const uint32_t q = float_to_bits(sum) - magic_bits;
+    const uint32_t base = (biased - 127u) << 1;
+    const uint32_t mag = (q + base) > 7u ? 7u : (q + base);
+    return (uint8_t)(sign | mag);
+}
+
+void pto_oracle_mx_quantize_e2m1(const float* src, uint8_t* data, uint8_t* scales, int rows, int k, long long ld,
+                                 int scale_alg)
+{
+    const int groups = k / 32;
+    for (int r = 0; r < rows; ++r) {
+        for (int g = 0; g < groups; ++g) {
+            const float* x = src + (size_t)r * ld + (size_t)g * 32;
+            float amax = 0.0f;
+            uint32_t amax_bf16 = 0;
+            for (int i = 0; i < 32; ++i) {
+                const float ax = fabsf(x[i]);
+                const uint32_t top = (float_to_bits(x[i]) >> 16) & 0x7FFFu;
+                if (ax > amax) {
+                    amax = ax;
+                }
+                if (top > amax_bf16) {
+                    amax_bf16 = top;
+                }
+            }
+            uint8_t e8m0 = 0;
+            float scaling;
+            if (scale_alg == 0) {
+                const uint32_t exponent = (amax_bf16 >> 7) & 0xFFu; /* of the truncated maximum */
+                e8m0 = (exponent <= 2u) ? 0u : (uint8_t)(exponent - 2u);
+            } else if (amax != 0.0f) {
+                volatile float descale = amax * (1.0f / 6.0f);
+                const uint32_t bits = float_to_bits(descale);
+                const uint32_t exponent = (bits & 0x7F800000u) >> 23;
+                const uint32_t mantissa = bits & 0x007FFFFFu;
+                const int round_up = mantissa > 0u && exponent != 0xFEu && !(exponent == 0u && mantissa <= 0x00400000u);
+                e8m0 = (uint8_t)(exponent + (round_up ? 1u : 0u));
+            }
+            scaling = (e8m0 >= 0xFEu) ? ldexpf(1.0f, -127) : bits_to_float((254u - (uint32_t)e8m0) << 23);
+            scales[(size_t)r * groups + g] = e8m0;
+            for (int i = 0; i < 32; i += 2) {
+                volatile float y0 = x[i] * scaling;
+                volatile float y1 = x[i + 1] * scaling;
+                data[(size_t)r * (k / 2) + (size_t)g * 16 + i / 2] =
+                    (uint8_t)(encode_e2m1_magic(y0) | (encode_e2m1_magic(y1) << 4));
+            }
+        }
+    }
+}
+
 void pto_oracle_mx_quantize_e4m3(const float* src, uint8_t* data, uint8_t* scales, int rows, int k, long long ld)
 {
     pto_oracle_mx_quantize_e4m3_alg(src, data, scales, rows, k, ld, 0);

@@ -394,6 +394,54 @@ void ref_mx_quantize_e4m3_nv(const float* src, uint8_t* data, uint8_t* scales, i
     }
 }
 
+// TQUANT<QuantType::MXFP4_E2M1> per row and 32-wide block with either scale rule (include/pto/cpu/TQuant.hpp:
+// ComputeMxGroupMax :280-305, ComputeMxSharedExponent :316-334, ComputeMxGroupScaling :336-347, StoreMxEncodedValue
+// :349-372 with EncodeE2M1Magic :155-176), float source; data: rows x k/2 bytes, element 2i in the low nibble.
+void ref_mx_quantize_e2m1(const float* src, uint8_t* data, uint8_t* scales, int rows, int k, int nv)
+{
+    using namespace pto::cpu_quant;
+    const int groups = k / 32;
+    std::memset(data, 0, static_cast<size_t>(rows) * (k / 2));
+    for (int r = 0; r < rows; ++r) {
+        for (int g = 0; g < groups; ++g) {
+            const float* x = src + static_cast<size_t>(r) * k + g * 32;
+            float amax = 0.0f;
+            uint16_t amax_bits = 0;
+            for (int i = 0; i < 32; ++i) {
+                if (nv) {
+                    amax = std::max(amax, std::fabs(x[i]));
+                } else {
+                    amax_bits = std::max(amax_bits, AbsBf16BitsFromFloat(x[i]));
+                }
+            }
+            if (!nv) {
+                amax = Bf16BitsToFloat(amax_bits);
+            }
+            uint8_t e;
+            float scaling;
+            if (nv) {
+                e = ComputeMxSharedExponent<QuantType::MXFP4_E2M1, QuantScaleAlg::NV>(amax);
+                scaling = ComputeMxGroupScaling<QuantType::MXFP4_E2M1, QuantScaleAlg::NV>(amax, e);
+            } else {
+                e = ComputeMxSharedExponent<QuantType::MXFP4_E2M1, QuantScaleAlg::OCP>(amax);
+                scaling = ComputeMxGroupScaling<QuantType::MXFP4_E2M1, QuantScaleAlg::OCP>(amax, e);
+            }
+            scales[static_cast<size_t>(r) * groups + g] = e;
+            for (int i = 0; i < 32; ++i) {
+                uint8_t code = NvMxFp4E2M1Spec::PS_MAX;
+                if (std::isinf(scaling)) {
+                    code = (scaling > 0) ? NvMxFp4E2M1Spec::PS_MAX : NvMxFp4E2M1Spec::NG_MIN;
+                } else if (!std::isnan(scaling)) {
+                    code = EncodeE2M1Magic(ApplyE2M1ScaleForSource<float>(x[i], scaling));
+                }
+                const int col = g * 32 + i;
+                uint8_t& byte = data[static_cast<size_t>(r) * (k / 2) + col / 2];
+                byte = (col & 1) ? static_cast<uint8_t>((byte & 0x0F) | (code << 4)) : static_cast<uint8_t>((byte & 0xF0) | (code & 0x0F));
+            }
+        }
+    }
+}
+
 double ref_fp8_to_double(uint8_t raw, int fmt)
 {
     return fmt == 6 ? static_cast<double>(float8_e5m2_t::FromRaw(raw)) : static_cast<double>(float8_e4m3_t::FromRaw(raw));

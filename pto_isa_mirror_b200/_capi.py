@@ -65,6 +65,7 @@ SYMBOLS = {
     "pto_b200_gemv_mx": (_i, [ctypes.c_void_p, _u8p, _u8p, _u8p, _u8p, _u8p, _u8p, _i, _i, _ll, _ll, _i, _i, _i]),
     "pto_b200_mx_quantize_e4m3": (_i, [ctypes.c_void_p, _u8p, _u8p, _u8p, _i, _i, _ll, _ll, _ll]),
     "pto_b200_mx_quantize_e4m3_ex": (_i, [ctypes.c_void_p, _u8p, _u8p, _u8p, _i, _i, _ll, _ll, _ll, _i]),
+    "pto_b200_mx_quantize_e2m1": (_i, [ctypes.c_void_p, _u8p, _u8p, _u8p, _i, _i, _ll, _ll, _ll, _i]),
     "pto_b200_gemm_mx_static": (
         _i,
         [ctypes.c_void_p, _u8p, _u8p, _u8p, _u8p, _u8p, _i, _i, _i, _ll, _ll, _ll, _ll, _ll, _i, _i, _i],

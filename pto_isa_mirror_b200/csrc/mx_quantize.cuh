@@ -130,4 +130,101 @@ __global__ void __launch_bounds__(kQuantThreads) mx_quantize_e4m3_kernel(const f
     }
 }
 
+// TQUANT to MXFP4: fp32 [rows][k] -> float4_e2m1x2_t bytes [rows][k / 2] (element 2i in the low nibble) + one e8m0
+// scale per 32 elements of K (include/pto/cpu/TQuant.hpp: group maximum ComputeMxGroupMax :280-305, shared exponent
+// ComputeE2M1SharedExponent :210-221 / ComputeNvSharedExponent with the e2m1 spec :39-45,:194-208, scaling :226-248,
+// element code EncodeE2M1Magic :155-176):
+//   OCP: amax = the largest |x| of the block TRUNCATED to bf16; e8m0 = max(biased_exponent(amax) - 2, 0)
+//   NV:  e8m0 = biased exponent of amax / 6, plus one unless amax / 6 is a power of two (0 for an all-zero block)
+//   scaling = 2^(127 - e8m0); code = sign | magnitude code of |x * scaling| rounded to nearest even on the e2m1 grid
+//   (steps of 0.5 below 2, 1 below 4, 2 above; 6 is the largest), the sign kept on a zero as well.
+// Inputs must be finite. Same thread layout as the e4m3 kernel: eight lanes own a block, a lane stores two bytes.
+__device__ __forceinline__ uint32_t encode_e2m1(float value)
+{
+    const uint32_t bits = __float_as_uint(value);
+    const uint32_t sign = (bits >> 28) & 0x8u;
+    const uint32_t abs_bits = bits & 0x7FFFFFFFu;
+    uint32_t biased = abs_bits >> 23;
+    biased = biased < 127u ? 127u : (biased > 129u ? 129u : biased);
+    const uint32_t magic_bits = (biased + 22u) << 23;
+    // adding 2^(biased - 105) leaves the magnitude, rounded to nearest even in units of 2^(biased - 128), in the low bits
+    const uint32_t q = __float_as_uint(__fadd_rn(__uint_as_float(abs_bits), __uint_as_float(magic_bits))) - magic_bits;
+    const uint32_t mag = q + ((biased - 127u) << 1);
+    return sign | (mag > 7u ? 7u : mag);
+}
+
+// src: [rows][ld_src] floats (16-byte aligned rows); data: [rows][ld_data] bytes (2-byte aligned rows, k / 2 used);
+// scales: [rows][ld_scales] bytes. k % 32 == 0.
+template <int ALG>
+__global__ void __launch_bounds__(kQuantThreads) mx_quantize_e2m1_kernel(const float* __restrict__ src,
+                                                                          uint8_t* __restrict__ data,
+                                                                          uint8_t* __restrict__ scales, int rows, int k,
+                                                                          long long ld_src, long long ld_data,
+                                                                          long long ld_scales)
+{
+    const int k4 = k / 4;
+    const long long total = static_cast<long long>(rows) * k4; // 16-byte items; a multiple of 8 per row
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    const unsigned group_mask = 0xFFu << (threadIdx.x & 24u);
+    const long long row_step = stride / k4;
+    const int col_step = static_cast<int>(stride - row_step * k4);
+    long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    long long cur_row = i / k4;
+    int cur_c4 = static_cast<int>(i - cur_row * k4);
+    // total and stride are multiples of 8: the eight lanes of a group are all in range or all out of range
+    while (i < total) {
+        float4 v[kQuantItems];
+        long long row[kQuantItems];
+        int c4[kQuantItems];
+#pragma unroll
+        for (int u = 0; u < kQuantItems; ++u) {
+            row[u] = -1;
+            if (i < total) {
+                row[u] = cur_row;
+                c4[u] = cur_c4;
+                v[u] = __ldcs(reinterpret_cast<const float4*>(src + cur_row * ld_src) + cur_c4);
+            }
+            i += stride;
+            cur_row += row_step;
+            cur_c4 += col_step;
+            if (cur_c4 >= k4) {
+                cur_c4 -= k4;
+                cur_row += 1;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kQuantItems; ++u) {
+            if (row[u] < 0) {
+                continue;
+            }
+            // the maximum as a bit pattern without the sign: for finite floats the integer order is the value order
+            uint32_t amax_bits = max(max(__float_as_uint(v[u].x) & 0x7FFFFFFFu, __float_as_uint(v[u].y) & 0x7FFFFFFFu),
+                                     max(__float_as_uint(v[u].z) & 0x7FFFFFFFu, __float_as_uint(v[u].w) & 0x7FFFFFFFu));
+            amax_bits = max(amax_bits, __shfl_xor_sync(group_mask, amax_bits, 1));
+            amax_bits = max(amax_bits, __shfl_xor_sync(group_mask, amax_bits, 2));
+            amax_bits = max(amax_bits, __shfl_xor_sync(group_mask, amax_bits, 4));
+            uint32_t e8m0;
+            if constexpr (ALG == MX_SCALE_OCP) {
+                const uint32_t exponent = amax_bits >> 23; // truncation to bf16 keeps the exponent field
+                e8m0 = exponent <= 2u ? 0u : exponent - 2u;
+            } else {
+                const uint32_t bits = __float_as_uint(__fmul_rn(__uint_as_float(amax_bits), 1.0f / 6.0f));
+                const uint32_t exponent = (bits & 0x7F800000u) >> 23;
+                const uint32_t mantissa = bits & 0x007FFFFFu;
+                const bool round_up = mantissa > 0u && !(exponent == 0u && mantissa <= 0x00400000u);
+                e8m0 = (amax_bits == 0u) ? 0u : exponent + (round_up ? 1u : 0u);
+            }
+            const float scaling = __uint_as_float((254u - e8m0) << 23); // e8m0 <= 252 for finite input: never zero
+            const uint32_t codes = encode_e2m1(__fmul_rn(v[u].x, scaling)) | (encode_e2m1(__fmul_rn(v[u].y, scaling)) << 4) |
+                                   (encode_e2m1(__fmul_rn(v[u].z, scaling)) << 8) |
+                                   (encode_e2m1(__fmul_rn(v[u].w, scaling)) << 12);
+            *reinterpret_cast<uint16_t*>(data + row[u] * ld_data + static_cast<long long>(c4[u]) * 2) =
+                static_cast<uint16_t>(codes);
+            if ((c4[u] & 7) == 0) {
+                scales[row[u] * ld_scales + (c4[u] >> 3)] = static_cast<uint8_t>(e8m0);
+            }
+        }
+    }
+}
+
 } // namespace pto_b200

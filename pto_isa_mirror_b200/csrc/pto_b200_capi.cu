@@ -1105,6 +1105,40 @@ extern "C" int pto_b200_mx_quantize_e4m3(void* stream, uint8_t* data, uint8_t* s
                                         PTO_B200_SCALE_OCP);
 }
 
+extern "C" int pto_b200_mx_quantize_e2m1(void* stream, uint8_t* data, uint8_t* scales, const uint8_t* src, int rows,
+                                         int k, long long ld_src, long long ld_data, long long ld_scales, int scale_alg)
+{
+    if (data == nullptr || scales == nullptr || src == nullptr || rows <= 0 || k <= 0 || k % 32 != 0 || ld_src < k ||
+        ld_data < k / 2 || ld_scales < k / 32) {
+        return PTO_B200_EINVAL;
+    }
+    if (scale_alg != PTO_B200_SCALE_OCP && scale_alg != PTO_B200_SCALE_NV) {
+        return PTO_B200_EDTYPE;
+    }
+    if ((reinterpret_cast<uintptr_t>(src) & 15u) || (ld_src & 3) != 0 || (reinterpret_cast<uintptr_t>(data) & 1u) ||
+        (ld_data & 1) != 0) {
+        return PTO_B200_EALIGN;
+    }
+    DeviceInfo* dev = nullptr;
+    if (int rc = device_info(&dev)) {
+        return rc;
+    }
+    auto kernel = scale_alg == PTO_B200_SCALE_NV ? mx_quantize_e2m1_kernel<MX_SCALE_NV> : mx_quantize_e2m1_kernel<MX_SCALE_OCP>;
+    int blocks_per_sm = 0;
+    if (int rc = note_cuda(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, kernel, kQuantThreads, 0),
+                           "mx_quantize occupancy")) {
+        return rc;
+    }
+    const long long items = static_cast<long long>(rows) * (k / 4);
+    const long long want = (items + kQuantThreads - 1) / kQuantThreads;
+    const long long cap = static_cast<long long>(dev->sm_count) * (blocks_per_sm > 0 ? blocks_per_sm : 1);
+    const int grid = static_cast<int>(want < cap ? want : cap);
+    kernel<<<grid, kQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const float*>(src), data, scales,
+                                                                          rows, k, ld_src, ld_data, ld_scales);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return note_cuda(cudaGetLastError(), "mx_quantize_e2m1 launch");
+}
+
 // ---------------------------------------------------------------- K-split reduction over peer memory
 
 static int fill_peers(PeerPointers& pp, void* const* ptrs, int world)

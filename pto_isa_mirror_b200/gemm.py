@@ -345,6 +345,33 @@ def mx_quantize_e4m3(src: torch.Tensor, stream: Optional[torch.cuda.Stream] = No
     return data, scales
 
 
+def mx_quantize_e2m1(src: torch.Tensor, stream: Optional[torch.cuda.Stream] = None,
+                     data: Optional[torch.Tensor] = None, scales: Optional[torch.Tensor] = None,
+                     scale_alg: int = _capi.SCALE_OCP):
+    """MX quantisation to MXFP4 (TQUANT, MXFP4_E2M1): float32 src [rows, K] -> (packed e2m1 bytes [rows, K/2] uint8 with
+    element 2i in the low nibble of byte i, e8m0 scales [rows, K/32] uint8): the operands ``gemm_mx`` takes with
+    ``a_fmt = b_fmt = E2M1``. Finite input only; ``scale_alg`` as for :func:`mx_quantize_e4m3`."""
+    lib = _capi.load()
+    _require_cuda_2d(src, "src")
+    if src.dtype != torch.float32:
+        raise ValueError("src must be float32")
+    rows, k = src.shape
+    if k % 32 != 0:
+        raise ValueError("K must be a multiple of 32")
+    if data is None:
+        data = torch.empty((rows, k // 2), dtype=torch.uint8, device=src.device)
+    if scales is None:
+        scales = torch.empty((rows, k // 32), dtype=torch.uint8, device=src.device)
+    for t, shape, name in ((data, (rows, k // 2), "data"), (scales, (rows, k // 32), "scales")):
+        _require_cuda_2d(t, name)
+        if t.dtype != torch.uint8 or tuple(t.shape) != shape:
+            raise ValueError(f"{name} must be a uint8 CUDA tensor of shape {shape}")
+    rc = lib.pto_b200_mx_quantize_e2m1(_stream_ptr(stream), data.data_ptr(), scales.data_ptr(), src.data_ptr(), rows, k,
+                                       src.stride(0), data.stride(0), scales.stride(0), scale_alg)
+    _capi.check(rc, "pto_b200_mx_quantize_e2m1")
+    return data, scales
+
+
 def cast_f32_to_bf16(src: torch.Tensor, out: Optional[torch.Tensor] = None,
                      stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
     lib = _capi.load()

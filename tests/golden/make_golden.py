@@ -167,6 +167,27 @@ def main():
             src[i, :32] *= np.float32(2.0) ** (i - 24)
         d, s = ref.mx_quantize_e4m3(src, 1)
         save("mx_quantize_nv", src=src, data=d, scales=s)
+    # TQUANT to MXFP4 (float4_e2m1x2_t) under both scale rules: zero and tiny blocks, huge values, every rounding tie
+    # of the e2m1 grid in both signs, maxima just below and on a power of two (the OCP rule truncates them to bf16), a
+    # range of block magnitudes
+    if wanted("mxfp4_quantize"):
+        src = gd.normal((64, 256), 17)
+        src[0, :32] = 0
+        src[1, :32] *= 1e-30
+        src[2, :32] *= 1e30
+        src[3, 5] = -1e-9
+        ties = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 7.0], dtype=np.float32)
+        src[4, :32] = np.concatenate([ties, -ties, ties * np.float32(0.999), -ties * np.float32(1.001)])
+        src[5, :32] = np.float32(6.0) * np.float32(2.0) ** np.arange(-16, 16)
+        src[6, :32] = np.linspace(-1, 1, 32).astype(np.float32)
+        src[6, 31] = np.float32(1.9999999)          # truncates to 1.9921875 in bf16: the OCP exponent stays 127
+        src[7, :32] = np.linspace(-1, 1, 32).astype(np.float32)
+        src[7, 0] = np.float32(-4.0)
+        for i in range(8, 40):
+            src[i, :32] *= np.float32(2.0) ** (i - 24)
+        d0, s0 = ref.mx_quantize_e2m1(src, 0)
+        d1, s1 = ref.mx_quantize_e2m1(src, 1)
+        save("mxfp4_quantize", src=src, data_ocp=d0, scales_ocp=s0, data_nv=d1, scales_nv=s1)
 
 
 if __name__ == "__main__":

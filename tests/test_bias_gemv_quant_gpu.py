@@ -359,3 +359,48 @@ def test_gemv_mx_long_rows_exact(n, k):
     exact = oracle.gemm_mx(x8, b8, sfx, sfb, pto.E4M3, pto.E5M2)[0]
     out = pto.gemv_mx(dev(x8[0]), dev(b8), dev(sfx[0]), dev(sfb), torch.float32, pto.E4M3, pto.E5M2)
     assert np.array_equal(host(out), exact)
+
+
+# ------------------------------------------------------------------ TQUANT to MXFP4 (float4_e2m1x2_t)
+
+@pytest.mark.parametrize("alg", ["ocp", "nv"])
+def test_mxfp4_quantiser_bit_exact(alg):
+    """pto_b200_mx_quantize_e2m1 against the simulator's fixture (every rounding tie, zero / tiny / huge blocks, maxima
+    that the OCP rule truncates to bf16) and, on a larger matrix with a strided view, against the oracle."""
+    from pto_isa_mirror_b200 import _capi
+
+    code = _capi.SCALE_OCP if alg == "ocp" else _capi.SCALE_NV
+    ocode = oracle.OCP if alg == "ocp" else oracle.NV
+    g = golden("mxfp4_quantize")
+    d, s = pto.mx_quantize_e2m1(dev(g["src"]), scale_alg=code)
+    assert np.array_equal(host(s), g["scales_" + alg])
+    assert np.array_equal(host(d), g["data_" + alg])
+    x = gd.normal((777, 1056), 19) * np.float32(3.0)
+    x[::7] *= np.float32(1e-6)
+    x[5] *= np.float32(1e20)
+    x[6, ::3] = 0
+    x[9, :64] = np.float32(2.0) ** np.arange(-32, 32, dtype=np.float32)
+    rd, rs = oracle.mx_quantize_e2m1(x, ocode)
+    d, s = pto.mx_quantize_e2m1(dev(x), scale_alg=code)
+    assert np.array_equal(host(s), rs) and np.array_equal(host(d), rd)
+    wide = torch.zeros((64, 512 + 64), dtype=torch.float32, device=DEV)
+    wide[:, :512] = dev(x[:64, :512])
+    d2, s2 = pto.mx_quantize_e2m1(wide[:, :512], scale_alg=code)
+    assert np.array_equal(host(d2), rd[:64, :256]) and np.array_equal(host(s2), rs[:64, :16])
+    with pytest.raises(pto.PtoB200Error):
+        pto.mx_quantize_e2m1(dev(x), scale_alg=5)
+
+
+def test_mxfp4_quantise_then_multiply():
+    """Both MXFP4 operands produced on the device by the quantiser and multiplied by the block-scaled kernel: equal to
+    the oracle's product of the same quantised bytes, and close to the fp32 product of the unquantised matrices."""
+    m, n, k = 256, 512, 1024
+    a32 = gd.normal((m, k), 51)
+    b32 = gd.normal((n, k), 52)
+    a4, sa = pto.mx_quantize_e2m1(dev(a32))
+    b4, sb = pto.mx_quantize_e2m1(dev(b32))
+    out = host(pto.gemm_mx(a4, b4, sa, sb, torch.float32, pto.E2M1, pto.E2M1))
+    ref = oracle.gemm_mx(host(a4)[:128], host(b4), host(sa)[:128], host(sb), oracle.E2M1, oracle.E2M1)
+    assert max_rel_err(out[:128], ref) <= MX_TOL
+    exact = a32.astype(np.float64) @ b32.astype(np.float64).T
+    assert np.abs(out - exact).max() / np.abs(exact).max() < 0.25      # 4-bit operands: a coarse product

@@ -96,6 +96,13 @@ def test_argument_errors_come_before_any_launch(lib):
     assert q(None, p, p, p, 4, 64, 64, 64, 1) == _capi.EINVAL                                   # ld_scales < k / 32
     assert q(None, p, p, p + 4, 4, 64, 64, 64, 2) == _capi.EALIGN                               # src not 16-byte aligned
     assert q(None, p, p, p, 4, 64, 66, 64, 2) == _capi.EALIGN                                   # ld_src % 4
+    q4 = lib.pto_b200_mx_quantize_e2m1
+    assert q4(None, p, p, None, 4, 64, 64, 32, 2, 0) == _capi.EINVAL
+    assert q4(None, p, p, p, 4, 64, 64, 16, 2, 0) == _capi.EINVAL                                 # ld_data < k / 2
+    assert q4(None, p, p, p, 4, 48, 48, 24, 2, 0) == _capi.EINVAL                                 # k % 32
+    assert q4(None, p, p, p, 4, 64, 64, 32, 2, 9) == _capi.EDTYPE                                 # unknown scale rule
+    assert q4(None, p + 1, p, p, 4, 64, 64, 32, 2, 1) == _capi.EALIGN                             # data not 2-byte aligned
+    assert q4(None, p, p, p, 4, 64, 64, 33, 2, 1) == _capi.EALIGN                                 # odd ld_data
     # the workspace-free MX entry reports argument errors like pto_b200_gemm_mx, before it needs a device
     mxs = lib.pto_b200_gemm_mx_static
     assert mxs(None, p, p, p, p, p, 16, 16, 48, 48, 48, 16, 2, 2, E4M3, E4M3, BF16) == _capi.EINVAL           # k % 32
