@@ -755,6 +755,17 @@ def aux_configs(dev, peaks):
                                            "frac_of_hbm_peak": gbytes / (ms * 1e-3) / peak_gbs, "peak_gbs": peak_gbs}
         del srcs, q_data, q_scales
         torch.cuda.empty_cache()
+    # the same source quantised to MXFP4: 4 bytes read + 1/2 + 1/32 written per element
+    rows = 32768
+    srcs = [torch.randn((rows, kq), generator=gen, device=dev) for _ in range(2)]
+    q_data = torch.empty((rows, kq // 2), dtype=torch.uint8, device=dev)
+    q_scales = torch.empty((rows, kq // 32), dtype=torch.uint8, device=dev)
+    ms = time_steps(lambda i: pto.mx_quantize_e2m1(srcs[i % 2], data=q_data, scales=q_scales), 20, 3, dev, 1) / 20
+    gbytes = rows * kq * (4 + 0.5 + 1 / 32) / 1e9
+    out[f"mxfp4_quantize_{rows}x8192"] = {"gbs": gbytes / (ms * 1e-3), "ms": ms, "bytes": int(gbytes * 1e9),
+                                          "frac_of_hbm_peak": gbytes / (ms * 1e-3) / peak_gbs, "peak_gbs": peak_gbs}
+    del srcs, q_data, q_scales
+    torch.cuda.empty_cache()
     return out
 
 
