@@ -139,18 +139,13 @@ __global__ void __launch_bounds__(kQuantThreads) mx_quantize_e4m3_kernel(const f
 //   scaling = 2^(127 - e8m0); code = sign | magnitude code of |x * scaling| rounded to nearest even on the e2m1 grid
 //   (steps of 0.5 below 2, 1 below 4, 2 above; 6 is the largest), the sign kept on a zero as well.
 // Inputs must be finite. Same thread layout as the e4m3 kernel: eight lanes own a block, a lane stores two bytes.
-__device__ __forceinline__ uint32_t encode_e2m1(float value)
+// Two floats -> two e2m1 codes in one byte (low nibble = first value): round to nearest even on the e2m1 grid,
+// saturating at +-6, the sign kept on zeros - what EncodeE2M1Magic computes with its power-of-two addition.
+__device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi)
 {
-    const uint32_t bits = __float_as_uint(value);
-    const uint32_t sign = (bits >> 28) & 0x8u;
-    const uint32_t abs_bits = bits & 0x7FFFFFFFu;
-    uint32_t biased = abs_bits >> 23;
-    biased = biased < 127u ? 127u : (biased > 129u ? 129u : biased);
-    const uint32_t magic_bits = (biased + 22u) << 23;
-    // adding 2^(biased - 105) leaves the magnitude, rounded to nearest even in units of 2^(biased - 128), in the low bits
-    const uint32_t q = __float_as_uint(__fadd_rn(__uint_as_float(abs_bits), __uint_as_float(magic_bits))) - magic_bits;
-    const uint32_t mag = q + ((biased - 127u) << 1);
-    return sign | (mag > 7u ? 7u : mag);
+    uint16_t r;
+    asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; mov.b16 %0, {t, 0}; }" : "=h"(r) : "f"(hi), "f"(lo));
+    return r;
 }
 
 // src: [rows][ld_src] floats (16-byte aligned rows); data: [rows][ld_data] bytes (2-byte aligned rows, k / 2 used);
@@ -215,9 +210,8 @@ __global__ void __launch_bounds__(kQuantThreads) mx_quantize_e2m1_kernel(const f
                 e8m0 = (amax_bits == 0u) ? 0u : exponent + (round_up ? 1u : 0u);
             }
             const float scaling = __uint_as_float((254u - e8m0) << 23); // e8m0 <= 252 for finite input: never zero
-            const uint32_t codes = encode_e2m1(__fmul_rn(v[u].x, scaling)) | (encode_e2m1(__fmul_rn(v[u].y, scaling)) << 4) |
-                                   (encode_e2m1(__fmul_rn(v[u].z, scaling)) << 8) |
-                                   (encode_e2m1(__fmul_rn(v[u].w, scaling)) << 12);
+            const uint32_t codes = cvt_e2m1x2(__fmul_rn(v[u].x, scaling), __fmul_rn(v[u].y, scaling)) |
+                                   (cvt_e2m1x2(__fmul_rn(v[u].z, scaling), __fmul_rn(v[u].w, scaling)) << 8);
             *reinterpret_cast<uint16_t*>(data + row[u] * ld_data + static_cast<long long>(c4[u]) * 2) =
                 static_cast<uint16_t>(codes);
             if ((c4[u] & 7) == 0) {
