@@ -327,7 +327,7 @@ def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=8, 
                          torch.randint(127, 130, (m, k // 32), generator=gen, device=dev, dtype=torch.uint8),
                          torch.randint(127, 130, (n, k // 32), generator=gen, device=dev, dtype=torch.uint8),
                          torch.empty((m, n), dtype=torch.bfloat16, device=dev)))
-        ws = torch.empty(pto.gemm_mx_workspace_bytes(m, n, k), dtype=torch.uint8, device=dev)
+        ws = torch.zeros(pto.gemm_mx_workspace_bytes(m, n, k, split_last_wave=True), dtype=torch.uint8, device=dev)
 
         def step(i):
             a, b, sfa, sfb, c = bufs[i % sets]
@@ -360,7 +360,7 @@ def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=8, 
         a, sfa = mx_quantize_torch(torch.randn((m, k), generator=gen, device=dev), fp8)
         b, sfb = mx_quantize_torch(torch.randn((n, k), generator=gen, device=dev), fp8)
         c = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
-        ws = torch.empty(pto.gemm_mx_workspace_bytes(m, n, k), dtype=torch.uint8, device=dev)
+        ws = torch.zeros(pto.gemm_mx_workspace_bytes(m, n, k, split_last_wave=True), dtype=torch.uint8, device=dev)
 
         def step(i):
             pto.gemm_mx(a, b, sfa, sfb, torch.bfloat16, fmt, fmt, workspace=ws, out=c)

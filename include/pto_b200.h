@@ -157,7 +157,11 @@ int pto_b200_gemm_quant(void* stream, uint8_t* out, const uint8_t* src0, const u
  *                       holds k / 2 bytes; bases 32-byte aligned, lda and ldb multiples of 64, k a multiple of 128);
  *                       out_dtype BF16 or F32; B is PTO_B200_B_DN; k % 32 == 0.
  *   workspace : device scratch of at least pto_b200_gemm_mx_workspace_bytes(m, n, k) bytes, 16-byte aligned;
- *               the scales are re-tiled into it by a small kernel on the same stream before the GEMM.
+ *               the scales are re-tiled into it by a small kernel on the same stream before the GEMM. With
+ *               pto_b200_gemm_workspace_bytes() MORE bytes (zero before their first use) the CTA-pair kernel also cuts a
+ *               partly filled last wave of tiles into K halves, as pto_b200_gemm_ws does, under the same rule: such a
+ *               workspace must not be used by two launches that can overlap. The same holds for the tiled_scales
+ *               buffer of pto_b200_mx_retile_scales / pto_b200_gemm_mx_pretiled.
  * Scale byte 0xFF (NaN in the e8m0 encoding) is outside the supported input domain.
  */
 int pto_b200_gemm_mx(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, const uint8_t* src2,

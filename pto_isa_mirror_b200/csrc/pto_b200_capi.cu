@@ -831,6 +831,13 @@ static int gemm_mx_impl(void* stream, uint8_t* out, const uint8_t* src0, const u
             o.sfb_map = &tsb;
             o.out_dtype = out_dtype;
             o.no_tma_store = dev->no_tma_store;
+            // a workspace with room beyond the re-tiled scales (pto_b200_gemm_workspace_bytes() more) also lets the
+            // last, partly filled wave of tiles be cut into K halves, as for the dense kernels
+            const size_t scale_bytes = pto_b200_gemm_mx_workspace_bytes(m, n, k);
+            if (workspace_bytes >= scale_bytes + kGemmWorkspaceBytes) {
+                o.workspace = workspace + scale_bytes;
+                o.workspace_bytes = workspace_bytes - scale_bytes;
+            }
             if (out_dtype == PTO_B200_F32) {
                 return launch_pair<KIND_MXF8, EPI_F32>(s, ta, tb, p, q, o);
             }

@@ -172,8 +172,13 @@ def gemm_quant(a: torch.Tensor, b_dn: torch.Tensor, out_dtype: torch.dtype = tor
     return out
 
 
-def gemm_mx_workspace_bytes(m: int, n: int, k: int) -> int:
-    return int(_capi.load().pto_b200_gemm_mx_workspace_bytes(m, n, k))
+def gemm_mx_workspace_bytes(m: int, n: int, k: int, split_last_wave: bool = False) -> int:
+    """Bytes of the re-tiled scales; with ``split_last_wave`` also the room (``pto_b200_gemm_workspace_bytes``) that
+    lets the CTA-pair kernel cut a partly filled last wave of tiles into K halves. A workspace of the larger size must
+    not be shared by calls that can overlap."""
+    lib = _capi.load()
+    extra = int(lib.pto_b200_gemm_workspace_bytes()) if split_last_wave else 0
+    return int(lib.pto_b200_gemm_mx_workspace_bytes(m, n, k)) + extra
 
 
 def gemm_mx(a: torch.Tensor, b_dn: torch.Tensor, sfa: torch.Tensor, sfb: torch.Tensor,
@@ -198,9 +203,8 @@ def gemm_mx(a: torch.Tensor, b_dn: torch.Tensor, sfa: torch.Tensor, sfb: torch.T
         raise ValueError("inner dimensions differ")
     if k % 32 != 0 or tuple(sfa.shape) != (m, k // 32) or tuple(sfb.shape) != (n, k // 32):
         raise ValueError("scales must be [M, K/32] and [N, K/32] with K a multiple of 32")
-    need = gemm_mx_workspace_bytes(m, n, k)
     if workspace is None:
-        workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
+        workspace = torch.zeros(gemm_mx_workspace_bytes(m, n, k, split_last_wave=True), dtype=torch.uint8, device=a.device)
     if out is None:
         out = torch.empty((m, n), dtype=out_dtype, device=a.device)
     if bias is not None:
@@ -231,7 +235,8 @@ def mx_retile_scales(sfa: torch.Tensor, sfb: torch.Tensor, k: int, workspace: Op
             raise ValueError(f"{name} must be [rows, K/32] bytes")
     m, n = sfa.shape[0], sfb.shape[0]
     if workspace is None:
-        workspace = torch.empty(gemm_mx_workspace_bytes(m, n, k), dtype=torch.uint8, device=sfa.device)
+        workspace = torch.zeros(gemm_mx_workspace_bytes(m, n, k, split_last_wave=True), dtype=torch.uint8,
+                                device=sfa.device)
     rc = lib.pto_b200_mx_retile_scales(_stream_ptr(stream), workspace.data_ptr(), workspace.numel(), sfa.data_ptr(),
                                        sfb.data_ptr(), m, n, k, sfa.stride(0), sfb.stride(0))
     _capi.check(rc, "pto_b200_mx_retile_scales")
