@@ -35,7 +35,8 @@ typedef enum {
     PTO_B200_S32 = 4,  /* int32_t                                            */
     PTO_B200_E4M3 = 5, /* float8_e4m3_t (fn variant: no inf, 0x7f NaN)      */
     PTO_B200_E5M2 = 6, /* float8_e5m2_t                                      */
-    PTO_B200_E2M1 = 7  /* float4_e2m1x2_t: two 4-bit values per byte, the even element in the low nibble */
+    PTO_B200_E2M1 = 7, /* float4_e2m1x2_t: two 4-bit values per byte, the even element in the low nibble */
+    PTO_B200_U8 = 8    /* uint8_t (destination of the 8-bit pre-quant stores)     */
 } pto_b200_dtype;
 
 typedef enum {
@@ -132,14 +133,16 @@ int pto_b200_gemm_s8_dequant(void* stream, uint8_t* out, const uint8_t* src0, co
  * quantize_element (:139-185); kernel usage kernels/manual/a2a3/dispatch_mega_combine/op_kernel/utils/
  * pto_gmm_preload_async_fixpipe_quant.hpp:75-124.
  *   in_dtype S8 (int32 accumulators: QS322BF16_PRE / VQS322BF16_PRE, DEQF16 / VDEQF16) or F16 / BF16 (fp32
- *   accumulators: QF322BF16_PRE / VQF322BF16_PRE, QF322F16_PRE / VQF322F16_PRE); out_dtype BF16 or F16; B is PTO_B200_B_DN.
+ *   accumulators: QF322BF16_PRE / VQF322BF16_PRE, QF322F16_PRE / VQF322F16_PRE); out_dtype BF16 or F16, or S8 / U8
+ *   (REQ8 / VREQ8 for int32 accumulators, QF322B8_PRE / VQF322B8_PRE for fp32 ones: out = relu?( clamp( rint(
+ *   float(acc) * scale_j + offset ) ) ) as one byte, offset = the 9-bit field in bits [45:37] of the word, clamp range
+ *   -128..127 when bit 46 of the word is set, else 0..255; S8 and U8 store the same byte); B is PTO_B200_B_DN.
  *   fp_words == NULL : scalar form, scale = the fp32 value in bits [31:0] of pre_quant_scalar for every column
  *   fp_words != NULL : vector form, n 64-bit words in device memory (8-byte aligned), one per column; the scale is the
  *                      19-bit float (sign, 8 exponent, 10 mantissa bits) in bits [31:13] of the word, i.e. fp32 with
  *                      the low 13 mantissa bits ignored (extract_m1_from_quant, common.hpp:116-137)
  *   relu != 0        : ReluPreMode::NormalRelu, applied after the scaling
- * Half outputs are clamped to +-65504 as the reference does. The integer destinations (REQ8 / VREQ8, SHIFTS322S16) and
- * the offset / sign fields of the word (bits 37-46) belong to them and are not implemented.
+ * Half outputs are clamped to +-65504 as the reference does. The int16 destination (SHIFTS322S16) is not implemented.
  */
 int pto_b200_gemm_quant(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, int m, int n, int k,
                         long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype,

@@ -546,7 +546,8 @@ void pto_oracle_dequant_bf16(const int32_t* acc, const float* s_row, const float
 /* TSTORE with a pre-quant scale word (cpu/TStore.hpp:154-181 -> quantize_element, cpu/common.hpp:139-185), modes as
    the overloads select them (common.hpp:58-108): int32 / float accumulators to bf16 / half, scalar form (fp32 scale in
    bits [31:0] of the word, one word for the whole tile) or vector form (one word per column, scale = the 19-bit float
-   in bits [31:13]), optional ReLU after the scaling. Saturation control of the task cookie is off (its default). */
+   in bits [31:13]), optional ReLU after the scaling. Saturation control of the task cookie is off (its default).
+   out_f16: 0 bfloat16, 1 half, 2 int8, 3 uint8 destinations. */
 void pto_oracle_quant_store(const void* acc, int acc_is_int, const uint64_t* words, int vector, int relu, int out_f16,
                             uint16_t* out, int m, int n, long long ld_acc, long long ld_out)
 {
@@ -559,6 +560,21 @@ void pto_oracle_quant_store(const void* acc, int acc_is_int, const uint64_t* wor
                                          : ((const float*)acc)[(size_t)i * ld_acc + j];
             volatile float t = src * scale;
             float r = t;
+            if (out_f16 >= 2) {
+                /* REQ8 / VREQ8 / QF322B8_PRE / VQF322B8_PRE (common.hpp:151-156): add the 9-bit offset of bits [45:37],
+                   round to nearest even, clamp to the signed range when bit 46 is set, else to 0..255; ReLU; the
+                   destination's integer cast. The result sits in the low byte of the 16-bit slot. */
+                const float offset = (float)((w >> 37) & 0x1FFu);
+                const int is_signed = (int)((w >> 46) & 1u);
+                volatile float shifted = r + offset;
+                float q = rintf(shifted);
+                q = fminf(fmaxf(q, is_signed ? -128.0f : 0.0f), is_signed ? 127.0f : 255.0f);
+                if (relu) {
+                    q = (q > 0.0f) ? q : 0.0f;
+                }
+                out[(size_t)i * ld_out + j] = (uint16_t)((uint32_t)(int32_t)q & 0xFFu);
+                continue;
+            }
             if (out_f16) {
                 /* DEQF16 / VDEQF16 clamp always; QF322F16_PRE / VQF322F16_PRE clamp finite values (common.hpp:157-164) */
                 if (acc_is_int || isfinite(r)) {

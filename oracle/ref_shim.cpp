@@ -301,7 +301,7 @@ uint16_t ref_quant_store(int acc_is_int, int out_f16, int vector, int relu, int3
         constexpr QuantMode_t mode = kVec ? GetVectorPreQuantMode<S, D>() : GetScalarPreQuantMode<S, D>();
         const S v = std::is_same_v<S, int32_t> ? static_cast<S>(acc_i) : static_cast<S>(acc_f);
         const D d = ConvertStoreValue<D, S, mode, kRelu>(v, word);
-        std::memcpy(&bits, &d, 2);
+        std::memcpy(&bits, &d, sizeof(D));
     };
     auto with_relu = [&](auto d, auto s, auto v) {
         if (relu) {
@@ -324,10 +324,19 @@ uint16_t ref_quant_store(int acc_is_int, int out_f16, int vector, int relu, int3
             with_vec(d, float{});
         }
     };
-    if (out_f16) {
-        with_src(half{});
-    } else {
-        with_src(bfloat16_t{});
+    switch (out_f16) { // destination: 0 bfloat16, 1 half, 2 int8, 3 uint8 (the 8-bit results come back in the low byte)
+        case 1:
+            with_src(half{});
+            break;
+        case 2:
+            with_src(int8_t{});
+            break;
+        case 3:
+            with_src(uint8_t{});
+            break;
+        default:
+            with_src(bfloat16_t{});
+            break;
     }
     return bits;
 }

@@ -33,12 +33,16 @@ enum EpilogueMode : int {
     EPI_F16 = 2,     // static_cast<half>(fp32), round to nearest even
     EPI_S32 = 3,     // store the int32 accumulator
     EPI_DEQ_BF16 = 4, // bf16((float(acc) * s_col[j]) * s_row[i])
-    EPI_QUANT16 = 5   // TSTORE with a pre-quant scale word: cast16(relu?(clamp(float(acc) * scale_j))), see QuantFlags
+    EPI_QUANT16 = 5,  // TSTORE with a pre-quant scale word: cast16(relu?(clamp(float(acc) * scale_j))), see QuantFlags
+    EPI_QUANT8 = 6    // the same to int8 / uint8: relu?(clamp(rint(float(acc) * scale_j + offset)))
 };
 
 // EPI_QUANT16 variants (GemmParams::quant_flags): the accumulator type, the 16-bit destination, ReLU, and whether the
 // scale is one word for the tile (TSTORE(dst, acc, preQuantScalar): fp32 in bits [31:0]) or one word per column
 // (TSTORE(dst, acc, fpTile) / TSTORE_FP: the 19-bit (1,8,10) float in bits [31:13]); include/pto/cpu/common.hpp:116-185.
+// EPI_QUANT8 (REQ8 / VREQ8 for int32 accumulators, QF322B8_PRE / VQF322B8_PRE for float ones, :151-156): the word also
+// carries a 9-bit offset in bits [45:37], added before rounding to nearest even, and the sign flag in bit 46 (clamp to
+// -128..127 when set, else to 0..255); the 8-bit result is stored as is.
 enum QuantFlags : int { QUANT_ACC_S32 = 1, QUANT_OUT_F16 = 2, QUANT_RELU = 4, QUANT_VECTOR = 8 };
 
 struct GemmParams {
@@ -143,11 +147,29 @@ __device__ __forceinline__ void tile_coords(int t, const GemmParams& p, int& mi,
 }
 
 // Words one 32-column chunk of an accumulator row becomes on its way out: 32 for 32-bit outputs, 16 (two values each)
-// for 16-bit outputs.
+// for 16-bit outputs, 8 (four values each) for 8-bit outputs.
 template <int EPI>
 struct OutWords {
-    static constexpr int kCount = (EPI == EPI_F32 || EPI == EPI_S32) ? 32 : 16;
+    static constexpr int kCount = (EPI == EPI_F32 || EPI == EPI_S32) ? 32 : (EPI == EPI_QUANT8 ? 8 : 16);
 };
+
+// The scale of a pre-quant word: fp32 in bits [31:0] (scalar form) or the 19-bit (1, 8, 10) float in bits [31:13]
+// (vector form), extract_m1_from_quant, include/pto/cpu/common.hpp:116-137.
+__device__ __forceinline__ float quant_word_scale(uint32_t lo, bool vector)
+{
+    if (!vector) {
+        return __uint_as_float(lo);
+    }
+    // sign, 8 exponent and 10 mantissa bits from [31:13]: fp32 with the low 13 mantissa bits dropped; a zero exponent
+    // field with a non-zero mantissa reads as (1 + m / 1024) * 2^-127 in the reference
+    const uint32_t e = (lo >> 23) & 0xFFu;
+    const uint32_t mnt = (lo >> 13) & 0x3FFu;
+    if (e != 0u || mnt == 0u) {
+        return __uint_as_float(e != 0u ? (lo & 0xFFFFE000u) : 0u);
+    }
+    const float mag = __fmul_rn(1.0f + static_cast<float>(mnt) * (1.0f / 1024.0f), __uint_as_float(0x00400000u)); // 2^-127
+    return (lo >> 31) ? -mag : mag;
+}
 
 // One 32-column chunk of one accumulator row -> output words: optional bias, then cast / dequantise. The bias is
 // added to the finished accumulator in the accumulator's own type, once per output element (TMATMUL_BIAS adds it
@@ -181,6 +203,28 @@ __device__ __forceinline__ void convert_chunk(const uint32_t (&v)[32], const Gem
         for (int i = 0; i < 32; ++i) {
             o[i] = w[i];
         }
+    } else if constexpr (EPI == EPI_QUANT8) {
+        const bool acc_int = (p.quant_flags & QUANT_ACC_S32) != 0;
+        const bool relu = (p.quant_flags & QUANT_RELU) != 0;
+        const bool vector = (p.quant_flags & QUANT_VECTOR) != 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            o[i] = 0u;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const unsigned long long word = vector ? ((i < n_left) ? __ldg(p.quant_words + col0 + i) : 0ull) : p.quant_word;
+            const float scale = quant_word_scale(static_cast<uint32_t>(word), vector);
+            const float offset = static_cast<float>(static_cast<uint32_t>(word >> 37) & 0x1FFu);
+            const bool is_signed = ((word >> 46) & 1ull) != 0;
+            const float src = acc_int ? __int2float_rn(static_cast<int>(w[i])) : __uint_as_float(w[i]);
+            float q = rintf(__fadd_rn(__fmul_rn(src, scale), offset));
+            q = fminf(fmaxf(q, is_signed ? -128.0f : 0.0f), is_signed ? 127.0f : 255.0f);
+            if (relu) {
+                q = (q > 0.0f) ? q : 0.0f;
+            }
+            o[i >> 2] |= (static_cast<uint32_t>(__float2int_rn(q)) & 0xFFu) << ((i & 3) * 8);
+        }
     } else {
         float f[32];
         if constexpr (EPI == EPI_QUANT16) {
@@ -192,23 +236,9 @@ __device__ __forceinline__ void convert_chunk(const uint32_t (&v)[32], const Gem
             const bool vector = (p.quant_flags & QUANT_VECTOR) != 0;
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-                float scale;
-                if (vector) {
-                    const uint32_t lo = (i < n_left) ? static_cast<uint32_t>(__ldg(p.quant_words + col0 + i)) : 0u;
-                    // sign, 8 exponent and 10 mantissa bits from [31:13]: fp32 with the low 13 mantissa bits dropped;
-                    // a zero exponent field with a non-zero mantissa reads as (1 + m / 1024) * 2^-127 in the reference
-                    const uint32_t e = (lo >> 23) & 0xFFu;
-                    const uint32_t mnt = (lo >> 13) & 0x3FFu;
-                    if (e != 0u || mnt == 0u) {
-                        scale = __uint_as_float(e != 0u ? (lo & 0xFFFFE000u) : 0u);
-                    } else {
-                        const float mag = __fmul_rn(1.0f + static_cast<float>(mnt) * (1.0f / 1024.0f),
-                                                    __uint_as_float(0x00400000u)); // 2^-127
-                        scale = (lo >> 31) ? -mag : mag;
-                    }
-                } else {
-                    scale = __uint_as_float(static_cast<uint32_t>(p.quant_word));
-                }
+                const uint32_t lo = vector ? ((i < n_left) ? static_cast<uint32_t>(__ldg(p.quant_words + col0 + i)) : 0u)
+                                           : static_cast<uint32_t>(p.quant_word);
+                const float scale = quant_word_scale(lo, vector);
                 const float src = acc_int ? __int2float_rn(static_cast<int>(w[i])) : __uint_as_float(w[i]);
                 float r = __fmul_rn(src, scale);
                 if (out_f16 && (acc_int || isfinite(r))) {
@@ -275,6 +305,19 @@ __device__ __forceinline__ void store_words(const uint32_t (&o)[OutWords<EPI>::k
             for (int i = 0; i < 32; ++i) {
                 if (i < n_left) {
                     dst[i] = o[i];
+                }
+            }
+        }
+    } else if constexpr (EPI == EPI_QUANT8) {
+        uint8_t* dst = reinterpret_cast<uint8_t*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
+        if ((reinterpret_cast<uintptr_t>(dst) & 15u) == 0 && n_left >= 32) {
+            reinterpret_cast<uint4*>(dst)[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            reinterpret_cast<uint4*>(dst)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                if (i < n_left) {
+                    dst[i] = static_cast<uint8_t>((o[i >> 2] >> ((i & 3) * 8)) & 0xFFu);
                 }
             }
         }
@@ -505,7 +548,7 @@ __global__ void __launch_bounds__(kNumThreads, 1)
     } else {
         // ---------------------------------------------------------------- TSTORE role
         const int quarter = warp & 3; // TMEM lanes this warp may read
-        const int esize = (EPI == EPI_F32 || EPI == EPI_S32) ? 4 : 2;
+        const int esize = (EPI == EPI_F32 || EPI == EPI_S32) ? 4 : (EPI == EPI_QUANT8 ? 1 : 2);
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0) && (((p.ldc * esize) & 15) == 0);
         int acc = 0;
         uint32_t acc_phase = 0;

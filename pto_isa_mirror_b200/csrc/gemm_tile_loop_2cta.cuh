@@ -426,7 +426,7 @@ __global__ void __cluster_dims__(2, 1, 1)
     } else if (warp < 6) {
         // ---------------------------------------------------------------- TSTORE role (both CTAs)
         const int quarter = warp & 3;
-        const int esize = kOut32 ? 4 : 2;
+        const int esize = kOut32 ? 4 : (EPI == EPI_QUANT8 ? 1 : 2);
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15u) == 0) && (((p.ldc * esize) & 15) == 0);
         uint8_t* epi_buf = smem + L::kEpiOff + quarter * kEpiBufs * L::kEpiBufBytes;
         uint8_t* my_line = epi_buf + lane * 128; // this thread's row inside a store box
@@ -586,8 +586,8 @@ __global__ void __cluster_dims__(2, 1, 1)
                         const uint32_t qv[4] = {q[i].x, q[i].y, q[i].z, q[i].w};
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            if constexpr (EPI == EPI_S32 || EPI == EPI_DEQ_BF16 || EPI == EPI_QUANT16) {
-                                if (EPI != EPI_QUANT16 || (p.quant_flags & QUANT_ACC_S32) != 0) {
+                            if constexpr (EPI == EPI_S32 || EPI == EPI_DEQ_BF16 || EPI == EPI_QUANT16 || EPI == EPI_QUANT8) {
+                                if ((EPI != EPI_QUANT16 && EPI != EPI_QUANT8) || (p.quant_flags & QUANT_ACC_S32) != 0) {
                                     v[4 * i + j] += qv[j]; // int32 accumulators: exact
                                 } else {
                                     v[4 * i + j] = __float_as_uint(__uint_as_float(qv[j]) + __uint_as_float(v[4 * i + j]));

@@ -117,6 +117,7 @@ int elem_size(int dtype)
         case PTO_B200_S32:
             return 4;
         case PTO_B200_S8:
+        case PTO_B200_U8:
         case PTO_B200_E4M3:
         case PTO_B200_E5M2:
             return 1;
@@ -344,7 +345,7 @@ int launch_pair(cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& t
         p.tail_token = static_cast<int>((t % 0x7FFFFFFEu) + 1);
     }
     // C leaves through TMA stores when it is 16-byte aligned with a 16-byte row pitch (the rule for any TMA copy)
-    constexpr int esize = (EPI == EPI_F32 || EPI == EPI_S32) ? 4 : 2;
+    constexpr int esize = (EPI == EPI_F32 || EPI == EPI_S32) ? 4 : (EPI == EPI_QUANT8 ? 1 : 2);
     CUtensorMap tc = ta;
     p.tma_store = 0;
     // ... and its rows end on a 16-byte boundary: at a ragged end the store unit is a whole 16-byte piece, which
@@ -575,7 +576,8 @@ extern "C" int pto_b200_gemm_quant(void* stream, uint8_t* out, const uint8_t* sr
 {
     const bool is16 = (in_dtype == PTO_B200_F16 || in_dtype == PTO_B200_BF16);
     const bool is8 = (in_dtype == PTO_B200_S8);
-    if ((!is16 && !is8) || !(out_dtype == PTO_B200_BF16 || out_dtype == PTO_B200_F16)) {
+    const bool out8 = (out_dtype == PTO_B200_S8 || out_dtype == PTO_B200_U8);
+    if ((!is16 && !is8) || !(out_dtype == PTO_B200_BF16 || out_dtype == PTO_B200_F16 || out8)) {
         return PTO_B200_EDTYPE;
     }
     if (fp_words != nullptr && (reinterpret_cast<uintptr_t>(fp_words) & 7u)) {
@@ -615,14 +617,16 @@ extern "C" int pto_b200_gemm_quant(void* stream, uint8_t* out, const uint8_t* sr
         GemmParams pp = p;
         PairLaunch o;
         o.out_dtype = out_dtype;
-        o.no_tma_store = dev->no_tma_store;
+        o.no_tma_store = dev->no_tma_store || out8; // 8-bit results leave from registers
         int rc;
         if (is8) {
             pp.idesc = make_idesc(2, 1, 1, false, kPairBlockN, false, kPairBlockM);
-            rc = launch_pair<KIND_I8, EPI_QUANT16>(s, ta, tb_half, pp, q, o);
+            rc = out8 ? launch_pair<KIND_I8, EPI_QUANT8>(s, ta, tb_half, pp, q, o)
+                      : launch_pair<KIND_I8, EPI_QUANT16>(s, ta, tb_half, pp, q, o);
         } else {
             pp.idesc = make_idesc(1, fmt, fmt, false, kPairBlockN, false, kPairBlockM);
-            rc = launch_pair<KIND_F16, EPI_QUANT16>(s, ta, tb_half, pp, q, o);
+            rc = out8 ? launch_pair<KIND_F16, EPI_QUANT8>(s, ta, tb_half, pp, q, o)
+                      : launch_pair<KIND_F16, EPI_QUANT16>(s, ta, tb_half, pp, q, o);
         }
         if (rc != -1) {
             return rc;
@@ -630,10 +634,12 @@ extern "C" int pto_b200_gemm_quant(void* stream, uint8_t* out, const uint8_t* sr
     }
     if (is8) {
         p.idesc = make_idesc(2, 1, 1, false, block_n, false);
-        return launch_block_n<KIND_I8, EPI_QUANT16, false>(block_n, s, ta, tb, p, dev->sm_count);
+        return out8 ? launch_block_n<KIND_I8, EPI_QUANT8, false>(block_n, s, ta, tb, p, dev->sm_count)
+                    : launch_block_n<KIND_I8, EPI_QUANT16, false>(block_n, s, ta, tb, p, dev->sm_count);
     }
     p.idesc = make_idesc(1, fmt, fmt, false, block_n, false);
-    return launch_block_n<KIND_F16, EPI_QUANT16, false>(block_n, s, ta, tb, p, dev->sm_count);
+    return out8 ? launch_block_n<KIND_F16, EPI_QUANT8, false>(block_n, s, ta, tb, p, dev->sm_count)
+                : launch_block_n<KIND_F16, EPI_QUANT16, false>(block_n, s, ta, tb, p, dev->sm_count);
 }
 
 extern "C" int pto_b200_gemm_s8_dequant(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1,

@@ -20,6 +20,7 @@ _TORCH_TO_PTO = {
     torch.float32: F32,
     torch.int8: S8,
     torch.int32: S32,
+    torch.uint8: _capi.U8,
 }
 _PTO_TO_TORCH = {v: k for k, v in _TORCH_TO_PTO.items()}
 if hasattr(torch, "float8_e4m3fn"):
@@ -145,7 +146,9 @@ def gemm_quant(a: torch.Tensor, b_dn: torch.Tensor, out_dtype: torch.dtype = tor
     """GEMM with the pre-quant store: TSTORE(dst, acc, preQuantScalar) when ``fp_words`` is None (the scale is the
     float32 value in the low 32 bits of ``pre_quant_scalar``), TSTORE(dst, acc, fpTile) / TSTORE_FP when ``fp_words`` is a
     CUDA tensor of n 64-bit words (int64 / uint64), one per column, whose bits [31:13] hold the scale. a, b_dn: int8
-    (int32 accumulators) or float16 / bfloat16 (float32 accumulators); the result is bfloat16 or float16."""
+    (int32 accumulators) or float16 / bfloat16 (float32 accumulators); the result is bfloat16 or float16, or - the
+    REQ8 / QF322B8_PRE forms - int8 / uint8: round(acc * scale + offset) with the word's offset (bits [45:37]) and sign
+    flag (bit 46: clamp to -128..127, else to 0..255)."""
     lib = _capi.load()
     _require_cuda_2d(a, "a")
     _require_cuda_2d(b_dn, "b_dn")
@@ -157,8 +160,8 @@ def gemm_quant(a: torch.Tensor, b_dn: torch.Tensor, out_dtype: torch.dtype = tor
         raise ValueError("inner dimensions differ")
     if out is None:
         out = torch.empty((m, n), dtype=out_dtype, device=a.device)
-    elif tuple(out.shape) != (m, n) or out.dtype not in (torch.bfloat16, torch.float16):
-        raise ValueError("out must be [m, n] bfloat16 or float16")
+    elif tuple(out.shape) != (m, n) or out.dtype not in (torch.bfloat16, torch.float16, torch.int8, torch.uint8):
+        raise ValueError("out must be [m, n] bfloat16, float16, int8 or uint8")
     words_ptr = None
     if fp_words is not None:
         if not fp_words.is_cuda or fp_words.element_size() != 8 or fp_words.numel() != n or not fp_words.is_contiguous():

@@ -404,3 +404,50 @@ def test_mxfp4_quantise_then_multiply():
     assert max_rel_err(out[:128], ref) <= MX_TOL
     exact = a32.astype(np.float64) @ b32.astype(np.float64).T
     assert np.abs(out - exact).max() / np.abs(exact).max() < 0.25      # 4-bit operands: a coarse product
+
+
+# ------------------------------------------------------------------ 8-bit destinations of the pre-quant store
+
+@pytest.mark.parametrize("name,words,vector,relu,odt", [
+    ("s32_scalar_s8", "w_si", False, False, torch.int8), ("s32_scalar_u8_relu", "w_ui", False, True, torch.uint8),
+    ("s32_vector_s8", "vec_i", True, False, torch.int8), ("s32_vector_s8_relu", "vec_i", True, True, torch.int8)])
+def test_quant_store_8_bit_golden_bit_exact(name, words, vector, relu, odt):
+    """REQ8 / VREQ8 on the int8 tile of configuration 3 against the simulator's own outputs."""
+    g = golden("quant_store_b8")
+    a, b, _, _ = gd.s8_inputs(128, 256, 1024, 2)
+    out = pto.gemm_quant(dev(a), dev(b), odt, pre_quant_scalar=int(g[words][0]),
+                         fp_words=words_dev(g[words]) if vector else None, relu=relu)
+    assert np.array_equal(host(out).view(np.uint8), g[name].astype(np.uint8))
+
+
+@pytest.mark.parametrize("kind", ["s8", "bf16"])
+def test_quant_store_8_bit_on_the_pair_kernel(kind):
+    """The 8-bit forms on a ragged problem that takes the CTA-pair kernel, rows off every alignment (pitch n + 3), against
+    the oracle's store applied to the GPU's own accumulators: bit-exact, padding untouched."""
+    m, n, k = 2300, 2328, 256
+    if kind == "s8":
+        a, b, _, _ = gd.s8_inputs(m, n, k, 91)
+        ta, tb = dev(a), dev(b)
+        acc = host(pto.gemm(ta, tb, torch.int32))
+        scale = np.float32(100.0 / np.abs(acc).max())
+    else:
+        a, b = gd.dense_inputs(m, n, k, "bf16", 92)
+        ta, tb = dev16(a, torch.bfloat16), dev16(b, torch.bfloat16)
+        acc = host(pto.gemm(ta, tb, torch.float32))
+        scale = np.float32(100.0 / np.abs(acc).max())
+    col = (gd.uniform((n,), 0.5, 1.5, 93, 0) * scale).astype(np.float32)
+    offs = (np.arange(n) % 9).astype(np.uint64)
+    sign = (np.arange(n) % 3 != 0).astype(np.uint64)
+    vec = col.view(np.uint32).astype(np.uint64) | (offs << np.uint64(37)) | (sign << np.uint64(46))
+    scalar = (np.array([scale * np.float32(1.7)]).view(np.uint32).astype(np.uint64) | (np.uint64(5) << np.uint64(37))
+              | (np.uint64(1) << np.uint64(46)))
+    for vector in (False, True):
+        for relu in (False, True):
+            for pitch in (n + 3, n + 24):
+                buf = torch.full((m + 2, pitch), 77, dtype=torch.uint8, device=DEV)
+                pto.gemm_quant(ta, tb, torch.uint8, pre_quant_scalar=int(scalar[0]),
+                               fp_words=words_dev(vec) if vector else None, relu=relu, out=buf[1:m + 1, :n])
+                got = host(buf)
+                want = oracle.quant_store(acc, vec if vector else scalar, vector, relu, oracle.OUT_U8).astype(np.uint8)
+                assert np.array_equal(got[1:m + 1, :n], want), (kind, vector, relu, pitch)
+                assert (got[0] == 77).all() and (got[m + 1] == 77).all() and (got[:, n:] == 77).all()

@@ -112,7 +112,7 @@ def test_argument_errors_come_before_any_launch(lib):
     assert mxs(None, p, p, p, p, p, 32768, 8192, 8192, 8192, 8192, 8192, 256, 256, E4M3, E4M3, BF16) == _capi.ESCRATCH
     # pre-quant store forms
     gq = lib.pto_b200_gemm_quant
-    assert gq(None, p, p, p, 16, 16, 16, 16, 16, 16, S8, F32, 0, None, 0) == _capi.EDTYPE         # 16-bit destinations only
+    assert gq(None, p, p, p, 16, 16, 16, 16, 16, 16, S8, F32, 0, None, 0) == _capi.EDTYPE         # 8- and 16-bit destinations only
     assert gq(None, p, p, p, 16, 16, 16, 16, 16, 16, F32, BF16, 0, None, 0) == _capi.EDTYPE
     assert gq(None, p, p, p, 16, 16, 16, 16, 16, 16, S8, BF16, 0, p + 4, 0) == _capi.EALIGN       # words not 8-byte aligned
     assert gq(None, None, p, p, 16, 16, 16, 16, 16, 16, S8, BF16, 0, None, 0) == _capi.EINVAL
