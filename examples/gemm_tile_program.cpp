@@ -4,7 +4,7 @@
 // (kernels/manual/a2a3/gemm_performance/gemm_performance_kernel.cpp:69-131, B column-major), (3) the fixed-signature
 // launcher, (4) the bias form of the K loop (TMATMUL_BIAS then TMATMUL_ACC, tests/cpu/st/testcase/tmatmul/
 // tmatmul_kernel.cpp:86-96), (5) a one-row TGEMV_BIAS, (6) the int8 K loop stored with a per-column scaling tile
-// (TSTORE_FP) and with one pre-quant scalar plus ReLU (kernels/manual/a2a3/dispatch_mega_combine/op_kernel/utils/
+// (TSTORE_FP), with one pre-quant scalar plus ReLU and requantised to int8 (kernels/manual/a2a3/dispatch_mega_combine/op_kernel/utils/
 // pto_gmm_preload_async_fixpipe_quant.hpp:75-124), (7) the block-scaled K loop with MX_A_ND / MX_B_DN scale tensors
 // (kernels/manual/a5/matmul_mxfp8_performance/mxmatmul_performance_kernel.cpp:153-344), (8) LaunchMxMatmul on e5m2
 // operands and (9) on float4_e2m1x2_t operands, two per byte (kernels/manual/a5/matmul_mxfp4_performance). Inputs are small integers so the fp32 results are exact; the program checks them against host loops and
@@ -302,6 +302,29 @@ int main()
         }
         std::printf("int8 program (TSTORE with a pre-quant scalar and ReLU): %d mismatches\n", n6);
         bad += n6;
+        // the same accumulators requantised to int8 (REQ8): scale 0.25, offset 3 in bits [45:37], signed clamp (bit 46)
+        using GlobalOut8 = GlobalTensor<int8_t, TileShape2D<int8_t, M, N, Layout::ND>, BaseShape2D<int8_t, M, N, Layout::ND>,
+                                        Layout::ND>;
+        int8_t* dOut8 = nullptr;
+        cudaMalloc(&dOut8, M * N);
+        GlobalOut8 out8Global(dOut8);
+        const float quarter = 0.25f;
+        uint32_t quarter_bits;
+        std::memcpy(&quarter_bits, &quarter, 4);
+        const uint64_t word8 = static_cast<uint64_t>(quarter_bits) | (3ull << 37) | (1ull << 46);
+        TSTORE(out8Global, cTile, word8);
+        cudaDeviceSynchronize();
+        std::vector<int8_t> out8(M * N);
+        cudaMemcpy(out8.data(), dOut8, out8.size(), cudaMemcpyDeviceToHost);
+        n6 = 0;
+        for (int i = 0; i < M * N; ++i) {
+            float r = std::nearbyint(static_cast<float>(acc[i]) * quarter + 3.0f);
+            r = r < -128.0f ? -128.0f : (r > 127.0f ? 127.0f : r);
+            n6 += (out8[i] != static_cast<int8_t>(r));
+        }
+        std::printf("int8 program (TSTORE to int8 with a pre-quant scalar, offset and signed clamp): %d mismatches\n", n6);
+        bad += n6;
+        cudaFree(dOut8);
         cudaFree(dA8);
         cudaFree(dB8);
         cudaFree(dWords);

@@ -180,4 +180,4 @@ def test_reference_tile_programs_run_exactly_on_gpu():
     proc = subprocess.run([exe], capture_output=True, text=True, timeout=120)
     assert proc.returncode == 0, proc.stdout + proc.stderr
     assert "tile programs ok" in proc.stdout
-    assert proc.stdout.count(": 0 mismatches") == 10
+    assert proc.stdout.count(": 0 mismatches") == 11
