@@ -951,9 +951,11 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--panels", type=int, default=8)
-    ap.add_argument("--mode", default="fused", choices=["fused", "p2p", "rs_ag", "allreduce"],
+    ap.add_argument("--mode", default="auto", choices=["auto", "fused", "p2p", "rs_ag", "allreduce"],
                     help="K-split step: fused = one kernel per rank (GEMM + exchange over peer memory); p2p = one GEMM "
-                         "per panel + this library's reduction kernels; rs_ag / allreduce = NCCL collectives")
+                         "per panel + this library's reduction kernels; rs_ag / allreduce = NCCL collectives; auto = "
+                         "p2p on two GPUs (a rank multiplies for 3 ms per step there and the per-panel form is the "
+                         "faster one under the power cap, measured 3.4-3.5 against 3.7-3.9 ms), fused on more")
     ap.add_argument("--regions", type=int, default=5, help="timed regions of exactly --steps steps each")
     ap.add_argument("--reduce-blocks", type=int, default=32)
     ap.add_argument("--gemm-streams", type=int, default=2, help="p2p mode: streams the panel GEMMs alternate between")
@@ -996,8 +998,9 @@ def main():
     name = args.workload or ("bf16_4096" if world == 1 else "ksplit_bf16_8192x65536x8192")
     spec = WORKLOADS[name]
     peaks = load_peaks()
+    mode = args.mode if args.mode != "auto" else ("p2p" if world == 2 else "fused")
     step, flops, ws_bytes, sets = make_step(name, spec, dev, seed=1, world=world, rank=rank, panels=args.panels,
-                                            mode=args.mode, gemm_blocks=args.gemm_blocks,
+                                            mode=mode, gemm_blocks=args.gemm_blocks,
                                             reduce_blocks=args.reduce_blocks,
                                             panel_rows=[int(x) for x in args.panel_rows.split(",") if x],
                                             use_multicast=not args.no_multicast, gemm_streams=args.gemm_streams)
@@ -1042,7 +1045,7 @@ def main():
                    "inputs": ("seeded torch.randn on device, N(0,1)/sqrt(K)" if kind in ("dense", "ksplit", "allgather")
                               else "seeded"),
                    **({"parallelism": f"ksplit{world}", "panels": args.panels,
-                       "reduce": getattr(step, "reduce_used", args.mode),
+                       "reduce": getattr(step, "reduce_used", mode),
                        "gemm_blocks": args.gemm_blocks, "reduce_blocks": args.reduce_blocks,
                        "gemm_streams": args.gemm_streams,
                        "panel_rows": getattr(step, "panel_rows", None)}
