@@ -74,6 +74,7 @@ template <> struct dtype_of<bfloat16_t> { static constexpr int value = PTO_B200_
 template <> struct dtype_of<float> { static constexpr int value = PTO_B200_F32; };
 template <> struct dtype_of<int8_t> { static constexpr int value = PTO_B200_S8; };
 template <> struct dtype_of<uint8_t> { static constexpr int value = PTO_B200_U8; };
+template <> struct dtype_of<int16_t> { static constexpr int value = PTO_B200_S16; };
 template <> struct dtype_of<int32_t> { static constexpr int value = PTO_B200_S32; };
 template <> struct dtype_of<float8_e4m3_t> { static constexpr int value = PTO_B200_E4M3; };
 template <> struct dtype_of<float8_e5m2_t> { static constexpr int value = PTO_B200_E5M2; };
@@ -627,8 +628,8 @@ inline void store_chain(GlobalData& dst, TileAcc_& src, const StoreQuant& quant)
 
 // CheckStoreQuantValid: the pre-quant forms implemented here take int32 or float accumulators to half / bfloat16
 // (QS322BF16_PRE, VQS322BF16_PRE, DEQF16, VDEQF16, QF322BF16_PRE, VQF322BF16_PRE, QF322F16_PRE, VQF322F16_PRE of
-// include/pto/cpu/common.hpp:19-37) and to int8_t / uint8_t (REQ8, VREQ8, QF322B8_PRE, VQF322B8_PRE); the int16
-// destination (SHIFTS322S16) is not built.
+// include/pto/cpu/common.hpp:19-37), to int8_t / uint8_t (REQ8, VREQ8, QF322B8_PRE, VQF322B8_PRE) and, from int32
+// accumulators, to int16_t (SHIFTS322S16, VSHIFTS322S16).
 template <typename TileData, typename GlobalData>
 constexpr void check_store_quant_valid()
 {
@@ -636,8 +637,9 @@ constexpr void check_store_quant_valid()
     using D = typename GlobalData::DType;
     static_assert((std::is_same_v<S, int32_t> || std::is_same_v<S, float>) &&
                       (std::is_same_v<D, half> || std::is_same_v<D, bfloat16_t> || std::is_same_v<D, int8_t> ||
-                       std::is_same_v<D, uint8_t>),
-                  "[PTO][SA] TSTORE pre-quant: int32 / float accumulators to half / bfloat16_t / int8_t / uint8_t only");
+                       std::is_same_v<D, uint8_t> || (std::is_same_v<D, int16_t> && std::is_same_v<S, int32_t>)),
+                  "[PTO][SA] TSTORE pre-quant: int32 / float accumulators to half / bfloat16_t / int8_t / uint8_t, int32 "
+                  "accumulators to int16_t");
 }
 } // namespace b200
 

@@ -36,7 +36,8 @@ typedef enum {
     PTO_B200_E4M3 = 5, /* float8_e4m3_t (fn variant: no inf, 0x7f NaN)      */
     PTO_B200_E5M2 = 6, /* float8_e5m2_t                                      */
     PTO_B200_E2M1 = 7, /* float4_e2m1x2_t: two 4-bit values per byte, the even element in the low nibble */
-    PTO_B200_U8 = 8    /* uint8_t (destination of the 8-bit pre-quant stores)     */
+    PTO_B200_U8 = 8,   /* uint8_t (destination of the 8-bit pre-quant stores)     */
+    PTO_B200_S16 = 9   /* int16_t (destination of the shifting pre-quant store)   */
 } pto_b200_dtype;
 
 typedef enum {
@@ -142,7 +143,9 @@ int pto_b200_gemm_s8_dequant(void* stream, uint8_t* out, const uint8_t* src0, co
  *                      19-bit float (sign, 8 exponent, 10 mantissa bits) in bits [31:13] of the word, i.e. fp32 with
  *                      the low 13 mantissa bits ignored (extract_m1_from_quant, common.hpp:116-137)
  *   relu != 0        : ReluPreMode::NormalRelu, applied after the scaling
- * Half outputs are clamped to +-65504 as the reference does. The int16 destination (SHIFTS322S16) is not implemented.
+ *   out_dtype S16 (in_dtype S8 only; SHIFTS322S16 / VSHIFTS322S16): out = relu?( int16( acc >> (1 + bits [35:32] of the
+ *   word) ) ), an arithmetic shift and the wrapping cast of the reference; no scale is applied.
+ * Half outputs are clamped to +-65504 as the reference does.
  */
 int pto_b200_gemm_quant(void* stream, uint8_t* out, const uint8_t* src0, const uint8_t* src1, int m, int n, int k,
                         long long lda, long long ldb, long long ldc, int in_dtype, int out_dtype,

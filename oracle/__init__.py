@@ -171,7 +171,7 @@ def dequant_bf16(acc: np.ndarray, s_row: np.ndarray, s_col: np.ndarray, truncate
     return out
 
 
-OUT_BF16, OUT_F16, OUT_S8, OUT_U8 = 0, 1, 2, 3
+OUT_BF16, OUT_F16, OUT_S8, OUT_U8, OUT_S16 = 0, 1, 2, 3, 4
 
 
 def quant_store(acc: np.ndarray, words, vector: bool, relu: bool = False, out_f16=False) -> np.ndarray:

@@ -547,7 +547,7 @@ void pto_oracle_dequant_bf16(const int32_t* acc, const float* s_row, const float
    the overloads select them (common.hpp:58-108): int32 / float accumulators to bf16 / half, scalar form (fp32 scale in
    bits [31:0] of the word, one word for the whole tile) or vector form (one word per column, scale = the 19-bit float
    in bits [31:13]), optional ReLU after the scaling. Saturation control of the task cookie is off (its default).
-   out_f16: 0 bfloat16, 1 half, 2 int8, 3 uint8 destinations. */
+   out_f16: 0 bfloat16, 1 half, 2 int8, 3 uint8, 4 int16 (int32 accumulators only) destinations. */
 void pto_oracle_quant_store(const void* acc, int acc_is_int, const uint64_t* words, int vector, int relu, int out_f16,
                             uint16_t* out, int m, int n, long long ld_acc, long long ld_out)
 {
@@ -558,6 +558,19 @@ void pto_oracle_quant_store(const void* acc, int acc_is_int, const uint64_t* wor
             const float scale = vector ? scale_from_19_bits(lo) : lo;
             const float src = acc_is_int ? (float)((const int32_t*)acc)[(size_t)i * ld_acc + j]
                                          : ((const float*)acc)[(size_t)i * ld_acc + j];
+            if (out_f16 == 4) {
+                /* SHIFTS322S16 / VSHIFTS322S16 (common.hpp:172-178): the int32 accumulator shifted right (arithmetic)
+                   by 1 + bits [35:32] of the word, then narrowed to int16 by the cast (it wraps; the clamp after it
+                   has nothing left to do); ReLU on the result. */
+                const int shift = (int)((w >> 32) & 0xFu) + 1;
+                const int32_t shifted = ((const int32_t*)acc)[(size_t)i * ld_acc + j] >> shift;
+                int16_t v16 = (int16_t)shifted;
+                if (relu && v16 < 0) {
+                    v16 = 0;
+                }
+                out[(size_t)i * ld_out + j] = (uint16_t)v16;
+                continue;
+            }
             volatile float t = src * scale;
             float r = t;
             if (out_f16 >= 2) {

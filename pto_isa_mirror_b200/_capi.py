@@ -12,7 +12,7 @@ _LIB_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib")
 LIB_PATH = os.path.join(_LIB_DIR, "libpto_b200.so")
 
 # pto_b200_dtype
-F16, BF16, F32, S8, S32, E4M3, E5M2, E2M1, U8 = range(9)
+F16, BF16, F32, S8, S32, E4M3, E5M2, E2M1, U8, S16 = range(10)
 # pto_b200_b_layout
 B_DN, B_ND = 0, 1
 # return codes

@@ -43,7 +43,8 @@ enum EpilogueMode : int {
 // EPI_QUANT8 (REQ8 / VREQ8 for int32 accumulators, QF322B8_PRE / VQF322B8_PRE for float ones, :151-156): the word also
 // carries a 9-bit offset in bits [45:37], added before rounding to nearest even, and the sign flag in bit 46 (clamp to
 // -128..127 when set, else to 0..255); the 8-bit result is stored as is.
-enum QuantFlags : int { QUANT_ACC_S32 = 1, QUANT_OUT_F16 = 2, QUANT_RELU = 4, QUANT_VECTOR = 8 };
+// QUANT_OUT_S16 (SHIFTS322S16 / VSHIFTS322S16, :172-178): int16(acc >> (1 + bits [35:32] of the word)), no scale.
+enum QuantFlags : int { QUANT_ACC_S32 = 1, QUANT_OUT_F16 = 2, QUANT_RELU = 4, QUANT_VECTOR = 8, QUANT_OUT_S16 = 16 };
 
 struct GemmParams {
     void* c;
@@ -227,6 +228,30 @@ __device__ __forceinline__ void convert_chunk(const uint32_t (&v)[32], const Gem
         }
     } else {
         float f[32];
+        if constexpr (EPI == EPI_QUANT16) {
+            if ((p.quant_flags & QUANT_OUT_S16) != 0) {
+                // the arithmetic shift, the wrapping cast to int16, ReLU
+                const bool relu16 = (p.quant_flags & QUANT_RELU) != 0;
+                const bool vector16 = (p.quant_flags & QUANT_VECTOR) != 0;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const unsigned long long word =
+                        vector16 ? ((i < n_left) ? __ldg(p.quant_words + col0 + i) : 0ull) : p.quant_word;
+                    const int shift = static_cast<int>((word >> 32) & 0xFull) + 1;
+                    int v16 = static_cast<short>(static_cast<int>(w[i]) >> shift);
+                    if (relu16 && v16 < 0) {
+                        v16 = 0;
+                    }
+                    const uint32_t bits = static_cast<uint32_t>(v16) & 0xFFFFu;
+                    if ((i & 1) == 0) {
+                        o[i >> 1] = bits;
+                    } else {
+                        o[i >> 1] |= bits << 16;
+                    }
+                }
+                return;
+            }
+        }
         if constexpr (EPI == EPI_QUANT16) {
             // quantize_element (include/pto/cpu/common.hpp:139-185): float(acc) * scale, the half forms clamp to
             // +-65504 (always for int32 accumulators, finite values only for float ones), ReLU after the scaling.

@@ -112,6 +112,7 @@ int elem_size(int dtype)
     switch (dtype) {
         case PTO_B200_F16:
         case PTO_B200_BF16:
+        case PTO_B200_S16:
             return 2;
         case PTO_B200_F32:
         case PTO_B200_S32:
@@ -137,6 +138,9 @@ int make_tensor_map(CUtensorMap* map, int dtype, const void* base, long long row
             break;
         case PTO_B200_BF16:
             dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+            break;
+        case PTO_B200_S16:
+            dt = CU_TENSOR_MAP_DATA_TYPE_UINT16; // store maps only: the bytes move unchanged
             break;
         case PTO_B200_F32:
         case PTO_B200_S32:
@@ -577,7 +581,9 @@ extern "C" int pto_b200_gemm_quant(void* stream, uint8_t* out, const uint8_t* sr
     const bool is16 = (in_dtype == PTO_B200_F16 || in_dtype == PTO_B200_BF16);
     const bool is8 = (in_dtype == PTO_B200_S8);
     const bool out8 = (out_dtype == PTO_B200_S8 || out_dtype == PTO_B200_U8);
-    if ((!is16 && !is8) || !(out_dtype == PTO_B200_BF16 || out_dtype == PTO_B200_F16 || out8)) {
+    const bool out_s16 = (out_dtype == PTO_B200_S16);
+    if ((!is16 && !is8) || !(out_dtype == PTO_B200_BF16 || out_dtype == PTO_B200_F16 || out8 || out_s16) ||
+        (out_s16 && !is8)) { // the shift form exists for int32 accumulators only
         return PTO_B200_EDTYPE;
     }
     if (fp_words != nullptr && (reinterpret_cast<uintptr_t>(fp_words) & 7u)) {
@@ -599,6 +605,7 @@ extern "C" int pto_b200_gemm_quant(void* stream, uint8_t* out, const uint8_t* sr
     p.quant_word = pre_quant_scalar;
     p.quant_words = fp_words;
     p.quant_flags = (is8 ? QUANT_ACC_S32 : 0) | (out_dtype == PTO_B200_F16 ? QUANT_OUT_F16 : 0) |
+                    (out_s16 ? QUANT_OUT_S16 : 0) |
                     (relu ? QUANT_RELU : 0) | (fp_words != nullptr ? QUANT_VECTOR : 0);
     CUtensorMap ta, tb;
     if (int rc = make_tensor_map(&ta, in_dtype, src0, m, k, lda, kelems, kBlockM)) {

@@ -21,6 +21,7 @@ _TORCH_TO_PTO = {
     torch.int8: S8,
     torch.int32: S32,
     torch.uint8: _capi.U8,
+    torch.int16: _capi.S16,
 }
 _PTO_TO_TORCH = {v: k for k, v in _TORCH_TO_PTO.items()}
 if hasattr(torch, "float8_e4m3fn"):
@@ -148,7 +149,8 @@ def gemm_quant(a: torch.Tensor, b_dn: torch.Tensor, out_dtype: torch.dtype = tor
     CUDA tensor of n 64-bit words (int64 / uint64), one per column, whose bits [31:13] hold the scale. a, b_dn: int8
     (int32 accumulators) or float16 / bfloat16 (float32 accumulators); the result is bfloat16 or float16, or - the
     REQ8 / QF322B8_PRE forms - int8 / uint8: round(acc * scale + offset) with the word's offset (bits [45:37]) and sign
-    flag (bit 46: clamp to -128..127, else to 0..255)."""
+    flag (bit 46: clamp to -128..127, else to 0..255); or int16 for int8 inputs - the SHIFTS322S16 form:
+    int16(acc >> (1 + bits [35:32] of the word))."""
     lib = _capi.load()
     _require_cuda_2d(a, "a")
     _require_cuda_2d(b_dn, "b_dn")
@@ -160,8 +162,9 @@ def gemm_quant(a: torch.Tensor, b_dn: torch.Tensor, out_dtype: torch.dtype = tor
         raise ValueError("inner dimensions differ")
     if out is None:
         out = torch.empty((m, n), dtype=out_dtype, device=a.device)
-    elif tuple(out.shape) != (m, n) or out.dtype not in (torch.bfloat16, torch.float16, torch.int8, torch.uint8):
-        raise ValueError("out must be [m, n] bfloat16, float16, int8 or uint8")
+    elif tuple(out.shape) != (m, n) or out.dtype not in (torch.bfloat16, torch.float16, torch.int8, torch.uint8,
+                                                         torch.int16):
+        raise ValueError("out must be [m, n] bfloat16, float16, int8, uint8 or int16")
     words_ptr = None
     if fp_words is not None:
         if not fp_words.is_cuda or fp_words.element_size() != 8 or fp_words.numel() != n or not fp_words.is_contiguous():

@@ -451,3 +451,39 @@ def test_quant_store_8_bit_on_the_pair_kernel(kind):
                 want = oracle.quant_store(acc, vec if vector else scalar, vector, relu, oracle.OUT_U8).astype(np.uint8)
                 assert np.array_equal(got[1:m + 1, :n], want), (kind, vector, relu, pitch)
                 assert (got[0] == 77).all() and (got[m + 1] == 77).all() and (got[:, n:] == 77).all()
+
+
+@pytest.mark.parametrize("name,words,vector,relu", [("s32_scalar_s16", "w_shift", False, False),
+                                                    ("s32_vector_s16", "vec_shift", True, False),
+                                                    ("s32_vector_s16_relu", "vec_shift", True, True)])
+def test_quant_store_int16_shift_golden_bit_exact(name, words, vector, relu):
+    """SHIFTS322S16 / VSHIFTS322S16 on the int8 tile of configuration 3 against the simulator's own outputs."""
+    g = golden("quant_store_s16")
+    a, b, _, _ = gd.s8_inputs(128, 256, 1024, 2)
+    out = pto.gemm_quant(dev(a), dev(b), torch.int16, pre_quant_scalar=int(g[words][0]),
+                         fp_words=words_dev(g[words]) if vector else None, relu=relu)
+    assert np.array_equal(host(out).view(np.uint16), g[name])
+
+
+def test_quant_store_int16_on_the_pair_kernel():
+    """The shift form on a ragged problem that takes the CTA-pair kernel (TMA store boxes for the 16-byte pitch, register
+    stores for the odd one), against the oracle's store applied to the GPU's own accumulators."""
+    m, n, k = 2300, 2328, 256
+    a, b, _, _ = gd.s8_inputs(m, n, k, 95)
+    ta, tb = dev(a), dev(b)
+    acc = host(pto.gemm(ta, tb, torch.int32))
+    vec = ((np.arange(n) % 7).astype(np.uint64) << np.uint64(32)) | np.uint64(0x777)
+    scalar = np.array([np.uint64(2) << np.uint64(32)], dtype=np.uint64)
+    for vector in (False, True):
+        for relu in (False, True):
+            for pitch in (n, n + 5):
+                buf = torch.full((m + 2, pitch), 77, dtype=torch.int16, device=DEV)
+                pto.gemm_quant(ta, tb, torch.int16, pre_quant_scalar=int(scalar[0]),
+                               fp_words=words_dev(vec) if vector else None, relu=relu, out=buf[1:m + 1, :n])
+                got = host(buf).view(np.uint16)
+                want = oracle.quant_store(acc, vec if vector else scalar, vector, relu, oracle.OUT_S16)
+                assert np.array_equal(got[1:m + 1, :n], want), (vector, relu, pitch)
+                assert (got[0] == 77).all() and (got[m + 1] == 77).all() and (got[:, n:] == 77).all()
+    with pytest.raises(pto.PtoB200Error):                       # float accumulators have no shift form
+        pto.gemm_quant(torch.zeros((128, 64), dtype=torch.bfloat16, device=DEV),
+                       torch.zeros((128, 64), dtype=torch.bfloat16, device=DEV), torch.int16)
