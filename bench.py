@@ -71,6 +71,7 @@ WORKLOADS = {
     "gemv_bf16_8192x32768": dict(kind="gemv", m=1, n=32768, k=8192),
     "gemv_mx_e4m3_8192x32768": dict(kind="gemv_mx", m=1, n=32768, k=8192),
     "mx_quantize_32768x8192": dict(kind="quant", m=32768, n=1, k=8192),
+    "mxfp4_quantize_32768x8192": dict(kind="quant", m=32768, n=1, k=8192, fmt="e2m1"),
 }
 
 
@@ -585,24 +586,26 @@ def make_step(name: str, spec: dict, dev, seed: int, world=1, rank=0, panels=8, 
         step.bytes = n * k + n * k // 32 + k + k // 32 + n * 4
         return step, 2.0 * n * k, 2 * (n * k + n * k // 32), 2
     if kind == "quant":
-        srcs = [torch.randn((m, k), generator=gen, device=dev) for _ in range(2)]             # 512 MiB > L2
-        q_data = torch.empty((m, k), dtype=torch.uint8, device=dev)
+        fp4 = spec.get("fmt") == "e2m1"                                                       # MXFP4: two codes per byte
+        srcs = [torch.randn((m, k), generator=gen, device=dev) for _ in range(2)]             # at least 512 MiB > L2
+        q_data = torch.empty((m, k // 2 if fp4 else k), dtype=torch.uint8, device=dev)
         q_scales = torch.empty((m, k // 32), dtype=torch.uint8, device=dev)
+        quantise = pto.mx_quantize_e2m1 if fp4 else pto.mx_quantize_e4m3
 
         def step(i):
-            pto.mx_quantize_e4m3(srcs[i % 2], data=q_data, scales=q_scales)
+            quantise(srcs[i % 2], data=q_data, scales=q_scales)
 
         def parity():
             import oracle
 
-            pto.mx_quantize_e4m3(srcs[0], data=q_data, scales=q_scales)
+            quantise(srcs[0], data=q_data, scales=q_scales)
             torch.cuda.synchronize(dev)
-            rd, rs = oracle.mx_quantize_e4m3(srcs[0][:256].cpu().numpy())
+            rd, rs = (oracle.mx_quantize_e2m1 if fp4 else oracle.mx_quantize_e4m3)(srcs[0][:256].cpu().numpy())
             exact = bool(np.array_equal(q_data[:256].cpu().numpy(), rd) and np.array_equal(q_scales[:256].cpu().numpy(), rs))
             return {"rows": 256, "bit_exact": exact, "ok": exact}
 
         step.parity = parity
-        step.bytes = int(m * k * (4 + 1 + 1 / 32))
+        step.bytes = int(m * k * (4 + (0.5 if fp4 else 1) + 1 / 32))
         return step, 0.0, 2 * m * k * 4, 2
     if kind == "allgather":
         import torch.distributed as dist
