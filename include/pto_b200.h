@@ -180,7 +180,7 @@ size_t pto_b200_gemm_mx_workspace_bytes(int m, int n, int k);
 /*
  * pto_b200_gemm_mx in two steps, for scales that do not change between calls (the weights' scales) or that a producer
  * can write in the tiled form directly: pto_b200_mx_retile_scales fills the workspace from the reference-layout scale
- * tensors (the two small re-tile kernels, 3.6 % of a 16384 x 8192 x 8192 call), pto_b200_gemm_mx_pretiled multiplies
+ * tensors (one small re-tile kernel, about 3 % of a 16384 x 8192 x 8192 call), pto_b200_gemm_mx_pretiled multiplies
  * with a workspace that was filled earlier for the same m, n, k. The reference's counterpart are its pre-tiled scale
  * layouts, Layout::MX_A_ZZ / Layout::MX_B_NN (include/pto/common/pto_tile.hpp:849-881,943-975), whose fractal order
  * belongs to its L0 scale buffers; here the order is the one tcgen05.cp copies into tensor memory: 512-byte atoms

@@ -659,12 +659,23 @@ __global__ void __launch_bounds__(kNumThreads, 1)
 // Layout::MX_B_DN for B; include/pto/common/pto_tile.hpp:883-910,1073-1102) into 512-byte atoms the
 // tcgen05.cp 32x128b.warpx4 copy expects: atom (k_block, row_block) holds 128 rows x 4 scales with
 // byte offset (r % 32) * 16 + (r / 32) * 4 + j. Rows / K-blocks past the end get 127 (= 2^0).
-__global__ void retile_scales_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int rows,
-                                     int k_groups, long long ld, int row_blocks, int k_blocks)
+// One launch re-tiles both operands' scales: items [0, a_blocks * k_blocks * 128) belong to A, the rest to B.
+__global__ void retile_scales_kernel(const uint8_t* __restrict__ src_a, uint8_t* __restrict__ dst_a, int rows_a,
+                                     long long ld_a, int a_blocks, const uint8_t* __restrict__ src_b,
+                                     uint8_t* __restrict__ dst_b, int rows_b, long long ld_b, int b_blocks, int k_groups,
+                                     int k_blocks)
 {
-    const long long total = static_cast<long long>(row_blocks) * k_blocks * 128;
-    for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long total_a = static_cast<long long>(a_blocks) * k_blocks * 128;
+    const long long total = total_a + static_cast<long long>(b_blocks) * k_blocks * 128;
+    for (long long it = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; it < total;
+         it += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const bool is_a = it < total_a;
+        const long long i = is_a ? it : it - total_a;
+        const uint8_t* src = is_a ? src_a : src_b;
+        uint8_t* dst = is_a ? dst_a : dst_b;
+        const int rows = is_a ? rows_a : rows_b;
+        const long long ld = is_a ? ld_a : ld_b;
+        const int row_blocks = is_a ? a_blocks : b_blocks;
         const int r_in = static_cast<int>(i % 128);
         const long long atom = i / 128;
         const int rb = static_cast<int>(atom % row_blocks);

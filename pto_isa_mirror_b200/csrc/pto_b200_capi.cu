@@ -823,14 +823,12 @@ static int gemm_mx_impl(void* stream, uint8_t* out, const uint8_t* src0, const u
         } else {
             p.idesc = make_idesc(0, a_fmt, b_fmt, false, block_n, true);
         }
-        const long long ta_items = static_cast<long long>(a_blocks) * p.k_blocks * 128;
-        const long long tb_items = static_cast<long long>(b_blocks) * p.k_blocks * 128;
-        const int ga = static_cast<int>((ta_items + 255) / 256 < 4096 ? (ta_items + 255) / 256 : 4096);
-        const int gb = static_cast<int>((tb_items + 255) / 256 < 4096 ? (tb_items + 255) / 256 : 4096);
+        const long long items = (static_cast<long long>(a_blocks) + b_blocks) * p.k_blocks * 128;
+        const int grid = static_cast<int>((items + 255) / 256 < 8192 ? (items + 255) / 256 : 8192);
         if (steps & MX_RETILE) {
-            retile_scales_kernel<<<ga, 256, 0, s>>>(src2, sfa_ws, m, k / 32, ld_sfa, a_blocks, p.k_blocks);
-            retile_scales_kernel<<<gb, 256, 0, s>>>(src3, sfb_ws, n, k / 32, ld_sfb, b_blocks, p.k_blocks);
-            g_launches.fetch_add(2, std::memory_order_relaxed);
+            retile_scales_kernel<<<grid, 256, 0, s>>>(src2, sfa_ws, m, ld_sfa, a_blocks, src3, sfb_ws, n, ld_sfb, b_blocks,
+                                                      k / 32, p.k_blocks);
+            g_launches.fetch_add(1, std::memory_order_relaxed);
             if (int rc = note_cuda(cudaGetLastError(), "retile_scales launch")) {
                 return rc;
             }
